@@ -1,0 +1,365 @@
+"""Benchmark of the low-bit matmul hot path.
+
+Headline workload (N = 1 GPU): decode-size A16W4 GEMV, M = 1, bf16, 8192 x 8192, group_size 128,
+with bias, over 32 DISTINCT layers per step (1.1 GB of packed weights, far larger than the 126 MB L2,
+so every launch streams its weights from HBM).  metric = algorithmic HBM GB/s.
+
+  value     kernel-only: the 32 gl_matmul launches of a step replayed as one CUDA graph, inputs resident
+  e2e       the public API (GemLiteLinear.forward) with host buffers: pinned-host x -> device, 32 chained
+            layer forwards, result -> host, every step (also as a CUDA graph; eager Python numbers beside it)
+  roofline  algorithmic bytes per launch / average launch time, against the measured HBM copy peak
+  cpu_baseline   the reference's CPU-capable torch path (unpack -> (W_q - z) * s -> matmul) on host cores
+  sweep     other batch sizes / formats of the benchmark configurations (GB/s for M <= 16, TFLOP/s above)
+
+`--impl reference` times that CPU path alone (the reference has no GPU-free way to run its Triton kernels;
+its CPU implementation is what can run without them).  With --gpus N > 1 (torchrun) every rank runs the
+same per-GPU workload (weak scaling, no data-path collective) and rank 0 reports the aggregate.
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_FEAT = K_FEAT = 8192
+GROUP = 128
+LAYERS = 32
+
+
+def algorithmic_bytes(M, N, K, nbits, group, itemsize=2, bias=True):
+    """Bytes each operand is read / written once: packed W + scales + zeros + x + out (+ bias)."""
+    G = K // group
+    return N * K * nbits // 8 + G * N * 2 * itemsize + M * K * itemsize + M * N * itemsize + (N * itemsize if bias else 0)
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 1585.3)), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, reasons = [], None, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx = float(r[1])
+            except Exception:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# -------------------------------------------------------------------------------------------------
+def cpu_path_sample(seconds=12.0, N=N_FEAT, K=K_FEAT, nbits=4, group=GROUP):
+    """Time the reference's CPU path (oracle port, torch ops, all host threads) for about `seconds`."""
+    from oracle import oracle
+    torch.set_num_threads(os.cpu_count() or 1)
+    g = torch.Generator().manual_seed(2000)
+    e = 32 // nbits
+    Wp = torch.randint(-2 ** 31, 2 ** 31 - 1, (N, K // e), generator=g, dtype=torch.int64).to(torch.int32)
+    s = (torch.randn(N * K // group, 1, generator=g).abs() * 0.02)
+    z = torch.rand(N * K // group, 1, generator=g) * (2 ** nbits - 1)
+    x = torch.randn(1, K, generator=g)
+    oracle.cpu_reference_forward(x, Wp, s, z, nbits, group)     # warm-up
+    times, t_end = [], time.perf_counter() + seconds
+    while time.perf_counter() < t_end or len(times) < 3:
+        t0 = time.perf_counter()
+        oracle.cpu_reference_forward(x, Wp, s, z, nbits, group)
+        times.append(time.perf_counter() - t0)
+        if len(times) >= 50:
+            break
+    times.sort()
+    med = times[len(times) // 2]
+    gbs = algorithmic_bytes(1, N, K, nbits, group, bias=False) / med / 1e9
+    return {"value": gbs, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": "%d forward passes of one %dx%d A16W%d layer (M=1, gs=%d): unpack + dequant + matmul in fp32 torch ops, median %.1f ms"
+                      % (len(times), N, K, nbits, group, med * 1e3), "ms_per_layer": med * 1e3}
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    per = max(2.0, min(20.0, 60.0 / max(1, args.steps + args.warmup)))
+    for _ in range(args.warmup):
+        cpu_path_sample(seconds=per / 4)
+    vals = [cpu_path_sample(seconds=per) for _ in range(max(1, args.steps))]
+    v = sum(r["value"] for r in vals) / len(vals)
+    ms = sum(r["ms_per_layer"] for r in vals) / len(vals) * LAYERS
+    base = dict(vals[-1]); base["value"] = v
+    print(json.dumps({
+        "impl": "reference", "metric": "A16W4 GEMV HBM GB/s (M=1, 8192x8192, gs=128, bf16)", "value": v, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "cfg2 A16W4 M=1 8192x8192 gs128: reference CPU path (torch unpack + dequant + matmul), one layer per sample", "l2": "n/a (CPU)"},
+        "cpu_baseline": base, "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0}))
+
+
+# -------------------------------------------------------------------------------------------------
+def build_layers(device, n_layers, M_max, nbits=4, group=GROUP, N=N_FEAT, K=K_FEAT, seed=1234):
+    from gemlite_b200 import helper
+    g = torch.Generator(device=device).manual_seed(seed)
+    proc = helper.A16Wn_HQQ_INT(device=str(device), dtype=torch.bfloat16, W_nbits=nbits)
+    layers = []
+    for _ in range(n_layers):
+        W_q = torch.randint(0, 2 ** nbits, (N, K), generator=g, device=device, dtype=torch.int32).to(torch.uint8)
+        s = (torch.randn(N * K // group, 1, generator=g, device=device).abs() * 0.02).to(torch.bfloat16)
+        # scales of the benchmark distribution make activations grow ~7x per chained layer; they are
+        # divided by that factor so that 32 chained layers stay finite (timing does not depend on it)
+        s = s / 6.7
+        z = (torch.rand(N * K // group, 1, generator=g, device=device) * (2 ** nbits - 1)).to(torch.bfloat16)
+        b = (torch.randn(N, generator=g, device=device) * 0.01).to(torch.bfloat16)
+        layers.append(proc.from_weights(W_q, s, z, bias=b))
+        del W_q
+    return layers
+
+
+def time_graph(fn, steps, warmup, stream):
+    """Capture fn() once, replay warmup + steps times; returns ms per step (CUDA events on `stream`)."""
+    with torch.cuda.stream(stream):
+        for _ in range(2):
+            fn()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            fn()
+        for _ in range(warmup):
+            graph.replay()
+        stream.synchronize()
+        return graph
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        return run_reference_arm(args)
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+
+    from gemlite_b200 import _lib, core
+    L = _lib.lib()
+    hbm_peak, bf16_peak, peak_kind = measured_peaks()
+    M = 1
+    layers = build_layers(device, LAYERS, M)
+    stream = torch.cuda.Stream(device)
+    bytes_per_launch = algorithmic_bytes(M, N_FEAT, K_FEAT, 4, GROUP)
+
+    # ---- kernel-only: 32 gl_matmul launches per step through the C ABI, inputs resident ----------
+    x_dev = torch.randn(M, K_FEAT, device=device, dtype=torch.bfloat16)
+    outs = [torch.empty(M, N_FEAT, device=device, dtype=torch.bfloat16) for _ in range(LAYERS)]
+    arg_structs = []
+    with torch.cuda.stream(stream):
+        for lyr, out in zip(layers, outs):
+            a = core._fill_args(x_dev, lyr.bias, lyr.W_q, lyr.scales, lyr.zeros, None, None, out, lyr.get_meta_args(), -1)
+            ws = core._workspace(device, int(L.gl_matmul_workspace_bytes(ctypes.byref(a))))
+            if ws is not None:
+                a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+            arg_structs.append(a)
+    kernel_name = L.gl_matmul_kernel_name(ctypes.byref(arg_structs[0])).decode()
+
+    def step_kernels():
+        sp = torch.cuda.current_stream(device).cuda_stream
+        for a in arg_structs:
+            st = L.gl_matmul(ctypes.byref(a), sp)
+            if st != 0:
+                raise RuntimeError(L.gl_last_error().decode())
+
+    graph = time_graph(step_kernels, args.steps, args.warmup, stream)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    time.sleep(0.3)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record(stream)
+    barrier()
+    ms_kernel = e0.elapsed_time(e1) / args.steps
+
+    # ---- end to end: pinned host x -> device, 32 chained GemLiteLinear.forward, result -> host ---
+    x_host = torch.randn(M, K_FEAT, dtype=torch.bfloat16).pin_memory()
+    y_host = torch.empty(M, N_FEAT, dtype=torch.bfloat16).pin_memory()
+    x_in = torch.empty(M, K_FEAT, device=device, dtype=torch.bfloat16)
+
+    def step_e2e():
+        x_in.copy_(x_host, non_blocking=True)
+        h = x_in
+        for lyr in layers:
+            h = lyr(h)
+        y_host.copy_(h, non_blocking=True)
+
+    graph_e2e = time_graph(step_e2e, args.steps, args.warmup, stream)
+    barrier()
+    with torch.cuda.stream(stream):
+        e0.record(stream)
+        for _ in range(args.steps):
+            graph_e2e.replay()
+        e1.record(stream)
+    barrier()
+    ms_e2e = e0.elapsed_time(e1) / args.steps
+    finite = bool(torch.isfinite(y_host.float()).all())
+    # eager Python path (no graph), wall-bounded by host launch overhead
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            step_e2e()
+        stream.synchronize()
+        e0.record(stream)
+        for _ in range(max(5, args.steps // 5)):
+            step_e2e()
+        e1.record(stream)
+        stream.synchronize()
+    ms_eager = e0.elapsed_time(e1) / max(5, args.steps // 5)
+    clocks = sampler.stop()
+
+    # ---- max over ranks ------------------------------------------------------------------------
+    if dist is not None:
+        t = torch.tensor([ms_kernel, ms_e2e, ms_eager], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_kernel, ms_e2e, ms_eager = t.tolist()
+    total_bytes = bytes_per_launch * LAYERS * world
+    value = total_bytes / (ms_kernel * 1e-3) / 1e9
+    e2e_value = total_bytes / (ms_e2e * 1e-3) / 1e9
+    achieved = bytes_per_launch * LAYERS / (ms_kernel * 1e-3) / 1e9     # per GPU, per launch average
+
+    result = {
+        "metric": "A16W4 GEMV HBM GB/s (M=1, 8192x8192, gs=128, bf16)", "value": value, "unit": "GB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_kernel, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "cfg2 A16W4 M=1 bf16 8192x8192 gs128 +bias: %d distinct layers per step, CUDA-graph replay" % LAYERS,
+                   "l2": "inputs larger than L2 (%.2f GB of packed weights per step cycle through 126 MB)" % (LAYERS * bytes_per_launch / 1e9),
+                   "kernel": kernel_name, "parallelism": "replicas x%d" % world, "us_per_launch": ms_kernel * 1e3 / LAYERS},
+        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2,
+                "ms_per_step": ms_e2e, "mode": "GemLiteLinear.forward x%d chained, CUDA-graph replay incl. H2D/D2H copies" % LAYERS,
+                "eager_ms_per_step": ms_eager, "eager_value": total_bytes / (ms_eager * 1e-3) / 1e9, "finite": finite},
+        "gpu_launches": args.steps * LAYERS,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+                     "traffic": None, "peak_kind": peak_kind, "frac_of_nominal_8000": achieved / 8000.0,
+                     "bytes_per_launch": bytes_per_launch},
+        "clocks": clocks,
+    }
+
+    if rank == 0 and not args.no_sweep:
+        result["sweep"] = sweep(device, layers, stream, hbm_peak, bf16_peak)
+    if rank == 0 and not args.no_cpu and world >= 1:
+        try:
+            result["cpu_baseline"] = cpu_path_sample(seconds=12.0)
+        except Exception as e:  # the CPU sample must not lose the GPU numbers
+            result["cpu_baseline"] = {"value": None, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port", "sample": "failed: %s" % e}
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(result))
+
+
+def sweep(device, layers, stream, hbm_peak, bf16_peak):
+    """Other batch sizes of the A16W4 configuration on the same 32 layers (graph replay, 10 steps)."""
+    from gemlite_b200 import _lib, core
+    L = _lib.lib()
+    res = []
+    for M in (1, 2, 4, 8, 16):
+        x = torch.randn(M, K_FEAT, device=device, dtype=torch.bfloat16)
+        outs = [torch.empty(M, N_FEAT, device=device, dtype=torch.bfloat16) for _ in layers]
+        structs = []
+        with torch.cuda.stream(stream):
+            for lyr, out in zip(layers, outs):
+                a = core._fill_args(x, lyr.bias, lyr.W_q, lyr.scales, lyr.zeros, None, None, out, lyr.get_meta_args(), -1)
+                ws = core._workspace(device, int(L.gl_matmul_workspace_bytes(ctypes.byref(a))))
+                if ws is not None:
+                    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+                structs.append(a)
+
+        def fn():
+            sp = torch.cuda.current_stream(device).cuda_stream
+            for a in structs:
+                if L.gl_matmul(ctypes.byref(a), sp) != 0:
+                    raise RuntimeError(L.gl_last_error().decode())
+        try:
+            graph = time_graph(fn, 10, 3, stream)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            with torch.cuda.stream(stream):
+                e0.record(stream)
+                for _ in range(10):
+                    graph.replay()
+                e1.record(stream)
+                stream.synchronize()
+            us = e0.elapsed_time(e1) / 10 / len(layers) * 1e3
+            b = algorithmic_bytes(M, N_FEAT, K_FEAT, 4, GROUP)
+            flops = 2.0 * M * N_FEAT * K_FEAT
+            res.append({"format": "A16W4", "M": M, "us_per_launch": us, "GBps": b / us / 1e3, "frac_hbm": b / us / 1e3 / hbm_peak,
+                        "TFLOPs": flops / us / 1e6, "kernel": L.gl_matmul_kernel_name(ctypes.byref(structs[0])).decode()})
+        except Exception as e:
+            res.append({"format": "A16W4", "M": M, "error": str(e)[:200]})
+    return res
+
+
+if __name__ == "__main__":
+    main()

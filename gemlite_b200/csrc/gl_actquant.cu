@@ -1,0 +1,290 @@
+// Dynamic activation quantisation kernels (HBM-bound elementwise + small reductions), sm_100a.
+//
+// Arithmetic follows the reference's active Triton kernels (aliases at
+// gemlite/quant_utils.py:2680-2684), in fp32 with IEEE division so that the results are
+// reproducible bit for bit:
+//   per-token fp8/int8   quant_utils.py:467-508
+//   mxfp8  (e8m0 per 32) quant_utils.py:1024-1093, power-of-two scale :697-705
+//   mxfp4  (e8m0 per 32) quant_utils.py:2005-2105, e2m1 by thresholds :66-73, 2081-2090
+//   nvfp4  (e4m3 per 16 + fp32 tensor scale) quant_utils.py:2161-2311, 2329-2431
+// Loads are 128-bit; one lane owns 8 consecutive k, a group of 32 (16) values is 4 (2)
+// adjacent lanes, so group maxima are one or two shuffles.  The NVFP4 tensor-wide amax is a
+// separate pass (atomicMax on the fp32 bit pattern) instead of the reference's in-kernel spin
+// barrier (quant_utils.py:2220-2231): nothing here waits on another CTA.
+#include "gl_common.cuh"
+
+namespace {
+
+__device__ __forceinline__ void load8(const void* x, int64_t idx, int dt, float (&v)[8]) {
+  if (dt == GL_FP32) {
+    const float4 a = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + idx)[0];
+    const float4 b = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + idx)[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  } else {
+    const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(x) + idx);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (dt == GL_BF16) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+      } else {
+        v[2 * i] = __half2float(__ushort_as_half((unsigned short)(w[i] & 0xffffu)));
+        v[2 * i + 1] = __half2float(__ushort_as_half((unsigned short)(w[i] >> 16)));
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// 2^ceil(log2(v)) by exponent bits, clamped to [2^-30, 2^127]; returns the biased exponent
+__device__ __forceinline__ uint32_t pow2_ceil_exp(float v) {
+  const uint32_t xi = __float_as_uint(v);
+  uint32_t e = (xi >> 23) & 0xffu;
+  if (xi & 0x7fffffu) e += 1u;
+  e = min(e, 254u);
+  e = max(e, 127u - 30u);
+  return e;
+}
+
+// e2m1 code of a scaled value: number of magnitude thresholds exceeded, sign in bit 3
+__device__ __forceinline__ uint32_t e2m1_code(float v) {
+  const float a = fabsf(v);
+  uint32_t idx = (a > 0.25f) + (a > 0.75f) + (a > 1.25f) + (a > 1.75f) + (a > 2.5f) + (a > 3.5f) + (a > 5.0f);
+  return (v >= 0.f) ? idx : (idx + 8u);
+}
+
+// ---------------------------------------------------------------------------------------------
+// per-token: one CTA per row (grid-stride), two passes over the row (second one hits L1/L2)
+template <bool INT8>
+__global__ void __launch_bounds__(256) per_token_kernel(const void* __restrict__ x, uint8_t* __restrict__ q,
+                                                        float* __restrict__ scales, int M, int K, int x_dtype) {
+  __shared__ float s_red[8];
+  __shared__ float s_scale;
+  const float qmax = INT8 ? 127.f : 448.f, qmin = INT8 ? -128.f : -448.f;
+  for (int m = blockIdx.x; m < M; m += gridDim.x) {
+    float amax = 0.f;
+    for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+      float v[8];
+      load8(x, (int64_t)m * K + k, x_dtype, v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    }
+    amax = warp_max(amax);
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float a = 0.f;
+      for (int i = 0; i < (int)(blockDim.x >> 5); ++i) a = fmaxf(a, s_red[i]);
+      const float s = fmaxf(a / qmax, 1e-6f);
+      s_scale = s;
+      scales[m] = s;
+    }
+    __syncthreads();
+    const float s = s_scale;
+    for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+      float v[8];
+      load8(x, (int64_t)m * K + k, x_dtype, v);
+      uint32_t o[2] = {0u, 0u};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float t = fminf(fmaxf(v[i] / s, qmin), qmax);
+        uint32_t b;
+        if (INT8) b = (uint32_t)(uint8_t)(int8_t)(int)roundf(t);
+        else b = (uint32_t)__nv_cvt_float_to_fp8(t, __NV_SATFINITE, __NV_E4M3);
+        o[i >> 2] |= b << (8 * (i & 3));
+      }
+      *reinterpret_cast<uint2*>(q + (int64_t)m * K + k) = make_uint2(o[0], o[1]);
+    }
+    __syncthreads();
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// mxfp4 / mxfp8: thread = 8 consecutive k of one row; 4 lanes = one group of 32
+template <bool FP4>
+__global__ void __launch_bounds__(256) mx_quant_kernel(const void* __restrict__ x, uint8_t* __restrict__ q,
+                                                       uint8_t* __restrict__ scales, int M, int Mpad, int K, int x_dtype) {
+  const int64_t units_per_row = K / 8;
+  const int64_t total = (int64_t)Mpad * units_per_row;
+  // the loop bound is warp-uniform so that every lane takes part in the group shuffles
+  for (int64_t u0 = blockIdx.x * (int64_t)blockDim.x + (threadIdx.x & ~31); u0 < total; u0 += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t u = u0 + (threadIdx.x & 31);
+    const bool valid = u < total;
+    const int m = valid ? (int)(u / units_per_row) : Mpad;
+    const int k = valid ? (int)(u % units_per_row) * 8 : 0;
+    float v[8];
+    const bool real = m < M;
+    if (real) load8(x, (int64_t)m * K + k, x_dtype, v);
+    else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = 0.f;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    const uint32_t e = pow2_ceil_exp(amax / (FP4 ? 6.f : 448.f));
+    const float scale = __uint_as_float(e << 23);
+    if (valid && (threadIdx.x & 3) == 0) scales[(int64_t)m * (K / 32) + k / 32] = real ? (uint8_t)e : (uint8_t)127;
+    if (!real) continue;
+    if (FP4) {
+      uint32_t o = 0u;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o |= e2m1_code(v[i] / scale) << (4 * i);
+      *reinterpret_cast<uint32_t*>(q + (int64_t)m * (K / 2) + k / 2) = o;
+    } else {
+      const float inv = 1.0f / scale;
+      uint32_t o[2] = {0u, 0u};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float t = fminf(fmaxf(v[i] * inv, -448.f), 448.f);
+        o[i >> 2] |= (uint32_t)__nv_cvt_float_to_fp8(t, __NV_SATFINITE, __NV_E4M3) << (8 * (i & 3));
+      }
+      *reinterpret_cast<uint2*>(q + (int64_t)m * K + k) = make_uint2(o[0], o[1]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// nvfp4 pass 1: tensor-wide max |x| as an fp32 bit pattern (non-negative floats order as uints)
+__global__ void __launch_bounds__(256) amax_kernel(const void* __restrict__ x, uint32_t* __restrict__ amax_bits,
+                                                   int64_t total_units, int x_dtype) {
+  float amax = 0.f;
+  for (int64_t u = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; u < total_units; u += (int64_t)gridDim.x * blockDim.x) {
+    float v[8];
+    load8(x, u * 8, x_dtype, v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  }
+  amax = warp_max(amax);
+  __shared__ float s_red[8];
+  if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float a = 0.f;
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) a = fmaxf(a, s_red[i]);
+    atomicMax(amax_bits, __float_as_uint(a));
+  }
+}
+
+// nvfp4 pass 2: thread = 8 consecutive k; 2 lanes = one group of 16
+__global__ void __launch_bounds__(256) nvfp4_quant_kernel(const void* __restrict__ x, uint8_t* __restrict__ q,
+                                                          uint8_t* __restrict__ scales, float* __restrict__ meta_out,
+                                                          const float* __restrict__ meta_in,
+                                                          const uint32_t* __restrict__ amax_bits, int M, int Mpad, int K,
+                                                          int x_dtype) {
+  float meta;
+  if (meta_in != nullptr) meta = *meta_in;
+  else meta = (448.f * 6.0f) / fmaxf(__uint_as_float(*amax_bits), 1e-6f);
+  if (blockIdx.x == 0 && threadIdx.x == 0) *meta_out = meta;
+  const int64_t units_per_row = K / 8;
+  const int64_t total = (int64_t)Mpad * units_per_row;
+  // the loop bound is warp-uniform so that every lane takes part in the group shuffles
+  for (int64_t u0 = blockIdx.x * (int64_t)blockDim.x + (threadIdx.x & ~31); u0 < total; u0 += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t u = u0 + (threadIdx.x & 31);
+    const bool valid = u < total;
+    const int m = valid ? (int)(u / units_per_row) : Mpad;
+    const int k = valid ? (int)(u % units_per_row) * 8 : 0;
+    const bool real = m < M;
+    float v[8];
+    if (real) load8(x, (int64_t)m * K + k, x_dtype, v);
+    else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = 0.f;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    const float sraw = fminf(amax * meta / 6.f, 448.f);
+    const uint8_t s8 = (uint8_t)__nv_cvt_float_to_fp8(sraw, __NV_SATFINITE, __NV_E4M3);
+    if (valid && (threadIdx.x & 1) == 0) scales[(int64_t)m * (K / 16) + k / 16] = real ? s8 : (uint8_t)0x38;  // 0x38 = 1.0 e4m3
+    if (!real) continue;
+    const float sfull = fmaxf(gl_e4m3_to_float(s8) / meta, 1e-6f);
+    uint32_t o = 0u;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o |= e2m1_code(v[i] / sfull) << (4 * i);
+    *reinterpret_cast<uint32_t*>(q + (int64_t)m * (K / 2) + k / 2) = o;
+  }
+}
+
+int check_x(const char* fn, const void* x, int M, int K, int x_dtype, int kmult) {
+  if (M < 0 || K <= 0) { gl_set_error("%s: bad shape M=%d K=%d", fn, M, K); return GL_E_INVALID; }
+  if (K % kmult != 0) { gl_set_error("%s: K=%d must be a multiple of %d", fn, K, kmult); return GL_E_INVALID; }
+  if (!(x_dtype == GL_FP16 || x_dtype == GL_BF16 || x_dtype == GL_FP32)) { gl_set_error("%s: unsupported activation dtype %d", fn, x_dtype); return GL_E_INVALID; }
+  if ((uintptr_t)x & 15) { gl_set_error("%s: x must be 16-byte aligned", fn); return GL_E_INVALID; }
+  return GL_OK;
+}
+unsigned grid_units(int64_t total_threads) {
+  int64_t b = gl_cdiv(total_threads, 256);
+  const int64_t cap = (int64_t)gl_num_sms() * 8;
+  if (b > cap) b = cap;
+  if (b < 1) b = 1;
+  return (unsigned)b;
+}
+
+}  // namespace
+
+extern "C" int gl_scale_activations_per_token(const void* x, void* q, float* scales, int32_t M, int32_t K,
+                                              int32_t x_dtype, int32_t q_dtype, void* stream) {
+  if (int rc = check_x("gl_scale_activations_per_token", x, M, K, x_dtype, 8)) return rc;
+  if (!(q_dtype == GL_FP8 || q_dtype == GL_INT8)) GL_FAIL(GL_E_INVALID, "gl_scale_activations_per_token: q_dtype must be FP8 (e4m3) or INT8, got %d", q_dtype);
+  if (M == 0) return GL_OK;
+  if (!q || !scales || ((uintptr_t)q & 7)) GL_FAIL(GL_E_INVALID, "gl_scale_activations_per_token: null or misaligned output");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int cap = gl_num_sms() * 8;
+  const unsigned grid = (unsigned)(M < cap ? M : cap);
+  if (q_dtype == GL_INT8) per_token_kernel<true><<<grid, 256, 0, st>>>(x, (uint8_t*)q, scales, M, K, x_dtype);
+  else per_token_kernel<false><<<grid, 256, 0, st>>>(x, (uint8_t*)q, scales, M, K, x_dtype);
+  GL_LAUNCH_CHECK("per_token_kernel");
+  return GL_OK;
+}
+
+extern "C" int gl_scale_activations_mxfp4(const void* x, uint8_t* q, uint8_t* scales, int32_t M, int32_t K,
+                                          int32_t x_dtype, void* stream) {
+  if (int rc = check_x("gl_scale_activations_mxfp4", x, M, K, x_dtype, 32)) return rc;
+  if (M == 0) return GL_OK;
+  if (!q || !scales || ((uintptr_t)q & 3)) GL_FAIL(GL_E_INVALID, "gl_scale_activations_mxfp4: null or misaligned output");
+  const int Mpad = (M + 31) / 32 * 32;
+  mx_quant_kernel<true><<<grid_units((int64_t)Mpad * (K / 8)), 256, 0, (cudaStream_t)stream>>>(x, q, scales, M, Mpad, K, x_dtype);
+  GL_LAUNCH_CHECK("mx_quant_kernel<fp4>");
+  return GL_OK;
+}
+
+extern "C" int gl_scale_activations_mxfp8(const void* x, uint8_t* q, uint8_t* scales, int32_t M, int32_t K,
+                                          int32_t x_dtype, void* stream) {
+  if (int rc = check_x("gl_scale_activations_mxfp8", x, M, K, x_dtype, 32)) return rc;
+  if (M == 0) return GL_OK;
+  if (!q || !scales || ((uintptr_t)q & 7)) GL_FAIL(GL_E_INVALID, "gl_scale_activations_mxfp8: null or misaligned output");
+  const int Mpad = (M + 31) / 32 * 32;
+  mx_quant_kernel<false><<<grid_units((int64_t)Mpad * (K / 8)), 256, 0, (cudaStream_t)stream>>>(x, q, scales, M, Mpad, K, x_dtype);
+  GL_LAUNCH_CHECK("mx_quant_kernel<fp8>");
+  return GL_OK;
+}
+
+extern "C" int gl_scale_activations_nvfp4(const void* x, uint8_t* q, uint8_t* scales, float* meta_scale,
+                                          const float* meta_in, uint32_t* amax_scratch, int32_t M, int32_t K,
+                                          int32_t x_dtype, void* stream) {
+  if (int rc = check_x("gl_scale_activations_nvfp4", x, M, K, x_dtype, 16)) return rc;
+  if (M == 0) return GL_OK;
+  if (!q || !scales || !meta_scale || ((uintptr_t)q & 3)) GL_FAIL(GL_E_INVALID, "gl_scale_activations_nvfp4: null or misaligned output");
+  if (meta_in == nullptr && amax_scratch == nullptr) GL_FAIL(GL_E_INVALID, "gl_scale_activations_nvfp4: amax_scratch needed for the dynamic tensor scale");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int Mpad = (M + 15) / 16 * 16;
+  if (meta_in == nullptr) {
+    GL_CUDA_CHECK(cudaMemsetAsync(amax_scratch, 0, sizeof(uint32_t), st));
+    const int64_t units = (int64_t)M * (K / 8);
+    amax_kernel<<<grid_units(units), 256, 0, st>>>(x, amax_scratch, units, x_dtype);
+    GL_LAUNCH_CHECK("amax_kernel");
+  }
+  nvfp4_quant_kernel<<<grid_units((int64_t)Mpad * (K / 8)), 256, 0, st>>>(x, q, scales, meta_scale, meta_in, amax_scratch, M, Mpad, K, x_dtype);
+  GL_LAUNCH_CHECK("nvfp4_quant_kernel");
+  return GL_OK;
+}

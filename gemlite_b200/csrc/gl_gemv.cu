@@ -1,0 +1,452 @@
+// Streaming low-bit GEMV / skinny GEMM for decode sizes (M <= 32), sm_100a.
+//
+// Replaces the reference's gemv / gemv_revsplitK / gemv_splitK Triton kernels
+// (gemlite/triton_kernels/gemv_kernels.py:245-426, gemv_revsplitK_kernels.py:248-443,
+// gemv_splitK_kernels.py:257-477) and its small-M gemm_splitK path
+// (gemm_splitK_kernels.py:300-523) for packed integer weights.
+//
+// The kernel is HBM-bound, so it is organised around the weight stream:
+//  * W_q is the reference's packed layout, int32 [K/e, N] row-major, e = 32/W_nbits values of
+//    one output column per word (gemlite/bitpack.py:36-60, gemlite/core.py:623-637).  Every
+//    lane issues 128-bit loads of 4 adjacent columns; a warp instruction covers 4 packed
+//    rows x 128 bytes, and U such loads per lane are kept in flight (register double buffer).
+//  * Fields are unpacked two at a time with one shift + one LOP3 into fp16/bf16 "magic
+//    number" pairs (BIAS+q) and fed straight to mma.sync m16n8k16 as the A operand (16
+//    output columns x 16 k); the activations are the B operand (8 batch rows per MMA), so
+//    M = 1..8 costs one MMA per 256 weights and M <= 32 re-uses the same A fragments.  The
+//    k order inside a packed word is permuted identically on both operands, which a dot
+//    product does not see.
+//  * Dequantisation is applied per group to the fp32 accumulators, not per weight:
+//        sum_k x_k*(q_k*s + z')  =  s * sum_k x_k*(BIAS+q_k)  +  (z' - BIAS*s) * sum_k x_k
+//    with the group sums of x computed once per CTA while x is staged in shared memory.
+//  * K is split over blockIdx.y.  Partial tiles go to an fp32 workspace; the last CTA to
+//    arrive for a column tile (arrival counter, no spinning) adds them in slice order, so the
+//    result is deterministic, then applies channel scales / bias and writes the output once.
+#include "gl_common.cuh"
+
+namespace {
+
+struct GemvParams {
+  const void* x; const int32_t* w; const void* scales; const void* zeros; const void* bias;
+  void* out; float* partials; unsigned int* counters;
+  int M, N, K;
+  int T;            // iterations over K: one iteration = 4 packed rows = 4*e k-values
+  int gi;           // iterations per quantisation group
+  int splitK;
+  int W_group_mode, channel_scale_mode, zero_is_scalar;
+  int out_dtype;
+  int max_slice_iters;
+};
+
+template <typename XT> struct XTraits;
+template <> struct XTraits<__nv_bfloat16> {
+  static constexpr uint32_t MAGIC = 0x43004300u;  // 128.0 | q, exact for q < 128
+  static constexpr float BIAS = 128.f;
+  __device__ static float to_float(uint16_t v) { return __uint_as_float((uint32_t)v << 16); }
+};
+template <> struct XTraits<__half> {
+  static constexpr uint32_t MAGIC = 0x64006400u;  // 1024.0 | q, exact for q < 1024
+  static constexpr float BIAS = 1024.f;
+  __device__ static float to_float(uint16_t v) { return __half2float(__ushort_as_half(v)); }
+};
+
+template <typename XT>
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1);
+template <>
+__device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                                        uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma16816<__half>(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                                 uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ int4 ldg_stream(const int32_t* p) {
+  int4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.s32 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+// load 4 consecutive meta values (scales / zeros of this lane's 4 columns) as fp32
+template <typename XT>
+__device__ __forceinline__ void load_meta4(const void* base, int64_t idx, float (&o)[4]) {
+  uint2 v = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(base) + idx);
+  o[0] = XTraits<XT>::to_float((uint16_t)(v.x & 0xffffu)); o[1] = XTraits<XT>::to_float((uint16_t)(v.x >> 16));
+  o[2] = XTraits<XT>::to_float((uint16_t)(v.y & 0xffffu)); o[3] = XTraits<XT>::to_float((uint16_t)(v.y >> 16));
+}
+
+// NB: bits per weight (4/2/1). XT: activation / scale dtype. MT: number of 8-row batch tiles
+// (M <= 8*MT). U: packed-row loads kept in flight per lane (per buffer).
+template <int NB, typename XT, int MT, int U>
+__global__ void __launch_bounds__(128) gl_gemv_stream_kernel(const GemvParams p) {
+  constexpr int E = 32 / NB;        // k-values per packed word
+  constexpr int H = E / 8;          // 16-byte pieces of x per packed row
+  constexpr int HALF = E / 2;       // field i is paired with field i + HALF
+  constexpr int MB = 8 * MT;        // batch rows held in shared memory
+  constexpr uint32_t FMASK = ((1u << NB) - 1u) * 0x00010001u;
+  using XTr = XTraits<XT>;
+
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int r = lane >> 2, t = lane & 3;
+
+  // K slice of this CTA, in iterations
+  const int split = blockIdx.y;
+  const int it0 = (int)(((long long)p.T * split) / p.splitK);
+  const int it1 = (int)(((long long)p.T * (split + 1)) / p.splitK);
+  const int nit = it1 - it0;
+  const int g0 = it0 / p.gi;                          // first group touched
+  const int nseg = (it1 + p.gi - 1) / p.gi - g0;      // group segments in this slice
+
+  // shared: xs [nit*4*H][MB] 16-byte units | csum [nit*4*H][MB] fp32 | xsum [nseg][MB] fp32
+  uint4* xs = reinterpret_cast<uint4*>(smem_raw);
+  const int nunits = nit * 4 * H;
+  float* csum = reinterpret_cast<float*>(xs + (size_t)p.max_slice_iters * 4 * H * MB);
+  float* xsum = csum + (size_t)p.max_slice_iters * 4 * H * MB;
+
+  // ---- stage x: permute k inside each packed row to the fragment order, sum per 8 values ----
+  {
+    const uint16_t* xg = reinterpret_cast<const uint16_t*>(p.x);
+    const int kbase = it0 * 4 * E;
+    for (int idx = threadIdx.x; idx < nunits * MB; idx += blockDim.x) {
+      const int m = idx % MB, u = idx / MB;            // u = packed_row_local*H + piece
+      uint4 o = make_uint4(0u, 0u, 0u, 0u);
+      float s = 0.f;
+      if (m < p.M) {
+        const int row = u / H, hh = u % H;
+        // piece hh holds, for pp = 2*hh, 2*hh+1: x[2pp], x[2pp+HALF], x[2pp+1], x[2pp+1+HALF]
+        const uint16_t* xr = xg + (size_t)m * p.K + kbase + row * E;
+        uint16_t v[8];
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const int pp = 2 * hh + q;
+          const uint32_t lo = *reinterpret_cast<const uint32_t*>(xr + 2 * pp);          // x[2pp], x[2pp+1]
+          const uint32_t hi = *reinterpret_cast<const uint32_t*>(xr + 2 * pp + HALF);   // x[2pp+HALF], x[2pp+1+HALF]
+          v[4 * q + 0] = (uint16_t)(lo & 0xffffu); v[4 * q + 1] = (uint16_t)(hi & 0xffffu);
+          v[4 * q + 2] = (uint16_t)(lo >> 16);     v[4 * q + 3] = (uint16_t)(hi >> 16);
+        }
+#pragma unroll
+        for (int q = 0; q < 8; ++q) s += XTr::to_float(v[q]);
+        o.x = v[0] | ((uint32_t)v[1] << 16); o.y = v[2] | ((uint32_t)v[3] << 16);
+        o.z = v[4] | ((uint32_t)v[5] << 16); o.w = v[6] | ((uint32_t)v[7] << 16);
+      }
+      xs[idx] = o;
+      csum[idx] = s;
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < nseg * MB; idx += blockDim.x) {
+    const int m = idx % MB, sg = idx / MB;
+    int a = (g0 + sg) * p.gi, b = a + p.gi;
+    a = max(a, it0) - it0; b = min(b, it1) - it0;
+    float s = 0.f;
+    for (int u = a * 4 * H; u < b * 4 * H; ++u) s += csum[u * MB + m];
+    xsum[idx] = s;
+  }
+  __syncthreads();
+
+  // ---- main loop ----------------------------------------------------------------------------
+  const int n0 = (blockIdx.x * nwarps + warp) * 32 + 4 * r;   // this lane's first column
+  const bool ncol_ok = n0 < p.N;
+  const int32_t* wp = p.w + (size_t)(it0 * 4 + t) * p.N + n0;
+  const size_t wstep = (size_t)4 * p.N;
+
+  float acc[2][MT][4], outv[2][MT][4];
+#pragma unroll
+  for (int a = 0; a < 2; ++a)
+#pragma unroll
+    for (int b = 0; b < MT; ++b)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) { acc[a][b][c] = 0.f; outv[a][b][c] = 0.f; }
+
+  int4 cur[U], nxt[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    cur[u] = make_int4(0, 0, 0, 0);
+    if (ncol_ok && u < nit) cur[u] = ldg_stream(wp + (size_t)u * wstep);
+  }
+
+  int seg = 0;
+  int seg_end = min((g0 + 1) * p.gi, it1) - it0;     // local iteration where the segment ends
+
+  auto flush = [&](int sgi) {
+    // out += alpha[col] * acc + beta[col] * xsum[m]
+    float al[4], be[4];
+    const int g = g0 + sgi;
+    if (p.W_group_mode >= 2) {
+      if (ncol_ok) load_meta4<XT>(p.scales, (int64_t)g * p.N + n0, al);
+      else { al[0] = al[1] = al[2] = al[3] = 0.f; }
+    } else { al[0] = al[1] = al[2] = al[3] = 1.f; }
+    float z[4] = {0.f, 0.f, 0.f, 0.f};
+    if (p.W_group_mode == 1 || p.W_group_mode >= 3) {
+      if (p.zero_is_scalar) { const float zz = (float)(*reinterpret_cast<const int32_t*>(p.zeros)); z[0] = z[1] = z[2] = z[3] = zz; }
+      else if (ncol_ok) load_meta4<XT>(p.zeros, (int64_t)g * p.N + n0, z);
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      if (p.W_group_mode == 4)      be[c] = z[c] - XTr::BIAS * al[c];          // fma(b, s, z')
+      else if (p.W_group_mode == 3) be[c] = -(XTr::BIAS + z[c]) * al[c];       // (b - z) * s
+      else if (p.W_group_mode == 1) be[c] = -(XTr::BIAS + z[c]);               // b - z
+      else                          be[c] = -XTr::BIAS * al[c];                // b * s | b
+    }
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      const float xs0 = xsum[sgi * MB + mt * 8 + 2 * t], xs1 = xsum[sgi * MB + mt * 8 + 2 * t + 1];
+#pragma unroll
+      for (int a = 0; a < 2; ++a) {
+        outv[a][mt][0] += al[2 * a] * acc[a][mt][0] + be[2 * a] * xs0;
+        outv[a][mt][1] += al[2 * a] * acc[a][mt][1] + be[2 * a] * xs1;
+        outv[a][mt][2] += al[2 * a + 1] * acc[a][mt][2] + be[2 * a + 1] * xs0;
+        outv[a][mt][3] += al[2 * a + 1] * acc[a][mt][3] + be[2 * a + 1] * xs1;
+        acc[a][mt][0] = acc[a][mt][1] = acc[a][mt][2] = acc[a][mt][3] = 0.f;
+      }
+    }
+  };
+
+  for (int itb = 0; itb < nit; itb += U) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      nxt[u] = make_int4(0, 0, 0, 0);
+      if (ncol_ok && itb + U + u < nit) nxt[u] = ldg_stream(wp + (size_t)(itb + U + u) * wstep);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int it = itb + u;
+      if (it < nit) {
+        const uint32_t w[4] = {(uint32_t)cur[u].x, (uint32_t)cur[u].y, (uint32_t)cur[u].z, (uint32_t)cur[u].w};
+        const int xrow = (it * 4 + t) * H;
+#pragma unroll
+        for (int hh = 0; hh < H; ++hh) {
+          uint4 xb[MT];
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) xb[mt] = xs[(size_t)(xrow + hh) * MB + mt * 8 + r];
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            const int pp = 2 * hh + q;               // MMA index inside the packed row
+            uint32_t f0[4], f1[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              f0[c] = ((w[c] >> (NB * (2 * pp))) & FMASK) | XTr::MAGIC;       // fields 2pp, 2pp+HALF
+              f1[c] = ((w[c] >> (NB * (2 * pp + 1))) & FMASK) | XTr::MAGIC;   // fields 2pp+1, 2pp+1+HALF
+            }
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+              const uint32_t b0 = q ? xb[mt].z : xb[mt].x, b1 = q ? xb[mt].w : xb[mt].y;
+              mma16816<XT>(acc[0][mt], f0[0], f0[1], f1[0], f1[1], b0, b1);
+              mma16816<XT>(acc[1][mt], f0[2], f0[3], f1[2], f1[3], b0, b1);
+            }
+          }
+        }
+        if (it + 1 == seg_end) {
+          flush(seg);
+          ++seg;
+          seg_end = min((g0 + seg + 1) * p.gi, it1) - it0;
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) cur[u] = nxt[u];
+  }
+
+  // ---- epilogue -------------------------------------------------------------------------------
+  // lane owns columns n0..n0+3 and batch rows m = mt*8 + 2t, 2t+1:
+  //   outv[a][mt][0] = (col 2a, m=2t)  [1] = (col 2a, 2t+1)  [2] = (col 2a+1, 2t)  [3] = (col 2a+1, 2t+1)
+  const bool multi = p.splitK > 1;
+  __shared__ int s_last;
+  if (multi) {
+    if (ncol_ok) {
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int m = mt * 8 + 2 * t + j;
+          if (m < p.M) {
+            float4 v = make_float4(outv[0][mt][j], outv[0][mt][2 + j], outv[1][mt][j], outv[1][mt][2 + j]);
+            *reinterpret_cast<float4*>(p.partials + ((size_t)split * p.M + m) * p.N + n0) = v;
+          }
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const unsigned int prev = atomicAdd(p.counters + blockIdx.x, 1u);
+      s_last = (prev == (unsigned int)(p.splitK - 1));
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (threadIdx.x == 0) p.counters[blockIdx.x] = 0u;   // leave the counter clean for the next call
+  }
+  if (!ncol_ok) return;
+
+  float chs[4] = {1.f, 1.f, 1.f, 1.f};
+  if (p.channel_scale_mode == 1) load_meta4<XT>(p.scales, n0, chs);
+  float bs[4] = {0.f, 0.f, 0.f, 0.f};
+  if (p.bias != nullptr) {
+    if (p.out_dtype == GL_FP32) { const float4 b = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.bias) + n0); bs[0] = b.x; bs[1] = b.y; bs[2] = b.z; bs[3] = b.w; }
+    else if (p.out_dtype == GL_BF16) load_meta4<__nv_bfloat16>(p.bias, n0, bs);
+    else load_meta4<__half>(p.bias, n0, bs);
+  }
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int m = mt * 8 + 2 * t + j;
+      if (m >= p.M) continue;
+      float v[4];
+      if (multi) {
+        v[0] = v[1] = v[2] = v[3] = 0.f;
+        for (int s = 0; s < p.splitK; ++s) {
+          const float4 q = __ldcg(reinterpret_cast<const float4*>(p.partials + ((size_t)s * p.M + m) * p.N + n0));
+          v[0] += q.x; v[1] += q.y; v[2] += q.z; v[3] += q.w;
+        }
+      } else {
+        v[0] = outv[0][mt][j]; v[1] = outv[0][mt][2 + j]; v[2] = outv[1][mt][j]; v[3] = outv[1][mt][2 + j];
+      }
+#pragma unroll
+      for (int c = 0; c < 4; ++c) v[c] = v[c] * chs[c] + bs[c];
+      const size_t o = (size_t)m * p.N + n0;
+      if (p.out_dtype == GL_BF16) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 pk; pk.x = *reinterpret_cast<uint32_t*>(&lo); pk.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + o) = pk;
+      } else if (p.out_dtype == GL_FP16) {
+        __half2 lo = __floats2half2_rn(v[0], v[1]), hi = __floats2half2_rn(v[2], v[3]);
+        uint2 pk; pk.x = *reinterpret_cast<uint32_t*>(&lo); pk.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(p.out) + o) = pk;
+      } else {
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + o) = make_float4(v[0], v[1], v[2], v[3]);
+      }
+    }
+}
+
+struct GemvPlan { int warps_n, splitK, MT, U, slice_iters; size_t smem; };
+
+constexpr int kMaxTiles = 16384;   // arrival counters reserved at the head of the workspace
+
+static int plan_for(const gl_matmul_args* a, GemvPlan* pl) {
+  const int e = a->elements_per_sample;
+  const int T = a->K / (4 * e);
+  pl->MT = a->M <= 8 ? 1 : (a->M <= 16 ? 2 : 4);
+  pl->U = 4;
+  pl->warps_n = 2;
+  if (a->N <= 32) pl->warps_n = 1;
+  const int H = e / 8, MB = 8 * pl->MT;
+  const int tiles = (int)gl_cdiv(a->N, 32 * pl->warps_n);
+  // slices: enough CTAs to fill the machine several times over, bounded by shared memory
+  const int sms = gl_num_sms();
+  const int per_iter_bytes = 4 * H * MB * (16 + 4);
+  const int max_iters_smem = (48 * 1024) / per_iter_bytes;
+  int want = (int)gl_cdiv((int64_t)sms * 7, tiles);
+  int min_split = (int)gl_cdiv(T, max_iters_smem);
+  int splitK = want > min_split ? want : min_split;
+  if (splitK > T / 2) splitK = T / 2 > 0 ? T / 2 : 1;
+  if (splitK < min_split) splitK = min_split;
+  if (splitK < 1) splitK = 1;
+  if (splitK > 64) splitK = 64 > min_split ? 64 : min_split;
+  pl->splitK = splitK;
+  pl->slice_iters = (int)gl_cdiv(T, splitK) + 1;
+  const int gi = a->group_size / (4 * e);
+  const int max_seg = pl->slice_iters / (gi > 0 ? gi : 1) + 2;
+  pl->smem = (size_t)pl->slice_iters * per_iter_bytes + (size_t)max_seg * MB * 4;
+  return tiles;
+}
+
+template <int NB, typename XT, int MT>
+static int launch_t(const GemvParams& p, dim3 grid, dim3 block, size_t smem, cudaStream_t st) {
+  auto kern = gl_gemv_stream_kernel<NB, XT, MT, 4>;
+  if (smem > 48 * 1024) GL_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<grid, block, smem, st>>>(p);
+  GL_LAUNCH_CHECK("gl_gemv_stream_kernel");
+  return GL_OK;
+}
+template <int NB, typename XT>
+static int launch_mt(int MT, const GemvParams& p, dim3 grid, dim3 block, size_t smem, cudaStream_t st) {
+  if (MT == 1) return launch_t<NB, XT, 1>(p, grid, block, smem, st);
+  if (MT == 2) return launch_t<NB, XT, 2>(p, grid, block, smem, st);
+  return launch_t<NB, XT, 4>(p, grid, block, smem, st);
+}
+template <typename XT>
+static int launch_nb(int NB, int MT, const GemvParams& p, dim3 grid, dim3 block, size_t smem, cudaStream_t st) {
+  if (NB == 4) return launch_mt<4, XT>(MT, p, grid, block, smem, st);
+  if (NB == 2) return launch_mt<2, XT>(MT, p, grid, block, smem, st);
+  return launch_mt<1, XT>(MT, p, grid, block, smem, st);
+}
+
+}  // namespace
+
+int gl_gemv_stream_supported(const gl_matmul_args* a) {
+  const int e = a->elements_per_sample;
+  if (a->M < 1 || a->M > 32) return 0;
+  if (!(a->W_nbits == 4 || a->W_nbits == 2 || a->W_nbits == 1)) return 0;
+  if (a->w_dtype != GL_INT32 || e != 32 / a->W_nbits) return 0;
+  if (!(a->x_dtype == GL_BF16 || a->x_dtype == GL_FP16) || a->input_dtype != a->x_dtype) return 0;
+  if (a->w_stride_n != 1 || a->w_stride_k != a->N) return 0;
+  if (a->N % 4 != 0 || a->K % (4 * e) != 0) return 0;
+  if (a->W_group_mode < 0 || a->W_group_mode > 4) return 0;
+  if (!(a->channel_scale_mode == 0 || a->channel_scale_mode == 1)) return 0;
+  if (a->group_size % (4 * e) != 0 || a->K % a->group_size != 0) return 0;
+  const bool need_s = a->W_group_mode >= 2 || a->channel_scale_mode == 1;
+  const bool need_z = a->W_group_mode == 1 || a->W_group_mode >= 3;
+  if (need_s && (a->scales == nullptr || a->meta_dtype != a->x_dtype)) return 0;
+  if (a->W_group_mode >= 2 && (a->s_stride_n != 1 || a->s_stride_g != a->N)) return 0;
+  if (need_z) {
+    if (a->zeros == nullptr) return 0;
+    if (a->zero_is_scalar) { if (a->zeros_dtype != GL_INT32) return 0; }
+    else if (a->zeros_dtype != a->x_dtype) return 0;
+  }
+  if (a->channel_scale_mode == 1 && a->W_group_mode >= 2) return 0;
+  if (!(a->out_dtype == GL_BF16 || a->out_dtype == GL_FP16 || a->out_dtype == GL_FP32)) return 0;
+  if (((uintptr_t)a->w & 15) || ((uintptr_t)a->x & 15) || ((uintptr_t)a->out & 15)) return 0;
+  if (need_s && ((uintptr_t)a->scales & 7)) return 0;
+  if (need_z && !a->zero_is_scalar && ((uintptr_t)a->zeros & 7)) return 0;
+  if (a->bias && ((uintptr_t)a->bias & 15)) return 0;
+  GemvPlan pl;
+  const int tiles = plan_for(a, &pl);
+  if (tiles > kMaxTiles) return 0;
+  if (pl.smem > 200 * 1024) return 0;
+  return 1;
+}
+
+uint64_t gl_matmul_counter_bytes(void) { return (uint64_t)kMaxTiles * sizeof(unsigned int); }
+
+uint64_t gl_gemv_stream_workspace(const gl_matmul_args* a) {
+  GemvPlan pl;
+  plan_for(a, &pl);
+  if (pl.splitK <= 1) return 0;
+  return gl_matmul_counter_bytes() + (uint64_t)pl.splitK * a->M * a->N * sizeof(float);
+}
+
+int gl_gemv_stream_launch(const gl_matmul_args* a, cudaStream_t st) {
+  GemvPlan pl;
+  const int tiles = plan_for(a, &pl);
+  const uint64_t need = gl_gemv_stream_workspace(a);
+  if (need > 0 && (a->workspace == nullptr || a->workspace_bytes < need))
+    GL_FAIL(GL_E_WORKSPACE, "gl_matmul: workspace of %llu bytes needed, %llu given",
+            (unsigned long long)need, (unsigned long long)a->workspace_bytes);
+  if (need > 0 && ((uintptr_t)a->workspace & 15)) GL_FAIL(GL_E_INVALID, "gl_matmul: workspace must be 16-byte aligned");
+  GemvParams p;
+  p.x = a->x; p.w = reinterpret_cast<const int32_t*>(a->w); p.scales = a->scales; p.zeros = a->zeros; p.bias = a->bias;
+  p.out = a->out;
+  p.counters = reinterpret_cast<unsigned int*>(a->workspace);
+  p.partials = need ? reinterpret_cast<float*>(reinterpret_cast<char*>(a->workspace) + gl_matmul_counter_bytes()) : nullptr;
+  p.M = a->M; p.N = a->N; p.K = a->K;
+  const int e = a->elements_per_sample;
+  p.T = a->K / (4 * e);
+  p.gi = a->group_size / (4 * e);
+  p.splitK = pl.splitK;
+  p.W_group_mode = a->W_group_mode; p.channel_scale_mode = a->channel_scale_mode; p.zero_is_scalar = a->zero_is_scalar;
+  p.out_dtype = a->out_dtype;
+  p.max_slice_iters = pl.slice_iters;
+  dim3 grid(tiles, pl.splitK), block(32 * pl.warps_n);
+  if (a->x_dtype == GL_BF16) return launch_nb<__nv_bfloat16>(a->W_nbits, pl.MT, p, grid, block, pl.smem, st);
+  return launch_nb<__half>(a->W_nbits, pl.MT, p, grid, block, pl.smem, st);
+}

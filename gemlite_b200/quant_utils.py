@@ -1,0 +1,212 @@
+"""Activation quantisation front ends and the offline MX / NV weight quantiser.
+
+``scale_activations_*`` keep the reference's names and return values
+(gemlite/quant_utils.py:2680-2684) and run as CUDA kernels through the C ABI.
+``WeightQuantizerMXFP`` is offline torch code (it prepares weights once, it is not on the
+matmul path) with the arithmetic of gemlite/quant_utils.py:75-232; it works on any device.
+"""
+from typing import Tuple
+
+import torch
+from torch import Tensor
+
+from . import _lib
+from .dtypes import TORCH_TO_DTYPE, DType
+
+_FP4_POS = [0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0]
+_FP4_THRESHOLDS = [0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0]  # midpoints between representable magnitudes
+_FP4_VALUES = _FP4_POS + [-v for v in _FP4_POS]             # code -> value, sign in bit 3
+
+
+def get_dtype_range(compute_dtype: torch.dtype):
+    info = torch.finfo(compute_dtype) if compute_dtype.is_floating_point else torch.iinfo(compute_dtype)
+    return info.min, info.max
+
+
+# ------------------------------------------------------------------------------------------
+# Offline weight quantiser (gemlite/quant_utils.py:75-232)
+# ------------------------------------------------------------------------------------------
+class WeightQuantizerMXFP:
+    def __init__(self, compute_dtype=torch.bfloat16, device="cuda:0"):
+        self.compute_dtype = compute_dtype
+        self.device = device
+
+    @staticmethod
+    def round_to_closest_fp4(tensor):
+        """Nearest E2M1 magnitude, ties to the smaller one (left bisect on the midpoints)."""
+        thr = torch.tensor(_FP4_THRESHOLDS, dtype=tensor.dtype, device=tensor.device)
+        pos = torch.tensor(_FP4_POS, dtype=tensor.dtype, device=tensor.device)
+        out = pos[torch.searchsorted(thr, tensor.abs().contiguous())]
+        return out * tensor.sign()
+
+    @staticmethod
+    def to_index(W_q):
+        """E2M1 codes of fp4-valued floats; -0.0 maps to code 0 like +0.0 (first match)."""
+        assert W_q.is_floating_point(), "Input should be floating point fp4 values."
+        vals = torch.tensor(_FP4_VALUES, dtype=W_q.dtype, device=W_q.device)
+        return (W_q.reshape(-1, 1) == vals.view(1, -1)).to(torch.uint8).argmax(dim=1).to(torch.uint8).view(W_q.shape)
+
+    def quantize_mxfp8(self, W, index=False, mx_fp8_dtype=torch.float8_e4m3fn):
+        group_size, eps = 32, 2.0 ** -30
+        min_val, max_val = get_dtype_range(mx_fp8_dtype)
+        W_flat = W.reshape(-1, group_size).float()
+        ideal = W_flat.abs().amax(dim=1, keepdim=True) / max_val
+        scales = (2 ** torch.ceil(torch.log2(ideal))).clamp_(min=eps)
+        W_q = (W_flat / scales).clamp_(min=min_val, max=max_val).to(mx_fp8_dtype)
+        if not index:
+            W_q = W_q.to(W_flat.dtype)
+        return W_q, scales.to(torch.float8_e8m0fnu)
+
+    def quantize_mxfp4(self, W, window_size: int = 0, index=False):
+        group_size, eps, max_val = 32, 2.0 ** -30, 6
+        W_flat = W.reshape(-1, group_size).float()
+        ideal = W_flat.abs().amax(dim=1, keepdim=True) / max_val
+        log2s = torch.ceil(torch.log2(ideal))
+        if window_size == 0:
+            scales = 2 ** log2s
+        else:
+            offs = torch.arange(-window_size, window_size + 1, device=W.device, dtype=log2s.dtype).view(1, -1)
+            cand = torch.pow(2, log2s + offs)
+            cand[cand < eps] = eps
+            W_r = self.round_to_closest_fp4(W_flat.unsqueeze(1) / cand.unsqueeze(-1)) * cand.unsqueeze(-1)
+            err = (W_flat.unsqueeze(1) - W_r).abs().mean(dim=-1)
+            scales = torch.gather(cand, 1, torch.argmin(err, dim=1, keepdim=True))
+        scales = scales.clamp_(eps)
+        W_q = self.round_to_closest_fp4(W_flat / scales)
+        if index:
+            W_q = self.to_index(W_q)
+        return W_q, scales.to(torch.float8_e8m0fnu)
+
+    def quantize_nvfp4(self, W, window_size: int = 0, index=False):
+        group_size, eps, max_val = 16, 1e-6, 6
+        fp8_dtype = torch.float8_e4m3fn
+        max_fp8 = torch.finfo(fp8_dtype).max  # 448
+        W_flat = W.reshape(-1, group_size).float()
+        ideal = W_flat.abs().amax(dim=1, keepdim=True) / max_val
+        meta_scales = (max_fp8 / ideal.max().clamp_(min=eps)).float()
+        ideal = (ideal * meta_scales).clamp_(max=max_fp8).to(fp8_dtype)
+        if window_size == 0:
+            scales = ideal
+        else:
+            offs = torch.arange(-window_size, window_size + 1, device=W.device, dtype=torch.int).view(1, -1)
+            cand = (ideal.view(torch.int8) + offs).clamp_(-128, 127).to(torch.int8)
+            cand[cand == -1] = 1   # 0xFF and 0x7F are the e4m3 NaN patterns
+            cand[cand == 127] = 1
+            cand = cand.view(fp8_dtype).float()
+            cand[cand < eps] = eps
+            W_r = self.round_to_closest_fp4(W_flat.unsqueeze(1) * (meta_scales / cand).unsqueeze(-1)) * (cand / meta_scales).unsqueeze(-1)
+            err = (W_flat.unsqueeze(1) - W_r).abs().mean(dim=-1)
+            scales = torch.gather(cand, 1, torch.argmin(err, dim=1, keepdim=True)).to(fp8_dtype)
+        scales_full = (scales.to(W_flat.dtype) / meta_scales).clamp_(min=eps)
+        W_q = self.round_to_closest_fp4(W_flat / scales_full)
+        if index:
+            W_q = self.to_index(W_q)
+        return W_q, scales, meta_scales
+
+    def dequantize(self, W_q, scales, shape=None, dtype=None, meta_scales=None):
+        if W_q.dtype == torch.uint8:
+            W_q = torch.tensor(_FP4_VALUES, dtype=torch.float32, device=W_q.device)[W_q.int()]
+        group_size = W_q.numel() // scales.numel()
+        out = W_q.reshape(-1, group_size).float() * scales.float().reshape(-1, 1)
+        if meta_scales is not None:
+            out = out * meta_scales
+        if shape is not None:
+            out = out.view(shape)
+        return out.to(self.compute_dtype if dtype is None else dtype)
+
+
+# ------------------------------------------------------------------------------------------
+# Dynamic activation quantisation (CUDA, via the C ABI)
+# ------------------------------------------------------------------------------------------
+def _as_2d(tensor):
+    _lib.require_cuda(tensor, "activations")
+    shape = tensor.shape
+    t = tensor.contiguous().view(-1, shape[-1])
+    if t.dtype not in (torch.float16, torch.bfloat16, torch.float32):
+        raise NotImplementedError("activation dtype %s is not supported" % t.dtype)
+    return t, shape
+
+
+def scale_activations_per_token(tensor: Tensor, w_dtype: torch.dtype, fp32_scale: bool = True) -> Tuple[Tensor, Tensor]:
+    """Per-row symmetric quantisation to fp8 e4m3 / int8: returns (q like tensor, scales fp32 [M, 1]).
+
+    Replaces scale_activations_per_token_triton_v3 (gemlite/quant_utils.py:510-539)."""
+    if w_dtype not in (torch.float8_e4m3fn, torch.int8):
+        raise NotImplementedError("per-token activation quantisation supports float8_e4m3fn and int8, got %s" % w_dtype)
+    x, shape = _as_2d(tensor)
+    M, K = x.shape
+    q = torch.empty((M, K), dtype=w_dtype, device=x.device)
+    scales = torch.empty((M, 1), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().gl_scale_activations_per_token(
+            x.data_ptr(), q.data_ptr(), scales.data_ptr(), M, K, TORCH_TO_DTYPE[x.dtype].value,
+            DType.INT8.value if w_dtype == torch.int8 else DType.FP8.value, _lib.current_stream_ptr(x.device)))
+    if not fp32_scale:
+        scales = scales.to(tensor.dtype)
+    return q.view(shape), scales
+
+
+def scale_activations_mxfp8(tensor: Tensor, w_dtype: torch.dtype = torch.float8_e4m3fn) -> Tuple[Tensor, Tensor]:
+    """MXFP8: (q e4m3 like tensor, e8m0 scale bytes uint8 [ceil32(M), K/32]).  quant_utils.py:1095-1124."""
+    if w_dtype != torch.float8_e4m3fn:
+        raise NotImplementedError("MXFP8 activations are e4m3 only")
+    x, shape = _as_2d(tensor)
+    M, K = x.shape
+    Mpad = (M + 31) // 32 * 32
+    q = torch.empty((M, K), dtype=w_dtype, device=x.device)
+    scales = torch.empty((Mpad, K // 32), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().gl_scale_activations_mxfp8(x.data_ptr(), q.data_ptr(), scales.data_ptr(), M, K,
+                                                        TORCH_TO_DTYPE[x.dtype].value, _lib.current_stream_ptr(x.device)))
+    return q.view(shape), scales
+
+
+def scale_activations_mxfp4(tensor: Tensor) -> Tuple[Tensor, Tensor]:
+    """MXFP4: (q uint8 [M, K/2] e2m1 pairs, e8m0 scale bytes uint8 [ceil32(M), K/32]).  quant_utils.py:2107-2135."""
+    x, _ = _as_2d(tensor)
+    M, K = x.shape
+    Mpad = (M + 31) // 32 * 32
+    q = torch.empty((M, K // 2), dtype=torch.uint8, device=x.device)
+    scales = torch.empty((Mpad, K // 32), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().gl_scale_activations_mxfp4(x.data_ptr(), q.data_ptr(), scales.data_ptr(), M, K,
+                                                        TORCH_TO_DTYPE[x.dtype].value, _lib.current_stream_ptr(x.device)))
+    return q, scales
+
+
+_NVFP4_SCRATCH = {}
+
+
+def _nvfp4_scratch(device):
+    """4 bytes per device for the tensor-wide amax (allocated once, outside any graph capture)."""
+    key = (device.type, device.index)
+    buf = _NVFP4_SCRATCH.get(key)
+    if buf is None:
+        buf = torch.zeros(1, dtype=torch.int32, device=device)
+        _NVFP4_SCRATCH[key] = buf
+    return buf
+
+
+def scale_activations_nvfp4(tensor: Tensor, meta_scale=None) -> Tuple[Tensor, Tensor, Tensor]:
+    """NVFP4: (q uint8 [M, K/2], e4m3 scales [ceil16(M), K/16], fp32 tensor scale [1]).
+
+    ``meta_scale`` (device fp32 tensor) switches to the static-scale path.  quant_utils.py:2434-2493."""
+    x, _ = _as_2d(tensor)
+    M, K = x.shape
+    Mpad = (M + 15) // 16 * 16
+    q = torch.empty((M, K // 2), dtype=torch.uint8, device=x.device)
+    scales = torch.empty((Mpad, K // 16), dtype=torch.float8_e4m3fn, device=x.device)
+    meta_out = torch.empty(1, dtype=torch.float32, device=x.device)
+    meta_in = None
+    if meta_scale is not None:
+        meta_in = meta_scale.to(device=x.device, dtype=torch.float32).reshape(-1)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().gl_scale_activations_nvfp4(
+            x.data_ptr(), q.data_ptr(), scales.data_ptr(), meta_out.data_ptr(),
+            None if meta_in is None else meta_in.data_ptr(), _nvfp4_scratch(x.device).data_ptr(),
+            M, K, TORCH_TO_DTYPE[x.dtype].value, _lib.current_stream_ptr(x.device)))
+    return q, scales, meta_out
+
+
+def scale_activations_per_block(tensor: Tensor, w_dtype: torch.dtype, block_size: int = 128):
+    raise NotImplementedError("128-wide block activation quantisation (channel_scale_mode 5) is not implemented")

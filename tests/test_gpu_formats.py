@@ -1,0 +1,123 @@
+"""GPU: the other weight formats through GemLiteLinear / the helper processors and the C ABI,
+against the oracle: A8W8 FP8 / INT8 dynamic (channel-wise scales), A16W8, MXFP4 / NVFP4 block-scaled
+with fused-in-forward activation quantisation, and weight-only MX / NV.  Tolerances: 1e-2 relative
+Frobenius for 16-bit paths, 3e-2 for FP8 / FP4 paths (quantisation of the activations is part of the
+operator, so the reference point is the oracle fed with the same quantised activations, at 1e-3,
+and the unquantised layer at the looser bound)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle
+from tests.util import rel_fro
+
+pytestmark = pytest.mark.gpu
+
+
+def _lin(seed, N, K, dtype=torch.bfloat16, M=4, wstd=0.02):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(M, K, generator=g).to(dtype)
+    W = (torch.randn(N, K, generator=g) * wstd).to(dtype)
+    return x, W
+
+
+@pytest.mark.parametrize("M", [1, 2, 16, 65, 130])
+@pytest.mark.parametrize("fp8", [True, False])
+def test_a8w8_dynamic(lib, M, fp8):
+    from gemlite_b200 import helper
+    N, K = 1024, 2048
+    x, W = _lin(50 + M, N, K, M=M)
+    proc = helper.A8W8_FP8_dynamic(device="cuda:0", dtype=torch.bfloat16) if fp8 else helper.A8W8_INT8_dynamic(device="cuda:0", dtype=torch.bfloat16)
+    lin = torch.nn.Linear(K, N, bias=False, dtype=torch.bfloat16)
+    lin.weight.data = W.clone()
+    layer = proc.from_linear(lin.cuda())
+    assert (layer.W_group_mode, layer.channel_scale_mode) == (0, 3)
+    assert layer.scales.dtype == torch.float32 and layer.W_q.shape == (K, N) and layer.W_q.stride() == (1, K)
+    y = layer(x.cuda()).float().cpu().numpy()
+    # oracle on the same quantised operands
+    xq, sx = oracle.scale_activations_per_token(x.float().numpy(), "fp8" if fp8 else "int8")
+    Wq = layer.W_q.t().contiguous().cpu()
+    if fp8:
+        Xd, Wd = oracle.e4m3_decode(xq).astype(np.float64), Wq.float().double().numpy()
+    else:
+        Xd, Wd = xq.astype(np.float64), Wq.double().numpy()
+    want_q = (Xd @ Wd.T) * sx.astype(np.float64) * layer.scales.cpu().double().numpy().reshape(1, -1)
+    assert rel_fro(y, want_q) < 5e-3, rel_fro(y, want_q)
+    want = (x.double() @ W.double().T).numpy()
+    assert rel_fro(y, want) < 5e-2
+
+
+@pytest.mark.parametrize("fp8", [True, False])
+def test_a16w8(lib, fp8):
+    from gemlite_b200 import helper
+    N, K = 512, 1024
+    x, W = _lin(60, N, K, torch.float16, M=3)
+    for post_scale in (False, True):
+        proc = (helper.A16W8_FP8 if fp8 else helper.A16W8_INT8)(device="cuda:0", dtype=torch.float16, post_scale=post_scale)
+        layer = proc.from_weights(W.cuda())
+        assert (layer.W_group_mode, layer.channel_scale_mode) == ((0, 1) if post_scale else (2, 0))
+        y = layer(x.cuda()).float().cpu().numpy()
+        Wd = layer.W_q.t().float().cpu().double() * layer.scales.cpu().double().view(-1, 1)
+        assert rel_fro(y, (x.double() @ Wd.T).numpy()) < 1e-2
+
+
+@pytest.mark.parametrize("fmt", ["mxfp4", "nvfp4"])
+@pytest.mark.parametrize("M", [1, 3, 16, 64, 100])
+def test_a4w4_block_scaled(lib, fmt, M):
+    # tests/test_mxfp.py shape: 4224 -> 2048, weights / 10
+    from gemlite_b200 import helper
+    N, K = 2048, 4224
+    g = torch.Generator().manual_seed(70 + M)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    lin = torch.nn.Linear(K, N, bias=False, dtype=torch.bfloat16)
+    lin.weight.data = (torch.randn(N, K, generator=g) / 10.0 / (K ** 0.5) * 8).to(torch.bfloat16)
+    W = lin.weight.data.clone()
+    proc = (helper.A4W4_MXFP_dynamic if fmt == "mxfp4" else helper.A4W4_NVFP_dynamic)(device="cuda:0", dtype=torch.bfloat16)
+    layer = proc.from_linear(lin.cuda())
+    gs = 32 if fmt == "mxfp4" else 16
+    assert (layer.W_group_mode, layer.channel_scale_mode) == (0, 4)
+    assert layer.W_q.numel() * layer.W_q.itemsize == N * K // 2            # tests/test_mxfp.py:96,102
+    assert layer.W_q.shape == (K // 2, N) and layer.scales.shape == (N, K // gs) and layer.scales.stride() == (1, N)
+    y = layer(x.cuda()).float().cpu().numpy()
+    # oracle: same quantised weights (checked against the oracle's quantiser) and activations
+    if fmt == "mxfp4":
+        codes, sw = oracle.quantize_mxfp4_weights(W.float().numpy())
+        xq, sx = oracle.scale_activations_mxfp4(x.float().numpy())
+        meta = None
+    else:
+        codes, sw, mw = oracle.quantize_nvfp4_weights(W.float().numpy())
+        xq, sx, mx = oracle.scale_activations_nvfp4(x.float().numpy())
+        meta = 1.0 / (float(mw) * float(mx))
+        assert np.float32(layer.meta_scale.item()) == mw
+    wq = oracle.pack_fp4_codes(codes)
+    assert np.array_equal(layer.W_q.t().contiguous().cpu().numpy(), wq)
+    assert np.array_equal(layer.scales.contiguous().view(torch.uint8).cpu().numpy(), sw)
+    want_q = oracle.matmul_mx(xq, sx, wq, sw, gs, meta_scale=meta)
+    assert rel_fro(y, want_q) < 5e-3, rel_fro(y, want_q)
+    want = (x.double() @ W.double().T).numpy()
+    assert rel_fro(y, want) < 0.25      # fp4 x fp4 quantisation noise itself (reference tolerance is on mean abs error)
+
+
+@pytest.mark.parametrize("which", ["A16W4_MXFP", "A16W8_MXFP", "A16W4_NVFP", "A8W4_MXFP", "A8W8_MXFP_post", "A8W8_MXFP_mx"])
+def test_weight_only_and_mixed_block_scaled(lib, which):
+    from gemlite_b200 import helper
+    N, K, M = 512, 1024, 5
+    x, W = _lin(80, N, K, torch.bfloat16, M=M)
+    lin = torch.nn.Linear(K, N, bias=False, dtype=torch.bfloat16)
+    lin.weight.data = W.clone()
+    if which == "A16W4_MXFP":
+        layer = helper.A16W4_MXFP(device="cuda:0", dtype=torch.bfloat16).from_linear(lin.cuda())
+    elif which == "A16W8_MXFP":
+        layer = helper.A16W8_MXFP(device="cuda:0", dtype=torch.bfloat16).from_linear(lin.cuda())
+    elif which == "A16W4_NVFP":
+        layer = helper.A16W4_NVFP(device="cuda:0", dtype=torch.bfloat16).from_linear(lin.cuda())
+    elif which == "A8W4_MXFP":
+        layer = helper.A8W4_MXFP_dynamic(device="cuda:0", dtype=torch.bfloat16, post_scale=False).from_linear(lin.cuda())
+    elif which == "A8W8_MXFP_post":
+        layer = helper.A8W8_MXFP_dynamic(device="cuda:0", dtype=torch.bfloat16, post_scale=True).from_linear(lin.cuda())
+    else:
+        layer = helper.A8W8_MXFP_dynamic(device="cuda:0", dtype=torch.bfloat16, post_scale=False).from_linear(lin.cuda())
+    y = layer(x.cuda()).float().cpu().numpy()
+    want = (x.double() @ W.double().T).numpy()
+    tol = 0.2 if "W4" in which else 0.06
+    assert rel_fro(y, want) < tol, (which, rel_fro(y, want))
