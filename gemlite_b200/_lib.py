@@ -31,7 +31,8 @@ class GLMatmulArgs(ctypes.Structure):
         ("channel_scale_mode", c_int32), ("W_group_mode", c_int32), ("zero_is_scalar", c_int32),
         ("matmul_type", c_int32),
         ("w_stride_k", c_int64), ("w_stride_n", c_int64), ("s_stride_g", c_int64), ("s_stride_n", c_int64),
-        ("kernel_override", c_int32), ("reserved", c_int32 * 3),
+        ("kernel_override", c_int32), ("sx_layout", c_int32), ("reserved", c_int32 * 2),
+        ("w_scales_atoms", c_void_p),
     ]
 
 
@@ -50,9 +51,9 @@ SIGNATURES = {
     "gl_unpack_over_cols": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_int32, c_int32, c_int32, c_int32, c_void_p]),
     "gl_unpack_over_rows": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_int32, c_int32, c_int32, c_int32, c_void_p]),
     "gl_scale_activations_per_token": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p]),
-    "gl_scale_activations_mxfp4": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p]),
-    "gl_scale_activations_mxfp8": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p]),
-    "gl_scale_activations_nvfp4": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p]),
+    "gl_scale_activations_mxfp4": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p]),
+    "gl_scale_activations_mxfp8": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p]),
+    "gl_scale_activations_nvfp4": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p]),
     "gl_cfg_load": (c_int32, [c_char_p, c_int32]),
     "gl_cfg_save": (c_int32, [c_char_p]),
     "gl_cfg_reset": (None, []),

@@ -167,7 +167,29 @@ def _workspace(device, nbytes):
     return ws
 
 
-def _fill_args(x2d, bias, W_q, scales, zeros, scales_x, meta_scale, out, meta_args, matmul_type):
+_SCALE_ATOMS = {}
+
+
+def _scale_atoms(scales):
+    """Weight scales of an MX / NV layer as 128x4 scale atoms (the reference's 5-D pre-shuffle,
+    gemlite/core.py:748-752), derived once per layer and kept beside the stored 2-D scales.
+    None when the shape does not tile (N % 128 or (K/group) % 4) or the general kernel is forced."""
+    if _KERNEL_OVERRIDE == 1 or scales is None or scales.dim() != 2:
+        return None
+    N, G = scales.shape
+    if N % 128 != 0 or G % 4 != 0:
+        return None
+    key = (scales.data_ptr(), N, G, scales.device.index)
+    hit = _SCALE_ATOMS.get(key)
+    if hit is None or hit[1] != scales._version:
+        s2d = scales.view(torch.uint8) if scales.dtype != torch.uint8 else scales
+        atoms = s2d.contiguous().view(N // 128, 4, 32, G // 4, 4).permute(0, 3, 2, 1, 4).contiguous()
+        hit = (atoms, scales._version)
+        _SCALE_ATOMS[key] = hit
+    return hit[0]
+
+
+def _fill_args(x2d, bias, W_q, scales, zeros, scales_x, meta_scale, out, meta_args, matmul_type, w_atoms=None, sx_layout=0):
     (_, W_nbits, group_size, _, eps, input_dtype, output_dtype, _, meta_dtype, channel_scale_mode,
      W_group_mode, _) = meta_args
     a = _lib.GLMatmulArgs()
@@ -196,6 +218,8 @@ def _fill_args(x2d, bias, W_q, scales, zeros, scales_x, meta_scale, out, meta_ar
     a.zero_is_scalar = int(has_zeros and zeros.numel() == 1)
     a.matmul_type = matmul_type
     a.kernel_override = _KERNEL_OVERRIDE
+    a.sx_layout = sx_layout
+    a.w_scales_atoms = None if w_atoms is None else w_atoms.data_ptr()
     a.w_stride_k, a.w_stride_n = W_q.stride(0), W_q.stride(1)
     if has_scales and scales.dim() == 2:
         if mx:   # logical [N, G]
@@ -230,6 +254,8 @@ def forward_functional(
     channel_scale_mode = meta_args[9]
 
     scales_x, meta_scale = None, None
+    w_atoms = _scale_atoms(scales) if (channel_scale_mode == 4 and input_dtype in (DType.MXFP4, DType.NVFP4)) else None
+    sx_layout = 0 if w_atoms is None else 1
     if bool(meta_args[0]) and enable_activation_scaling(x.numel() // x.shape[-1]):
         if input_dtype in FP8_INT8_DTYPES and channel_scale_mode == 5:
             x, scales_x = scale_activations_per_block(x, w_dtype=DTYPE_TO_TORCH[input_dtype.value])
@@ -240,12 +266,12 @@ def forward_functional(
         elif input_dtype == DType.MXFP8 and channel_scale_mode == 2:
             x, scales_x = scale_activations_per_token(x, w_dtype=torch.float8_e4m3fn)
         elif input_dtype == DType.MXFP4 and channel_scale_mode == 4:
-            x, scales_x = scale_activations_mxfp4(x)
+            x, scales_x = scale_activations_mxfp4(x, scale_layout=sx_layout)
         elif input_dtype == DType.NVFP4 and channel_scale_mode == 4:
             static_meta = GEMLITE_NVFP4_INPUT_SCALES.get(W_q.data_ptr()) if GEMLITE_NVFP4_INPUT_SCALES else None
             if static_meta is None and GEMLITE_FAST_NVFP4:
                 static_meta = GEMLITE_NVFP4_META_SCALES[x.device.index]
-            x, scales_x, meta_a = scale_activations_nvfp4(x, meta_scale=static_meta)
+            x, scales_x, meta_a = scale_activations_nvfp4(x, meta_scale=static_meta, scale_layout=sx_layout)
             meta_scale = (1.0 / (layer_meta_scale * meta_a)).reshape(1)   # stays on the device (graph-safe)
     if meta_scale is None and meta_args[2] == 16 and is_mx_dtype(input_dtype):
         meta_scale = layer_meta_scale.reshape(1)   # weight-only NVFP4: stored tensor scale
@@ -256,7 +282,7 @@ def forward_functional(
         return out.view(out_shape)
     if bias is not None and bias.dtype != out.dtype:
         bias = bias.to(out.dtype)
-    a = _fill_args(x2d, bias, W_q, scales, zeros, scales_x, meta_scale, out, meta_args, matmul_type)
+    a = _fill_args(x2d, bias, W_q, scales, zeros, scales_x, meta_scale, out, meta_args, matmul_type, w_atoms, sx_layout)
     L = _lib.lib()
     with torch.cuda.device(x.device):
         ws = _workspace(x.device, int(L.gl_matmul_workspace_bytes(ctypes.byref(a))))

@@ -45,7 +45,7 @@ extern "C" int gl_get_matmul_type(int32_t M, int32_t W_nbits, int32_t is_mx_dtyp
 
 namespace {
 
-enum KernelId { K_INVALID = 0, K_STREAM, K_GENERIC };
+enum KernelId { K_INVALID = 0, K_STREAM, K_TC, K_GENERIC };
 
 int validate(const gl_matmul_args* a) {
   if (a == nullptr) GL_FAIL(GL_E_INVALID, "gl_matmul: null argument struct");
@@ -66,7 +66,7 @@ int validate(const gl_matmul_args* a) {
   if (a->W_group_mode >= 2 && a->scales == nullptr) GL_FAIL(GL_E_INVALID, "gl_matmul: W_group_mode %d needs scales", a->W_group_mode);
   if ((a->W_group_mode == 1 || a->W_group_mode >= 3) && a->zeros == nullptr) GL_FAIL(GL_E_INVALID, "gl_matmul: W_group_mode %d needs zeros", a->W_group_mode);
   if ((a->channel_scale_mode == 1 || a->channel_scale_mode == 3) && a->scales == nullptr) GL_FAIL(GL_E_INVALID, "gl_matmul: channel_scale_mode %d needs scales", a->channel_scale_mode);
-  for (int i = 0; i < 3; ++i) if (a->reserved[i] != 0) GL_FAIL(GL_E_INVALID, "gl_matmul: reserved fields must be 0");
+  for (int i = 0; i < 2; ++i) if (a->reserved[i] != 0) GL_FAIL(GL_E_INVALID, "gl_matmul: reserved fields must be 0");
   return GL_OK;
 }
 
@@ -79,6 +79,7 @@ KernelId select(const gl_matmul_args* a, int* family_out) {
   if (mx && (fam == GL_MM_GEMV_REVSPLITK || fam == GL_MM_GEMV_SPLITK)) return K_INVALID;  // as the reference: MX only on GEMV / GEMM*
   if (a->kernel_override == 1) return K_GENERIC;
   if (!mx && gl_gemv_stream_supported(a)) return K_STREAM;
+  if (gl_gemm_tc_supported(a)) return K_TC;
   return K_GENERIC;
 }
 
@@ -89,6 +90,7 @@ extern "C" uint64_t gl_matmul_workspace_bytes(const gl_matmul_args* a) {
   int fam;
   const KernelId k = select(a, &fam);
   if (k == K_STREAM) return gl_gemv_stream_workspace(a);
+  if (k == K_TC) return gl_matmul_counter_bytes();
   return 0;
 }
 
@@ -97,6 +99,7 @@ extern "C" const char* gl_matmul_kernel_name(const gl_matmul_args* a) {
   int fam;
   switch (select(a, &fam)) {
     case K_STREAM: return "gl_gemv_stream_kernel";
+    case K_TC: return "gl_gemm_tc_kernel";
     case K_GENERIC: return "gl_generic_kernel";
     default: return "invalid";
   }
@@ -109,6 +112,7 @@ extern "C" int gl_matmul(const gl_matmul_args* a, void* stream) {
   int fam;
   switch (select(a, &fam)) {
     case K_STREAM: return gl_gemv_stream_launch(a, st);
+    case K_TC: return gl_gemm_tc_launch(a, st);
     case K_GENERIC: return gl_generic_launch(a, st);
     default:
       GL_FAIL(GL_E_UNSUPPORTED, "gl_matmul: kernel family %d does not support MX / NV block-scaled dtypes", fam);

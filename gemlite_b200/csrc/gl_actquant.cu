@@ -52,6 +52,12 @@ __device__ __forceinline__ uint32_t pow2_ceil_exp(float v) {
   return e;
 }
 
+// index of the scale of (row m, group kg): plain rows [*, G] or 128-row x 4-group atoms of 512 bytes
+__device__ __forceinline__ int64_t scale_index(int m, int kg, int G, int layout) {
+  if (layout == 0) return (int64_t)m * G + kg;
+  return ((int64_t)(m >> 7) * (G >> 2) + (kg >> 2)) * 512 + (m & 31) * 16 + ((m & 127) >> 5) * 4 + (kg & 3);
+}
+
 // e2m1 code of a scaled value: number of magnitude thresholds exceeded, sign in bit 3
 __device__ __forceinline__ uint32_t e2m1_code(float v) {
   const float a = fabsf(v);
@@ -109,7 +115,7 @@ __global__ void __launch_bounds__(256) per_token_kernel(const void* __restrict__
 // mxfp4 / mxfp8: thread = 8 consecutive k of one row; 4 lanes = one group of 32
 template <bool FP4>
 __global__ void __launch_bounds__(256) mx_quant_kernel(const void* __restrict__ x, uint8_t* __restrict__ q,
-                                                       uint8_t* __restrict__ scales, int M, int Mpad, int K, int x_dtype) {
+                                                       uint8_t* __restrict__ scales, int M, int Mpad, int K, int x_dtype, int layout) {
   const int64_t units_per_row = K / 8;
   const int64_t total = (int64_t)Mpad * units_per_row;
   // the loop bound is warp-uniform so that every lane takes part in the group shuffles
@@ -132,7 +138,7 @@ __global__ void __launch_bounds__(256) mx_quant_kernel(const void* __restrict__ 
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
     const uint32_t e = pow2_ceil_exp(amax / (FP4 ? 6.f : 448.f));
     const float scale = __uint_as_float(e << 23);
-    if (valid && (threadIdx.x & 3) == 0) scales[(int64_t)m * (K / 32) + k / 32] = real ? (uint8_t)e : (uint8_t)127;
+    if (valid && (threadIdx.x & 3) == 0) scales[scale_index(m, k / 32, K / 32, layout)] = real ? (uint8_t)e : (uint8_t)127;
     if (!real) continue;
     if (FP4) {
       uint32_t o = 0u;
@@ -179,7 +185,7 @@ __global__ void __launch_bounds__(256) nvfp4_quant_kernel(const void* __restrict
                                                           uint8_t* __restrict__ scales, float* __restrict__ meta_out,
                                                           const float* __restrict__ meta_in,
                                                           const uint32_t* __restrict__ amax_bits, int M, int Mpad, int K,
-                                                          int x_dtype) {
+                                                          int x_dtype, int layout) {
   float meta;
   if (meta_in != nullptr) meta = *meta_in;
   else meta = (448.f * 6.0f) / fmaxf(__uint_as_float(*amax_bits), 1e-6f);
@@ -205,7 +211,7 @@ __global__ void __launch_bounds__(256) nvfp4_quant_kernel(const void* __restrict
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
     const float sraw = fminf(amax * meta / 6.f, 448.f);
     const uint8_t s8 = (uint8_t)__nv_cvt_float_to_fp8(sraw, __NV_SATFINITE, __NV_E4M3);
-    if (valid && (threadIdx.x & 1) == 0) scales[(int64_t)m * (K / 16) + k / 16] = real ? s8 : (uint8_t)0x38;  // 0x38 = 1.0 e4m3
+    if (valid && (threadIdx.x & 1) == 0) scales[scale_index(m, k / 16, K / 16, layout)] = real ? s8 : (uint8_t)0x38;  // 0x38 = 1.0 e4m3
     if (!real) continue;
     const float sfull = fmaxf(gl_e4m3_to_float(s8) / meta, 1e-6f);
     uint32_t o = 0u;
@@ -247,44 +253,53 @@ extern "C" int gl_scale_activations_per_token(const void* x, void* q, float* sca
   return GL_OK;
 }
 
+static int check_layout(const char* fn, int layout, int G) {
+  if (layout != 0 && layout != 1) { gl_set_error("%s: scale_layout must be 0 or 1", fn); return GL_E_INVALID; }
+  if (layout == 1 && G % 4 != 0) { gl_set_error("%s: scale atoms need K / group_size to be a multiple of 4", fn); return GL_E_INVALID; }
+  return GL_OK;
+}
+
 extern "C" int gl_scale_activations_mxfp4(const void* x, uint8_t* q, uint8_t* scales, int32_t M, int32_t K,
-                                          int32_t x_dtype, void* stream) {
+                                          int32_t x_dtype, int32_t scale_layout, void* stream) {
   if (int rc = check_x("gl_scale_activations_mxfp4", x, M, K, x_dtype, 32)) return rc;
   if (M == 0) return GL_OK;
   if (!q || !scales || ((uintptr_t)q & 3)) GL_FAIL(GL_E_INVALID, "gl_scale_activations_mxfp4: null or misaligned output");
-  const int Mpad = (M + 31) / 32 * 32;
-  mx_quant_kernel<true><<<grid_units((int64_t)Mpad * (K / 8)), 256, 0, (cudaStream_t)stream>>>(x, q, scales, M, Mpad, K, x_dtype);
+  if (int rc = check_layout("gl_scale_activations_mxfp4", scale_layout, K / 32)) return rc;
+  const int Mpad = scale_layout ? (M + 127) / 128 * 128 : (M + 31) / 32 * 32;
+  mx_quant_kernel<true><<<grid_units((int64_t)Mpad * (K / 8)), 256, 0, (cudaStream_t)stream>>>(x, q, scales, M, Mpad, K, x_dtype, scale_layout);
   GL_LAUNCH_CHECK("mx_quant_kernel<fp4>");
   return GL_OK;
 }
 
 extern "C" int gl_scale_activations_mxfp8(const void* x, uint8_t* q, uint8_t* scales, int32_t M, int32_t K,
-                                          int32_t x_dtype, void* stream) {
+                                          int32_t x_dtype, int32_t scale_layout, void* stream) {
   if (int rc = check_x("gl_scale_activations_mxfp8", x, M, K, x_dtype, 32)) return rc;
   if (M == 0) return GL_OK;
   if (!q || !scales || ((uintptr_t)q & 7)) GL_FAIL(GL_E_INVALID, "gl_scale_activations_mxfp8: null or misaligned output");
-  const int Mpad = (M + 31) / 32 * 32;
-  mx_quant_kernel<false><<<grid_units((int64_t)Mpad * (K / 8)), 256, 0, (cudaStream_t)stream>>>(x, q, scales, M, Mpad, K, x_dtype);
+  if (int rc = check_layout("gl_scale_activations_mxfp8", scale_layout, K / 32)) return rc;
+  const int Mpad = scale_layout ? (M + 127) / 128 * 128 : (M + 31) / 32 * 32;
+  mx_quant_kernel<false><<<grid_units((int64_t)Mpad * (K / 8)), 256, 0, (cudaStream_t)stream>>>(x, q, scales, M, Mpad, K, x_dtype, scale_layout);
   GL_LAUNCH_CHECK("mx_quant_kernel<fp8>");
   return GL_OK;
 }
 
 extern "C" int gl_scale_activations_nvfp4(const void* x, uint8_t* q, uint8_t* scales, float* meta_scale,
                                           const float* meta_in, uint32_t* amax_scratch, int32_t M, int32_t K,
-                                          int32_t x_dtype, void* stream) {
+                                          int32_t x_dtype, int32_t scale_layout, void* stream) {
   if (int rc = check_x("gl_scale_activations_nvfp4", x, M, K, x_dtype, 16)) return rc;
+  if (int rc = check_layout("gl_scale_activations_nvfp4", scale_layout, K / 16)) return rc;
   if (M == 0) return GL_OK;
   if (!q || !scales || !meta_scale || ((uintptr_t)q & 3)) GL_FAIL(GL_E_INVALID, "gl_scale_activations_nvfp4: null or misaligned output");
   if (meta_in == nullptr && amax_scratch == nullptr) GL_FAIL(GL_E_INVALID, "gl_scale_activations_nvfp4: amax_scratch needed for the dynamic tensor scale");
   cudaStream_t st = (cudaStream_t)stream;
-  const int Mpad = (M + 15) / 16 * 16;
+  const int Mpad = scale_layout ? (M + 127) / 128 * 128 : (M + 15) / 16 * 16;
   if (meta_in == nullptr) {
     GL_CUDA_CHECK(cudaMemsetAsync(amax_scratch, 0, sizeof(uint32_t), st));
     const int64_t units = (int64_t)M * (K / 8);
     amax_kernel<<<grid_units(units), 256, 0, st>>>(x, amax_scratch, units, x_dtype);
     GL_LAUNCH_CHECK("amax_kernel");
   }
-  nvfp4_quant_kernel<<<grid_units((int64_t)Mpad * (K / 8)), 256, 0, st>>>(x, q, scales, meta_scale, meta_in, amax_scratch, M, Mpad, K, x_dtype);
+  nvfp4_quant_kernel<<<grid_units((int64_t)Mpad * (K / 8)), 256, 0, st>>>(x, q, scales, meta_scale, meta_in, amax_scratch, M, Mpad, K, x_dtype, scale_layout);
   GL_LAUNCH_CHECK("nvfp4_quant_kernel");
   return GL_OK;
 }

@@ -1,0 +1,524 @@
+// Tensor-core GEMM for prefill sizes (M >= 64) on tcgen05 / TMEM, sm_100a.
+//
+// Replaces the reference's gemm / gemm_splitK Triton kernels for large batches
+// (gemlite/triton_kernels/gemm_kernels.py:285-496 integer / fp8 weights, :509-737 MX / NV block-scaled).
+//
+// One CTA computes a 128 x BN output tile; the accumulator lives in TMEM (128 lanes x BN fp32 columns).
+// Shared memory holds a ring of K stages; every operand row of a stage is 128 bytes of K (64 bf16 / 128 fp8 /
+// 256 fp4 values) in the 128-byte-swizzled K-major layout tcgen05.mma reads through shared-memory descriptors.
+// Warp roles (warp-specialised, mbarrier pipelines, every wait bounded):
+//   warp 0        TMA producer: activations (always) and weights (fp8 / int8 / fp4: already K-major in memory);
+//                 block-scaled formats also bulk-copy their scale-factor atoms
+//   warp 1        allocates TMEM, issues tcgen05.mma (one elected lane), commits stages back to the producer
+//   warps 2-5     epilogue: tcgen05.ld the accumulator, channel / tensor scales, bias, cast, store
+//   warps 6-13    (A16Wn only) dequantisers: packed int32 words staged by TMA -> unpack -> (q - z) * s in
+//                 bf16/fp16 exactly as the reference's dequantize() -> swizzled B tile in shared memory
+// Formats:
+//   A16Wn   kind::f16, B produced in shared memory by the dequant warps (the reference's packed [K/8, N] layout
+//           is N-major, tcgen05 wants K-major: one packed word = one 16-byte swizzle chunk of a B row)
+//   A8W8    kind::f8f6f4 (e4m3 x e4m3) or kind::i8, fp32 / int32 accumulate, epilogue acc * s_x[m] * s_w[n]
+//   MXFP4   kind::mxf4.block_scale (e8m0 per 32), NVFP4 kind::mxf4nvf4.block_scale (ue4m3 per 16): scale
+//           factors are copied shared -> TMEM with tcgen05.cp from 128-row x 4-scale atoms (512 bytes)
+#include "gl_tc_common.cuh"
+#include <string.h>
+
+using namespace gltc;
+
+namespace {
+
+constexpr int kNumEpiWarps = 4;
+constexpr int kNumDeqWarps = 8;
+
+struct TcParams {
+  int M, N, K, nkt;
+  uint32_t idesc;
+  void* out; int out_dtype;
+  const void* bias;
+  const float* scales_x;                        // [M] per-token activation scales or null
+  const void* scales_w; int scales_w_dtype;     // [N] channel scales or null
+  const float* meta_scale;                      // tensor scale (NVFP4) or null
+  int* status;
+  // block-scaled formats: scale-factor atoms [rows/128][kblocks][512 B]
+  const uint8_t* sfa; const uint8_t* sfb; int sf_kblocks;
+  // A16Wn
+  const void* gscales; const void* gzeros; int group_size; int W_group_mode; int zero_is_scalar;
+};
+
+template <int KIND> struct KindTraits;
+template <> struct KindTraits<KIND_F16>    { static constexpr int ELEMS_PER_ROW = 64;  static constexpr int SF_ATOMS = 0; };
+template <> struct KindTraits<KIND_F8F6F4> { static constexpr int ELEMS_PER_ROW = 128; static constexpr int SF_ATOMS = 0; };
+template <> struct KindTraits<KIND_I8>     { static constexpr int ELEMS_PER_ROW = 128; static constexpr int SF_ATOMS = 0; };
+template <> struct KindTraits<KIND_MXF4>   { static constexpr int ELEMS_PER_ROW = 256; static constexpr int SF_ATOMS = 2; };
+template <> struct KindTraits<KIND_NVF4>   { static constexpr int ELEMS_PER_ROW = 256; static constexpr int SF_ATOMS = 4; };
+
+constexpr uint32_t next_pow2_cols(uint32_t c) { return c <= 32 ? 32 : c <= 64 ? 64 : c <= 128 ? 128 : c <= 256 ? 256 : 512; }
+
+// ---- epilogue shared by all formats ---------------------------------------------------------------
+template <bool INT_ACC>
+__device__ __forceinline__ void epilogue_tile(const TcParams& p, uint32_t tmem_d, int m0, int n0, int BN, int epi_warp, int lane) {
+  const int quad = epi_warp & 3;                       // TMEM lane quadrant this warp may read
+  const int m = m0 + quad * 32 + lane;
+  const float sx = (p.scales_x != nullptr && m < p.M) ? p.scales_x[m] : 1.f;
+  const float ms = (p.meta_scale != nullptr) ? *p.meta_scale : 1.f;
+  for (int c0 = 0; c0 < BN; c0 += 32) {
+    if (n0 + c0 >= p.N) break;                         // warp-uniform
+    uint32_t rr[32];
+    tmem_ld_32x32(tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, rr);
+    if (m >= p.M) continue;
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      float a = INT_ACC ? (float)(int32_t)rr[i] : __uint_as_float(rr[i]);
+      a *= ms;
+      const int n = n0 + c0 + i;
+      float sw = 1.f;
+      if (p.scales_w != nullptr && n < p.N) sw = gl_load_as_float(p.scales_w, n, p.scales_w_dtype);
+      a *= sx * sw;
+      if (p.bias != nullptr && n < p.N) a += gl_load_as_float(p.bias, n, p.out_dtype);
+      v[i] = a;
+    }
+    const int nb = n0 + c0;
+    const size_t o = (size_t)m * p.N + nb;
+    const bool full = (nb + 32 <= p.N);
+    if (p.out_dtype == GL_BF16 || p.out_dtype == GL_FP16) {
+      if (full && (p.N % 8 == 0)) {
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.out) + o);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint32_t w[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (p.out_dtype == GL_BF16) { __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * q + 2 * j], v[8 * q + 2 * j + 1]); w[j] = *reinterpret_cast<uint32_t*>(&h); }
+            else { __half2 h = __floats2half2_rn(v[8 * q + 2 * j], v[8 * q + 2 * j + 1]); w[j] = *reinterpret_cast<uint32_t*>(&h); }
+          }
+          dst[q] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      } else {
+        for (int i = 0; i < 32 && nb + i < p.N; ++i) gl_store_out(p.out, o + i, v[i], p.out_dtype);
+      }
+    } else {
+      if (full && (p.N % 4 == 0)) {
+        float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + o);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+      } else {
+        for (int i = 0; i < 32 && nb + i < p.N; ++i) reinterpret_cast<float*>(p.out)[o + i] = v[i];
+      }
+    }
+  }
+}
+
+// ---- both operands by TMA: fp8 / int8 / mxfp4 / nvfp4 ---------------------------------------------
+template <int KIND, int BN, int STAGES>
+__global__ void __launch_bounds__(192, 1) gl_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,
+                                                            const __grid_constant__ CUtensorMap tmB, const TcParams p) {
+  using KT = KindTraits<KIND>;
+  constexpr bool MX = KT::SF_ATOMS > 0;
+  constexpr int A_BYTES = 128 * 128, B_BYTES = BN * 128;
+  constexpr int SFA_BYTES = KT::SF_ATOMS * 512, SFB_BYTES = KT::SF_ATOMS * 512 * (BN / 128);
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+  constexpr uint32_t SFA_COL = BN, SFB_COL = BN + KT::SF_ATOMS * 4;
+  constexpr uint32_t TMEM_COLS = next_pow2_cols(BN + KT::SF_ATOMS * 4 * (1 + BN / 128));
+
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tmem_full = empty + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
+  __shared__ int s_abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (p.M + 127) / 128;
+  const int m0 = (blockIdx.x % tiles_m) * 128, n0 = (blockIdx.x / tiles_m) * BN;
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
+    mbar_init(tmem_full, 1);
+    fence_barrier_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+  }
+  if (MX) {   // scale-factor atoms that a short last K tile does not overwrite must hold finite numbers
+    for (int s = 0; s < STAGES; ++s)
+      for (int i = threadIdx.x; i < (SFA_BYTES + SFB_BYTES) / 4; i += blockDim.x)
+        reinterpret_cast<uint32_t*>(smem + s * STAGE_BYTES + A_BYTES + B_BYTES)[i] = 0u;
+    fence_proxy_async_smem();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kt = 0; kt < p.nkt; ++kt) {
+        const int s = kt % STAGES;
+        if (!mbar_wait(empty + s, (uint32_t)(((kt / STAGES) & 1) ^ 1), &s_abort, p.status, 2)) break;
+        unsigned char* st = smem + s * STAGE_BYTES;
+        uint32_t bytes = A_BYTES + B_BYTES;
+        int atoms = 0;
+        const int valid_nb = min(BN / 128, (p.N - n0 + 127) / 128);   // 128-column blocks of this tile that exist
+        if (MX) {
+          atoms = min(KT::SF_ATOMS, p.sf_kblocks - kt * KT::SF_ATOMS);
+          bytes += (uint32_t)atoms * 512u * (1 + valid_nb);
+        }
+        mbar_expect_tx(full + s, bytes);
+        tma_load_2d(st, &tmA, full + s, kt * 128, m0);
+        tma_load_2d(st + A_BYTES, &tmB, full + s, kt * 128, n0);
+        if (MX) {
+          const size_t koff = (size_t)kt * KT::SF_ATOMS;
+          bulk_load_1d(st + A_BYTES + B_BYTES, p.sfa + ((size_t)(m0 / 128) * p.sf_kblocks + koff) * 512, (uint32_t)atoms * 512u, full + s);
+          for (int nb = 0; nb < valid_nb; ++nb)
+            bulk_load_1d(st + A_BYTES + B_BYTES + SFA_BYTES + nb * KT::SF_ATOMS * 512,
+                         p.sfb + ((size_t)(n0 / 128 + nb) * p.sf_kblocks + koff) * 512, (uint32_t)atoms * 512u, full + s);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int kt = 0; kt < p.nkt && ok; ++kt) {
+        const int s = kt % STAGES;
+        if (!mbar_wait(full + s, (uint32_t)((kt / STAGES) & 1), &s_abort, p.status, 3)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sa = smem_u32(smem + s * STAGE_BYTES), sb = sa + A_BYTES;
+        if (MX) {
+#pragma unroll
+          for (int a = 0; a < KT::SF_ATOMS; ++a) {
+            tmem_cp_sf(tmem_base + SFA_COL + a * 4, smem_desc_sf(sb + B_BYTES + a * 512));
+#pragma unroll
+            for (int nb = 0; nb < BN / 128; ++nb)
+              tmem_cp_sf(tmem_base + SFB_COL + a * 4 * (BN / 128) + nb * 4, smem_desc_sf(sb + B_BYTES + SFA_BYTES + (nb * KT::SF_ATOMS + a) * 512));
+          }
+        }
+        const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sb);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t accum = (kt > 0 || j > 0) ? 1u : 0u;
+          if constexpr (KIND == KIND_MXF4) {
+            const uint32_t sfid = (uint32_t)(2 * (j & 1));
+            mma_ss_block_scaled<KIND>(tmem_base, da + 2 * j, db + 2 * j, p.idesc | (sfid << 29) | (sfid << 4),
+                                      tmem_base + SFA_COL + (j >> 1) * 4, tmem_base + SFB_COL + (j >> 1) * 4 * (BN / 128), accum);
+          } else if constexpr (KIND == KIND_NVF4) {
+            mma_ss_block_scaled<KIND>(tmem_base, da + 2 * j, db + 2 * j, p.idesc,
+                                      tmem_base + SFA_COL + j * 4, tmem_base + SFB_COL + j * 4 * (BN / 128), accum);
+          } else {
+            mma_ss<KIND>(tmem_base, da + 2 * j, db + 2 * j, p.idesc, accum);
+          }
+        }
+        tc_commit(empty + s);
+      }
+      if (ok) tc_commit(tmem_full);
+    }
+  } else {
+    if (mbar_wait(tmem_full, 0u, &s_abort, p.status, 4)) {
+      tc_fence_after();
+      epilogue_tile<KIND == KIND_I8>(p, tmem_base, m0, n0, BN, warp, lane);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---- A16Wn: weights dequantised into the B tile by eight warps -------------------------------------
+template <typename XT> struct H2;
+template <> struct H2<__nv_bfloat16> {
+  using T = __nv_bfloat162;
+  static constexpr uint32_t MAGIC = 0x43004300u;
+  __device__ static T from_float(float v) { return __float2bfloat162_rn(v); }
+};
+template <> struct H2<__half> {
+  using T = __half2;
+  static constexpr uint32_t MAGIC = 0x64006400u;
+  __device__ static T from_float(float v) { return __float2half2_rn(v); }
+};
+
+template <typename XT, int NB, int BN, int STAGES>
+__global__ void __launch_bounds__(448, 1) gl_gemm_tc_a16wn_kernel(const __grid_constant__ CUtensorMap tmA,
+                                                                  const __grid_constant__ CUtensorMap tmW, const TcParams p) {
+  constexpr int E = 32 / NB;                           // k values per packed word
+  constexpr int WROWS = 64 / E;                        // packed rows per 64-wide K tile (8 for 4-bit)
+  constexpr int A_BYTES = 128 * 128, B_BYTES = BN * 128, W_BYTES = WROWS * BN * 4;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES + ((W_BYTES + 1023) / 1024) * 1024;
+  constexpr uint32_t TMEM_COLS = next_pow2_cols(BN);
+  constexpr int HALF = 16 / NB;                        // field a shares a 32-bit extraction with field a + HALF
+  constexpr uint32_t FMASK = ((1u << NB) - 1u) * 0x00010001u;
+  using h2 = typename H2<XT>::T;
+
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);   // A landed
+  uint64_t* wfull = full + STAGES;                                              // packed W landed
+  uint64_t* bready = wfull + STAGES;                                            // B tile written by the dequant warps
+  uint64_t* empty = bready + STAGES;                                            // MMAs of the stage retired
+  uint64_t* tmem_full = empty + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
+  __shared__ int s_abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (p.M + 127) / 128;
+  const int m0 = (blockIdx.x % tiles_m) * 128, n0 = (blockIdx.x / tiles_m) * BN;
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(wfull + s, 1); mbar_init(bready + s, kNumDeqWarps); mbar_init(empty + s, 1); }
+    mbar_init(tmem_full, 1);
+    fence_barrier_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmW);
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kt = 0; kt < p.nkt; ++kt) {
+        const int s = kt % STAGES;
+        if (!mbar_wait(empty + s, (uint32_t)(((kt / STAGES) & 1) ^ 1), &s_abort, p.status, 2)) break;
+        unsigned char* st = smem + s * STAGE_BYTES;
+        mbar_expect_tx(wfull + s, W_BYTES);
+        tma_load_2d(st + A_BYTES + B_BYTES, &tmW, wfull + s, n0, kt * WROWS);
+        mbar_expect_tx(full + s, A_BYTES);
+        tma_load_2d(st, &tmA, full + s, kt * 64, m0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int kt = 0; kt < p.nkt && ok; ++kt) {
+        const int s = kt % STAGES;
+        const uint32_t ph = (uint32_t)((kt / STAGES) & 1);
+        if (!mbar_wait(full + s, ph, &s_abort, p.status, 3) || !mbar_wait(bready + s, ph, &s_abort, p.status, 5)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+        const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sa + A_BYTES);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) mma_ss<KIND_F16>(tmem_base, da + 2 * j, db + 2 * j, p.idesc, (kt > 0 || j > 0) ? 1u : 0u);
+        tc_commit(empty + s);
+      }
+      if (ok) tc_commit(tmem_full);
+    }
+  } else if (warp < 2 + kNumEpiWarps) {
+    if (mbar_wait(tmem_full, 0u, &s_abort, p.status, 4)) {
+      tc_fence_after();
+      epilogue_tile<false>(p, tmem_base, m0, n0, BN, warp, lane);
+    }
+  } else {
+    // dequant warps: warp dw owns 32 columns (BN = 256) or 32 columns x half of the packed rows (BN = 128)
+    const int dw = warp - 2 - kNumEpiWarps;
+    constexpr int CBLOCKS = BN / 32;                       // 32-column blocks in the tile
+    constexpr int RSPLIT = kNumDeqWarps / CBLOCKS;         // warps sharing one column block (1 or 2)
+    constexpr int RPW = WROWS / RSPLIT;                    // packed rows per warp
+    const int nl = (dw % CBLOCKS) * 32 + lane;             // column inside the tile
+    const int c_begin = (dw / CBLOCKS) * RPW;
+    const int n = n0 + nl;
+    const bool n_ok = n < p.N;
+    constexpr uint32_t kMagic = H2<XT>::MAGIC;
+    uint32_t magic_bits = kMagic;
+    const h2 magic = *reinterpret_cast<const h2*>(&magic_bits);
+    int g_cur = -1;
+    h2 s2 = H2<XT>::from_float(1.f), z2 = H2<XT>::from_float(0.f);
+    if (p.zero_is_scalar && p.gzeros) z2 = H2<XT>::from_float((float)(*reinterpret_cast<const int32_t*>(p.gzeros)));
+    for (int kt = 0; kt < p.nkt; ++kt) {
+      const int s = kt % STAGES;
+      if (!mbar_wait(wfull + s, (uint32_t)((kt / STAGES) & 1), &s_abort, p.status, 6)) break;
+      const int g = (kt * 64) / p.group_size;
+      if (g != g_cur) {
+        g_cur = g;
+        if (n_ok) {
+          if (p.W_group_mode >= 2) { const XT v = reinterpret_cast<const XT*>(p.gscales)[(size_t)g * p.N + n]; s2 = h2(v, v); }
+          if ((p.W_group_mode == 1 || p.W_group_mode >= 3) && !p.zero_is_scalar) { const XT v = reinterpret_cast<const XT*>(p.gzeros)[(size_t)g * p.N + n]; z2 = h2(v, v); }
+        }
+      }
+      unsigned char* st = smem + s * STAGE_BYTES;
+      const uint32_t* wst = reinterpret_cast<const uint32_t*>(st + A_BYTES + B_BYTES);
+      unsigned char* brow = st + A_BYTES + nl * 128;
+      const int wgm = p.W_group_mode;
+#pragma unroll
+      for (int cc = 0; cc < RPW; ++cc) {
+        const int c = c_begin + cc;                        // packed row inside the K tile
+        const uint32_t w = wst[c * BN + nl];
+        // pair a = (field a, field a + HALF), dequantised exactly as dequantize() does in the scale dtype
+        uint32_t P[HALF];
+#pragma unroll
+        for (int a = 0; a < HALF; ++a) {
+          uint32_t bits = ((w >> (NB * a)) & FMASK) | kMagic;
+          h2 q = __hsub2(*reinterpret_cast<h2*>(&bits), magic);            // exact integer code
+          if (wgm == 4) q = __hfma2(q, s2, z2);
+          else if (wgm == 3) q = __hmul2(__hsub2(q, z2), s2);
+          else if (wgm == 2) q = __hmul2(q, s2);
+          else if (wgm == 1) q = __hsub2(q, z2);
+          P[a] = *reinterpret_cast<uint32_t*>(&q);
+        }
+        // natural k order: low halves are fields 0..HALF-1, high halves fields HALF..2*HALF-1
+        uint32_t L[HALF / 2], Hh[HALF / 2];
+#pragma unroll
+        for (int j = 0; j < HALF / 2; ++j) {
+          L[j] = __byte_perm(P[2 * j], P[2 * j + 1], 0x5410);
+          Hh[j] = __byte_perm(P[2 * j], P[2 * j + 1], 0x7632);
+        }
+        const int chunk0 = c * (E / 8);
+        if constexpr (NB == 4) {
+          *reinterpret_cast<uint4*>(brow + (((chunk0) ^ (nl & 7)) << 4)) = make_uint4(L[0], L[1], Hh[0], Hh[1]);
+        } else {
+          constexpr int CH = HALF / 8;                     // chunks per half (1 for 2-bit, 2 for 1-bit)
+#pragma unroll
+          for (int ch = 0; ch < CH; ++ch) {
+            *reinterpret_cast<uint4*>(brow + (((chunk0 + ch) ^ (nl & 7)) << 4)) = make_uint4(L[4 * ch], L[4 * ch + 1], L[4 * ch + 2], L[4 * ch + 3]);
+            *reinterpret_cast<uint4*>(brow + (((chunk0 + CH + ch) ^ (nl & 7)) << 4)) = make_uint4(Hh[4 * ch], Hh[4 * ch + 1], Hh[4 * ch + 2], Hh[4 * ch + 3]);
+          }
+        }
+      }
+      fence_proxy_async_smem();                            // generic-proxy stores -> visible to the tensor core
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bready + s);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+
+template <typename K>
+static int set_smem(K kern, size_t smem) {
+  GL_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  return GL_OK;
+}
+
+template <int KIND, int BN, int STAGES>
+static int launch_tma_kernel(const CUtensorMap& tmA, const CUtensorMap& tmB, const TcParams& p, cudaStream_t st) {
+  using KT = KindTraits<KIND>;
+  constexpr size_t stage = 128 * 128 + BN * 128 + KT::SF_ATOMS * 512 * (1 + BN / 128);
+  const size_t smem = 1024 + STAGES * stage + (2 * STAGES + 1) * 8 + 16;
+  auto kern = gl_gemm_tc_kernel<KIND, BN, STAGES>;
+  if (int rc = set_smem(kern, smem)) return rc;
+  const int tiles = ((p.M + 127) / 128) * ((p.N + BN - 1) / BN);
+  kern<<<tiles, 192, smem, st>>>(tmA, tmB, p);
+  GL_LAUNCH_CHECK("gl_gemm_tc_kernel");
+  return GL_OK;
+}
+
+template <typename XT, int NB, int BN, int STAGES>
+static int launch_a16_kernel(const CUtensorMap& tmA, const CUtensorMap& tmW, const TcParams& p, cudaStream_t st) {
+  constexpr int WROWS = 64 / (32 / NB);
+  constexpr size_t stage = 128 * 128 + BN * 128 + ((WROWS * BN * 4 + 1023) / 1024) * 1024;
+  const size_t smem = 1024 + STAGES * stage + (4 * STAGES + 1) * 8 + 16;
+  auto kern = gl_gemm_tc_a16wn_kernel<XT, NB, BN, STAGES>;
+  if (int rc = set_smem(kern, smem)) return rc;
+  const int tiles = ((p.M + 127) / 128) * ((p.N + BN - 1) / BN);
+  kern<<<tiles, 448, smem, st>>>(tmA, tmW, p);
+  GL_LAUNCH_CHECK("gl_gemm_tc_a16wn_kernel");
+  return GL_OK;
+}
+
+enum TcPath { TC_NONE = 0, TC_A16WN, TC_FP8, TC_INT8, TC_MXFP4, TC_NVFP4 };
+
+static TcPath classify(const gl_matmul_args* a) {
+  if (a->M < 1) return TC_NONE;
+  if (((uintptr_t)a->x & 15) || ((uintptr_t)a->w & 15) || ((uintptr_t)a->out & 15)) return TC_NONE;
+  if (!(a->out_dtype == GL_BF16 || a->out_dtype == GL_FP16 || a->out_dtype == GL_FP32)) return TC_NONE;
+  if (a->channel_scale_mode == 5) return TC_NONE;
+  const int e = a->elements_per_sample;
+  // A16Wn: fp16 / bf16 activations, 4- or 2-bit codes packed in int32 along K, group-wise meta data
+  if ((a->x_dtype == GL_BF16 || a->x_dtype == GL_FP16) && a->input_dtype == a->x_dtype && a->w_dtype == GL_INT32 &&
+      (a->W_nbits == 4 || a->W_nbits == 2 || a->W_nbits == 1) && e == 32 / a->W_nbits) {
+    if (a->w_stride_n != 1 || a->w_stride_k != a->N || a->N % 4 != 0) return TC_NONE;
+    if (a->group_size % 64 != 0) return TC_NONE;
+    if (!(a->channel_scale_mode == 0 || a->channel_scale_mode == 1)) return TC_NONE;
+    const bool need_s = a->W_group_mode >= 2, need_z = a->W_group_mode == 1 || a->W_group_mode >= 3;
+    if ((need_s || a->channel_scale_mode == 1) && (a->scales == nullptr || a->meta_dtype != a->x_dtype)) return TC_NONE;
+    if (need_s && (a->s_stride_n != 1 || a->s_stride_g != a->N)) return TC_NONE;
+    if (need_z && a->zeros == nullptr) return TC_NONE;
+    if (need_z && !a->zero_is_scalar && a->zeros_dtype != a->x_dtype) return TC_NONE;
+    if (need_z && a->zero_is_scalar && a->zeros_dtype != GL_INT32) return TC_NONE;
+    if (a->channel_scale_mode == 1 && a->W_group_mode >= 2) return TC_NONE;
+    return TC_A16WN;
+  }
+  // A8W8: e4m3 x e4m3 or int8 x int8, weights [N, K] with K contiguous, optional per-token / per-channel scales
+  if (e == 1 && a->W_nbits == 8 && a->W_group_mode == 0 && a->w_stride_k == 1 && a->w_stride_n == a->K && a->K % 16 == 0) {
+    if ((a->channel_scale_mode == 2 || a->channel_scale_mode == 3) && a->scales_x == nullptr) return TC_NONE;
+    if ((a->channel_scale_mode == 1 || a->channel_scale_mode == 3) && a->scales == nullptr) return TC_NONE;
+    if (a->x_dtype == GL_FP8 && a->w_dtype == GL_FP8 && a->input_dtype == GL_FP8) return TC_FP8;
+    if (a->x_dtype == GL_INT8 && a->w_dtype == GL_INT8 && a->input_dtype == GL_INT8) return TC_INT8;
+    return TC_NONE;
+  }
+  // MXFP4 / NVFP4 with block-scaled activations: both operands packed e2m1, scale factors given as atoms
+  if ((a->input_dtype == GL_MXFP4 || a->input_dtype == GL_NVFP4) && a->x_dtype == GL_UINT8 && a->w_dtype == GL_UINT8 && e == 2 &&
+      a->channel_scale_mode == 4 && a->w_stride_k == 1 && a->w_stride_n == a->K / 2 && a->K % 32 == 0) {
+    const int gs = a->input_dtype == GL_MXFP4 ? 32 : 16;
+    if (a->group_size != gs || a->w_scales_atoms == nullptr || a->scales_x == nullptr || a->sx_layout != 1) return TC_NONE;
+    if ((a->K / gs) % 4 != 0) return TC_NONE;
+    if (((uintptr_t)a->w_scales_atoms & 15) || ((uintptr_t)a->scales_x & 15)) return TC_NONE;
+    return a->input_dtype == GL_MXFP4 ? TC_MXFP4 : TC_NVFP4;
+  }
+  return TC_NONE;
+}
+
+}  // namespace
+
+int gl_gemm_tc_supported(const gl_matmul_args* a) { return classify(a) != TC_NONE; }
+
+int gl_gemm_tc_launch(const gl_matmul_args* a, cudaStream_t st) {
+  const TcPath path = classify(a);
+  if (path == TC_NONE) GL_FAIL(GL_E_UNSUPPORTED, "gl_matmul: no tensor-core kernel for this problem");
+  if (a->workspace == nullptr || a->workspace_bytes < gl_matmul_counter_bytes())
+    GL_FAIL(GL_E_WORKSPACE, "gl_matmul: workspace of %llu bytes needed", (unsigned long long)gl_matmul_counter_bytes());
+  TcParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = a->M; p.N = a->N; p.K = a->K;
+  p.out = a->out; p.out_dtype = a->out_dtype; p.bias = a->bias;
+  p.status = reinterpret_cast<int*>(reinterpret_cast<char*>(a->workspace) + gl_matmul_counter_bytes() - 256);
+  p.meta_scale = nullptr;
+  const int BN = (a->N >= 256 && ((int64_t)((a->M + 127) / 128) * ((a->N + 255) / 256) >= 96)) ? 256 : 128;
+  CUtensorMap tmA, tmB;
+  if (path == TC_A16WN) {
+    p.nkt = (a->K + 63) / 64;
+    p.idesc = gl_idesc(1, a->x_dtype == GL_BF16 ? 1 : 0, a->x_dtype == GL_BF16 ? 1 : 0, 128, BN);
+    if (a->channel_scale_mode == 1) { p.scales_w = a->scales; p.scales_w_dtype = a->meta_dtype; }
+    p.gscales = a->scales; p.gzeros = a->zeros; p.group_size = a->group_size; p.W_group_mode = a->W_group_mode; p.zero_is_scalar = a->zero_is_scalar;
+    const int wrows = 64 / a->elements_per_sample;
+    if (int rc = gl_make_tmap_2d(&tmA, a->x, a->x_dtype == GL_BF16 ? 1 : 2, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->K * 2, 64, 128, true)) return rc;
+    if (int rc = gl_make_tmap_2d(&tmB, a->w, 3, (uint64_t)a->N, (uint64_t)(a->K / a->elements_per_sample), (uint64_t)a->N * 4, (uint32_t)BN, (uint32_t)wrows, false)) return rc;
+#define GL_A16(XT, NB)                                                                              \
+    (BN == 256 ? launch_a16_kernel<XT, NB, 256, 3>(tmA, tmB, p, st) : launch_a16_kernel<XT, NB, 128, 4>(tmA, tmB, p, st))
+    if (a->x_dtype == GL_BF16) {
+      if (a->W_nbits == 4) return GL_A16(__nv_bfloat16, 4);
+      if (a->W_nbits == 2) return GL_A16(__nv_bfloat16, 2);
+      return GL_A16(__nv_bfloat16, 1);
+    }
+    if (a->W_nbits == 4) return GL_A16(__half, 4);
+    if (a->W_nbits == 2) return GL_A16(__half, 2);
+    return GL_A16(__half, 1);
+#undef GL_A16
+  }
+  if (path == TC_FP8 || path == TC_INT8) {
+    p.nkt = (a->K + 127) / 128;
+    p.idesc = (path == TC_FP8) ? gl_idesc(1, 0, 0, 128, BN) : gl_idesc(2, 1, 1, 128, BN);
+    if (a->channel_scale_mode == 2 || a->channel_scale_mode == 3) p.scales_x = reinterpret_cast<const float*>(a->scales_x);
+    if (a->channel_scale_mode == 1 || a->channel_scale_mode == 3) { p.scales_w = a->scales; p.scales_w_dtype = a->meta_dtype; }
+    if (int rc = gl_make_tmap_2d(&tmA, a->x, 0, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->K, 128, 128, true)) return rc;
+    if (int rc = gl_make_tmap_2d(&tmB, a->w, 0, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)a->K, 128, (uint32_t)BN, true)) return rc;
+    if (path == TC_FP8) return BN == 256 ? launch_tma_kernel<KIND_F8F6F4, 256, 4>(tmA, tmB, p, st) : launch_tma_kernel<KIND_F8F6F4, 128, 6>(tmA, tmB, p, st);
+    return BN == 256 ? launch_tma_kernel<KIND_I8, 256, 4>(tmA, tmB, p, st) : launch_tma_kernel<KIND_I8, 128, 6>(tmA, tmB, p, st);
+  }
+  // block-scaled fp4
+  const int gs = path == TC_MXFP4 ? 32 : 16;
+  p.nkt = (a->K + 255) / 256;
+  p.idesc = gl_idesc_block_scaled(1, path == TC_MXFP4 ? 1 : 0, 128, BN);
+  p.sfa = reinterpret_cast<const uint8_t*>(a->scales_x);
+  p.sfb = reinterpret_cast<const uint8_t*>(a->w_scales_atoms);
+  p.sf_kblocks = a->K / gs / 4;
+  p.meta_scale = (path == TC_NVFP4) ? a->meta_scale : nullptr;
+  if (int rc = gl_make_tmap_2d(&tmA, a->x, 0, (uint64_t)a->K / 2, (uint64_t)a->M, (uint64_t)a->K / 2, 128, 128, true)) return rc;
+  if (int rc = gl_make_tmap_2d(&tmB, a->w, 0, (uint64_t)a->K / 2, (uint64_t)a->N, (uint64_t)a->K / 2, 128, (uint32_t)BN, true)) return rc;
+  if (path == TC_MXFP4) return BN == 256 ? launch_tma_kernel<KIND_MXF4, 256, 3>(tmA, tmB, p, st) : launch_tma_kernel<KIND_MXF4, 128, 5>(tmA, tmB, p, st);
+  return BN == 256 ? launch_tma_kernel<KIND_NVF4, 256, 3>(tmA, tmB, p, st) : launch_tma_kernel<KIND_NVF4, 128, 5>(tmA, tmB, p, st);
+}

@@ -102,7 +102,10 @@ __global__ void __launch_bounds__(128) gl_generic_kernel(const GenParams p) {
             xv = gl_load_as_float(a.x, (int64_t)m * a.K + k, a.x_dtype);
           }
           if (p.is_mx && a.channel_scale_mode == 4) {
-            const uint32_t sa = reinterpret_cast<const uint8_t*>(a.scales_x)[(int64_t)m * p.sx_stride + k / p.gx];
+            const int kg = k / p.gx;
+            const int64_t si = a.sx_layout == 0 ? (int64_t)m * p.sx_stride + kg
+                                                : ((int64_t)(m >> 7) * (p.sx_stride >> 2) + (kg >> 2)) * 512 + (m & 31) * 16 + ((m & 127) >> 5) * 4 + (kg & 3);
+            const uint32_t sa = reinterpret_cast<const uint8_t*>(a.scales_x)[si];
             xv *= (p.gx == 16) ? gl_e4m3_to_float(sa) : gl_e8m0_to_float(sa);
           }
           acc[i] = fmaf(xv, b, acc[i]);

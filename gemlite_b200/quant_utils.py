@@ -146,31 +146,37 @@ def scale_activations_per_token(tensor: Tensor, w_dtype: torch.dtype, fp32_scale
     return q.view(shape), scales
 
 
-def scale_activations_mxfp8(tensor: Tensor, w_dtype: torch.dtype = torch.float8_e4m3fn) -> Tuple[Tensor, Tensor]:
+def _scale_buffer(M, G, pad, scale_layout, dtype, device):
+    """Row layout [ceil_pad(M), G] (what the reference returns) or, for scale_layout=1, the 128x4 scale
+    atoms the block-scaled tensor-core kernel reads: [ceil128(M)/128, G/4, 512] bytes."""
+    if scale_layout == 0:
+        return torch.empty(((M + pad - 1) // pad * pad, G), dtype=dtype, device=device)
+    return torch.empty(((M + 127) // 128, G // 4, 512), dtype=dtype, device=device)
+
+
+def scale_activations_mxfp8(tensor: Tensor, w_dtype: torch.dtype = torch.float8_e4m3fn, scale_layout: int = 0) -> Tuple[Tensor, Tensor]:
     """MXFP8: (q e4m3 like tensor, e8m0 scale bytes uint8 [ceil32(M), K/32]).  quant_utils.py:1095-1124."""
     if w_dtype != torch.float8_e4m3fn:
         raise NotImplementedError("MXFP8 activations are e4m3 only")
     x, shape = _as_2d(tensor)
     M, K = x.shape
-    Mpad = (M + 31) // 32 * 32
     q = torch.empty((M, K), dtype=w_dtype, device=x.device)
-    scales = torch.empty((Mpad, K // 32), dtype=torch.uint8, device=x.device)
+    scales = _scale_buffer(M, K // 32, 32, scale_layout, torch.uint8, x.device)
     with torch.cuda.device(x.device):
         _lib.check(_lib.lib().gl_scale_activations_mxfp8(x.data_ptr(), q.data_ptr(), scales.data_ptr(), M, K,
-                                                        TORCH_TO_DTYPE[x.dtype].value, _lib.current_stream_ptr(x.device)))
+                                                        TORCH_TO_DTYPE[x.dtype].value, scale_layout, _lib.current_stream_ptr(x.device)))
     return q.view(shape), scales
 
 
-def scale_activations_mxfp4(tensor: Tensor) -> Tuple[Tensor, Tensor]:
+def scale_activations_mxfp4(tensor: Tensor, scale_layout: int = 0) -> Tuple[Tensor, Tensor]:
     """MXFP4: (q uint8 [M, K/2] e2m1 pairs, e8m0 scale bytes uint8 [ceil32(M), K/32]).  quant_utils.py:2107-2135."""
     x, _ = _as_2d(tensor)
     M, K = x.shape
-    Mpad = (M + 31) // 32 * 32
     q = torch.empty((M, K // 2), dtype=torch.uint8, device=x.device)
-    scales = torch.empty((Mpad, K // 32), dtype=torch.uint8, device=x.device)
+    scales = _scale_buffer(M, K // 32, 32, scale_layout, torch.uint8, x.device)
     with torch.cuda.device(x.device):
         _lib.check(_lib.lib().gl_scale_activations_mxfp4(x.data_ptr(), q.data_ptr(), scales.data_ptr(), M, K,
-                                                        TORCH_TO_DTYPE[x.dtype].value, _lib.current_stream_ptr(x.device)))
+                                                        TORCH_TO_DTYPE[x.dtype].value, scale_layout, _lib.current_stream_ptr(x.device)))
     return q, scales
 
 
@@ -187,15 +193,14 @@ def _nvfp4_scratch(device):
     return buf
 
 
-def scale_activations_nvfp4(tensor: Tensor, meta_scale=None) -> Tuple[Tensor, Tensor, Tensor]:
+def scale_activations_nvfp4(tensor: Tensor, meta_scale=None, scale_layout: int = 0) -> Tuple[Tensor, Tensor, Tensor]:
     """NVFP4: (q uint8 [M, K/2], e4m3 scales [ceil16(M), K/16], fp32 tensor scale [1]).
 
     ``meta_scale`` (device fp32 tensor) switches to the static-scale path.  quant_utils.py:2434-2493."""
     x, _ = _as_2d(tensor)
     M, K = x.shape
-    Mpad = (M + 15) // 16 * 16
     q = torch.empty((M, K // 2), dtype=torch.uint8, device=x.device)
-    scales = torch.empty((Mpad, K // 16), dtype=torch.float8_e4m3fn, device=x.device)
+    scales = _scale_buffer(M, K // 16, 16, scale_layout, torch.float8_e4m3fn, x.device)
     meta_out = torch.empty(1, dtype=torch.float32, device=x.device)
     meta_in = None
     if meta_scale is not None:
@@ -204,7 +209,7 @@ def scale_activations_nvfp4(tensor: Tensor, meta_scale=None) -> Tuple[Tensor, Te
         _lib.check(_lib.lib().gl_scale_activations_nvfp4(
             x.data_ptr(), q.data_ptr(), scales.data_ptr(), meta_out.data_ptr(),
             None if meta_in is None else meta_in.data_ptr(), _nvfp4_scratch(x.device).data_ptr(),
-            M, K, TORCH_TO_DTYPE[x.dtype].value, _lib.current_stream_ptr(x.device)))
+            M, K, TORCH_TO_DTYPE[x.dtype].value, scale_layout, _lib.current_stream_ptr(x.device)))
     return q, scales, meta_out
 
 

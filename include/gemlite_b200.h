@@ -118,8 +118,17 @@ typedef struct gl_matmul_args {
   int64_t      w_stride_k, w_stride_n;
   int64_t      s_stride_g, s_stride_n;
   int32_t      kernel_override; /* 0 = library picks the kernel; 1 = the general CUDA-core kernel (testing / debugging) */
-  int32_t      reserved[3];    /* must be 0 */
+  int32_t      sx_layout;      /* layout of block-scaled `scales_x`: 0 = [Mpad, K/g] rows, 1 = 128x4 scale atoms */
+  int32_t      reserved[2];    /* must be 0 */
+  const void*  w_scales_atoms; /* optional copy of the MX / NV weight scales as 128x4 scale atoms, or NULL   */
 } gl_matmul_args;
+
+/* "128x4 scale atoms": the scale-factor layout block-scaled tcgen05.mma reads, identical to the reference's 5-D
+ * pre-shuffled scales [1, R/128, G/4, 2, 256] (gemlite/core.py:748-752): for row r (output column n for
+ * weights, batch row m for activations) and group g,
+ *   byte offset = ((r/128) * (G/4) + g/4) * 512 + (r%32) * 16 + ((r%128)/32) * 4 + g%4,   G = K / group_size.
+ * Rows are padded to a multiple of 128 and G must be a multiple of 4.  The tensor-core kernels for MXFP4 /
+ * NVFP4 need both operands' scales in this layout; the general kernel reads the row layouts. */
 
 /* library / build info */
 GL_API int         gl_abi_version(void);
@@ -178,10 +187,11 @@ GL_API int gl_unpack_over_rows(const void* in, void* out, int64_t rows_packed, i
 GL_API int gl_scale_activations_per_token(const void* x, void* q, float* scales, int32_t M, int32_t K,
                                    int32_t x_dtype, int32_t q_dtype, void* stream);
 /* x [M,K] -> q uint8 [M,K/2] (e2m1 pairs, even k low nibble) + e8m0 bytes
- * scales [ceil32(M), K/32] (pad rows = 127).
+ * scales [ceil32(M), K/32] (pad rows = 127); scale_layout 1 writes them as 128x4 scale atoms over
+ * ceil128(M) rows instead (see gl_matmul_args).
  * Replaces scale_activations_mxfp4 (v5 kernel), gemlite/quant_utils.py:1993-2135. */
 GL_API int gl_scale_activations_mxfp4(const void* x, uint8_t* q, uint8_t* scales, int32_t M, int32_t K,
-                               int32_t x_dtype, void* stream);
+                               int32_t x_dtype, int32_t scale_layout, void* stream);
 /* x [M,K] -> q uint8 [M,K/2] + e4m3 bytes scales [ceil16(M), K/16] (pad rows = 1.0) and the
  * fp32 tensor scale meta_scale[0] = 448*6/max(amax,1e-6).  When meta_in != NULL that
  * device scalar is used instead of the dynamic amax (static / calibrated scale) and copied to
@@ -189,11 +199,11 @@ GL_API int gl_scale_activations_mxfp4(const void* x, uint8_t* q, uint8_t* scales
  * Replaces scale_activations_nvfp4 (fused v6 / v5 kernels), gemlite/quant_utils.py:2152-2493. */
 GL_API int gl_scale_activations_nvfp4(const void* x, uint8_t* q, uint8_t* scales, float* meta_scale,
                                const float* meta_in, uint32_t* amax_scratch,
-                               int32_t M, int32_t K, int32_t x_dtype, void* stream);
+                               int32_t M, int32_t K, int32_t x_dtype, int32_t scale_layout, void* stream);
 /* x [M,K] -> q fp8 e4m3 [M,K] + e8m0 bytes scales [ceil32(M), K/32] (pad rows = 127).
  * Replaces scale_activations_mxfp8 (v4 kernel), gemlite/quant_utils.py:1024-1124. */
 GL_API int gl_scale_activations_mxfp8(const void* x, uint8_t* q, uint8_t* scales, int32_t M, int32_t K,
-                               int32_t x_dtype, void* stream);
+                               int32_t x_dtype, int32_t scale_layout, void* stream);
 
 /* ---- tile-config cache: gemlite/core.py:80-89, 838-906 ---------------------------------- */
 /* The cache maps  family name -> signature string "(Mb, N, K, group_size, e, type_id)" -> a

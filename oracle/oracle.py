@@ -328,14 +328,19 @@ def quantize_mxfp4_weights(W):
     return codes, sb
 
 
-def quantize_nvfp4_weights(W):
-    """gemlite/quant_utils.py:171-219.  -> (codes [N, K], e4m3 bytes [N, K/16], meta fp32)."""
+def quantize_nvfp4_weights(W, meta=None):
+    """gemlite/quant_utils.py:171-219.  -> (codes [N, K], e4m3 bytes [N, K/16], meta fp32).
+
+    The tensor scale 448 / max(amax/6) is written `448 / tensor` in the reference, which torch evaluates
+    as tensor.reciprocal() * 448; the last bit of that product differs between torch's CPU and CUDA
+    kernels, so a caller comparing against a layer quantised on a GPU passes the layer's `meta`."""
     W = np.asarray(W, dtype=np.float32)
     N, K = W.shape
     g = W.reshape(-1, 16)
     ideal = (np.abs(g).max(1, keepdims=True) / np.float32(6.0)).astype(np.float32)
-    # torch evaluates `448 / tensor` as tensor.reciprocal() * 448 (quant_utils.py:186)
-    meta = np.float32((np.float32(1.0) / np.maximum(ideal.max(), np.float32(1e-6))) * np.float32(448.0))
+    if meta is None:
+        meta = np.float32((np.float32(1.0) / np.maximum(ideal.max(), np.float32(1e-6))) * np.float32(448.0))
+    meta = np.float32(meta)
     s8 = e4m3_encode(np.minimum((ideal * meta).astype(np.float32), np.float32(448.0)))
     sfull = np.maximum((e4m3_decode(s8) / meta).astype(np.float32), np.float32(1e-6))
     codes = _round_fp4_weights((g / sfull).astype(np.float32)).reshape(N, K)

