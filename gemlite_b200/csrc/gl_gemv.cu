@@ -7,47 +7,42 @@
 //
 // The kernel is HBM-bound, so it is organised around the weight stream:
 //  * W_q is the reference's packed layout, int32 [K/e, N] row-major, e = 32/W_nbits values of
-//    one output column per word (gemlite/bitpack.py:36-60, gemlite/core.py:623-637).  Every warp
-//    owns a strip of 32 columns (128-byte rows) and runs its own TMA pipeline: boxes of R packed
-//    rows x 128 bytes land in a ring of S shared-memory stages (128-byte swizzle), all S issued
-//    before anything else happens in the kernel, and a stage is re-armed as soon as the warp has
-//    read it.  No register is spent on loads in flight and the weights never pass through L1.
-//  * Each lane reads 16 bytes (4 columns x 1 packed row) per iteration from the stage,
-//    conflict-free, unpacks fields two at a time with one shift + one LOP3 into fp16/bf16
-//    "magic number" pairs (BIAS+q) and feeds them straight to mma.sync m16n8k16 as the A
-//    operand (16 output columns x 16 k); the activations are the B operand (8 batch rows per
-//    MMA), so M = 1..8 costs one MMA per 256 weights and M <= 32 re-uses the same A fragments.
-//    The k order inside a packed word and the column order inside a strip are permuted
-//    identically on both sides, which a dot product does not see.
+//    one output column per word (gemlite/bitpack.py:36-60, gemlite/core.py:623-637).  Every lane
+//    issues 128-bit streaming loads of 4 adjacent columns (a warp instruction covers 4 packed rows x
+//    128 bytes); two batches of U loads per lane are in flight (register double buffer).
+//  * Fields are unpacked two at a time with one shift + one LOP3 into fp16/bf16 "magic number"
+//    pairs (BIAS+q) and fed straight to mma.sync m16n8k16 as the A operand (16 output columns x
+//    16 k); the activations are the B operand (8 batch rows per MMA), so M = 1..8 costs one MMA
+//    per 256 weights and M <= 32 re-uses the same A fragments.  The k order inside a packed word
+//    is permuted identically on both operands, which a dot product does not see.
 //  * Dequantisation is applied per group to the fp32 accumulators, not per weight:
 //        sum_k x_k*(q_k*s + z')  =  s * sum_k x_k*(BIAS+q_k)  +  (z' - BIAS*s) * sum_k x_k
 //    with the group sums of x computed once per CTA while x is staged in shared memory.
-//  * K is split over blockIdx.y.  Partial tiles go to an fp32 workspace; the last CTA to
-//    arrive for a column tile (arrival counter, no spinning) adds them in slice order, so the
-//    result is deterministic, then applies channel scales / bias and writes the output once.
-//  * Programmatic dependent launch: the weight prefetch runs before griddepcontrol.wait, so in a
-//    chain of layers it overlaps the tail of the previous kernel; activations, workspace and
-//    output are only touched after the wait.
+//  * K is split over blockIdx.y.  Up to 8 slices form a thread-block cluster: each CTA parks its fp32
+//    partial tile in shared memory and the ranks add disjoint column slices through distributed
+//    shared memory in rank order (deterministic, no global scratch).  More slices go through an fp32
+//    workspace: the last CTA to arrive for a column tile (arrival counter, no spinning) adds the
+//    partials in slice order.  Channel scales / bias are applied once, in the final sum.
+//  * Programmatic dependent launch: the first batch of weight loads and the scale / zero prefetch
+//    are issued before griddepcontrol.wait, so in a chain of layers they overlap the tail of the
+//    previous kernel; activations, workspace and output are only touched after the wait.
 #include "gl_tc_common.cuh"
 #include <stdlib.h>
 #include <string.h>
 
 namespace {
 
-constexpr int kStageRows = 16;                    // packed rows per TMA box (4 iterations)
-constexpr int kStageBytes = kStageRows * 128;     // 2 KB
-constexpr int kItersPerStage = kStageRows / 4;
 constexpr int kMaxTiles = 16384;                  // arrival counters at the head of the workspace
 constexpr int kStatusBytes = 256;                 // device status word after the counters
 
 struct GemvParams {
-  const void* x; const void* scales; const void* zeros; const void* bias;
+  const void* x; const int32_t* w; const void* scales; const void* zeros; const void* bias;
   void* out; float* partials; unsigned int* counters; int* status;
   int M, N, K;
   int T;            // iterations over K: one iteration = 4 packed rows = 4*e k-values
   int gi;           // iterations per quantisation group
   int splitK;
-  int stages;       // TMA ring depth per warp
+  int cluster;      // CTAs per thread-block cluster along K (1 = split-K through the global workspace)
   int W_group_mode, channel_scale_mode, zero_is_scalar;
   int out_dtype;
   int max_slice_iters, max_seg;
@@ -83,6 +78,13 @@ __device__ __forceinline__ void mma16816<__half>(float (&d)[4], uint32_t a0, uin
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ int4 ldg_stream(const int32_t* p) {
+  int4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.s32 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
 // load 4 consecutive meta values (scales / zeros of this lane's 4 columns) as fp32
 template <typename XT>
 __device__ __forceinline__ void load_meta4(const void* base, int64_t idx, float (&o)[4]) {
@@ -92,23 +94,19 @@ __device__ __forceinline__ void load_meta4(const void* base, int64_t idx, float 
 }
 
 // NB: bits per weight (4/2/1). XT: activation / scale dtype. MT: number of 8-row batch tiles (M <= 8*MT).
-template <int NB, typename XT, int MT>
-__global__ void __launch_bounds__(128) gl_gemv_stream_kernel(const __grid_constant__ CUtensorMap tmW, const GemvParams p) {
+// U: packed-row loads per lane per batch; two batches are in flight (register double buffer).
+template <int NB, typename XT, int MT, int U>
+__global__ void __launch_bounds__(128) gl_gemv_stream_kernel(const GemvParams p) {
   constexpr int E = 32 / NB;        // k-values per packed word
   constexpr int H = E / 8;          // 16-byte pieces of x per packed row
   constexpr int HALF = E / 2;       // field i is paired with field i + HALF
   constexpr uint32_t FMASK = ((1u << NB) - 1u) * 0x00010001u;
   using XTr = XTraits<XT>;
 
-  extern __shared__ unsigned char smem_dyn[];
-  unsigned char* smem_raw = smem_dyn + ((1024u - (gltc::smem_u32(smem_dyn) & 1023u)) & 1023u);   // swizzled TMA tiles need 1 KB alignment
-  __shared__ int s_abort;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ int s_last;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int r = lane >> 2, t = lane & 3;
-  // column chunk of this lane inside the 128-byte row: lanes of one quarter-warp (two values of r,
-  // four packed rows) must hit eight different 16-byte bank groups under the 128-byte swizzle
-  const int cr = ((r & 1) << 2) | (r >> 1);
 
   // K slice of this CTA, in iterations
   const int split = blockIdx.y;
@@ -117,38 +115,27 @@ __global__ void __launch_bounds__(128) gl_gemv_stream_kernel(const __grid_consta
   const int nit = it1 - it0;
   const int g0 = it0 / p.gi;                          // first group touched
   const int nseg = (it1 + p.gi - 1) / p.gi - g0;      // group segments in this slice
-  const int nst = (nit + kItersPerStage - 1) / kItersPerStage;
 
-  // shared: [warp][stage] weight tiles | barriers | xs | csum | xsum
-  const int S = p.stages;
-  unsigned char* wtiles = smem_raw + (size_t)warp * S * kStageBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)nwarps * S * kStageBytes) + warp * S;
-  unsigned char* after = smem_raw + (size_t)nwarps * S * kStageBytes + (size_t)nwarps * S * sizeof(uint64_t);
-  after = reinterpret_cast<unsigned char*>(((uintptr_t)after + 15) & ~(uintptr_t)15);
-  uint4* xs = reinterpret_cast<uint4*>(after);                    // [iteration][piece][batch row][quad lane] 16-byte units
+  // shared: xs | xsum | scales | zeros   (xs is re-used for the partial tile of the cluster reduction)
+  uint4* xs = reinterpret_cast<uint4*>(smem_raw);                 // [iteration][piece][batch row][quad lane] 16-byte units
   const int xs_units = p.max_slice_iters * H * p.M * 4;
-  float* xsum = reinterpret_cast<float*>(xs + xs_units);          // [segment][8*MT]
   const int cta_cols = nwarps * 32;
+  const int part_units = (p.M * cta_cols + 3) / 4;                // fp32 partial tile, in 16-byte units
+  float* xsum = reinterpret_cast<float*>(xs + max(xs_units, part_units));   // [segment][8*MT]
   uint16_t* ms = reinterpret_cast<uint16_t*>(xsum + (size_t)p.max_seg * 8 * MT);   // scales [segment][cta_cols]
   uint16_t* mz = ms + (size_t)p.max_seg * cta_cols;                                // zeros  [segment][cta_cols]
 
-  const int wcol0 = (blockIdx.x * nwarps + warp) * 32;             // first column of this warp's strip
-  const bool strip_ok = wcol0 < p.N;
-  if (threadIdx.x == 0) s_abort = 0;
-  if (lane == 0) {
-    if (warp == 0) gltc::prefetch_tmap(&tmW);
-    for (int s = 0; s < S; ++s) gltc::mbar_init(bars + s, 1);
-    gltc::fence_barrier_init();
+  // ---- before the dependency wait: everything that only touches weights ---------------------------
+  const int n0 = (blockIdx.x * nwarps + warp) * 32 + 4 * r;      // this lane's first column
+  const bool ncol_ok = n0 < p.N;
+  const int32_t* wp = p.w + (size_t)(it0 * 4 + t) * p.N + n0;
+  const size_t wstep = (size_t)4 * p.N;
+  int4 cur[U], nxt[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    cur[u] = make_int4(0, 0, 0, 0);
+    if (ncol_ok && u < nit) cur[u] = ldg_stream(wp + (size_t)u * wstep);
   }
-  __syncwarp();
-  // ---- prefetch: fill the ring before anything else ----------------------------------------------
-  if (lane == 0 && strip_ok) {
-    for (int s = 0; s < S && s < nst; ++s) {
-      gltc::mbar_expect_tx(bars + s, kStageBytes);
-      gltc::tma_load_2d(wtiles + s * kStageBytes, &tmW, bars + s, wcol0, (it0 + s * kItersPerStage) * 4);
-    }
-  }
-  // group scales / zeros of this CTA's columns and K slice: constants, fetched before the dependency wait
   {
     const bool need_s = p.W_group_mode >= 2;
     const bool need_z = (p.W_group_mode == 1 || p.W_group_mode >= 3) && !p.zero_is_scalar;
@@ -171,7 +158,6 @@ __global__ void __launch_bounds__(128) gl_gemv_stream_kernel(const __grid_consta
   }
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  __syncthreads();   // s_abort visible
 
   // ---- stage x in fragment order and sum it per quantisation group ------------------------------------
   // One (segment, batch row) pair is handled by a group of GL lanes: each lane permutes 16-byte units of x
@@ -228,16 +214,15 @@ __global__ void __launch_bounds__(128) gl_gemv_stream_kernel(const __grid_consta
   __syncthreads();
 
   // ---- main loop ----------------------------------------------------------------------------
-  const int n0 = wcol0 + 4 * cr;                                  // this lane's first column
-  const bool ncol_ok = n0 < p.N;
-
-  float acc[2][MT][4], outv[2][MT][4];
+  // acc[q][a][mt]: separate accumulators for the two MMAs of a packed row (q) so that consecutive MMAs do not
+  // depend on each other; they are added when a group is flushed
+  float acc[2][2][MT][4], outv[2][MT][4];
 #pragma unroll
   for (int a = 0; a < 2; ++a)
 #pragma unroll
     for (int b = 0; b < MT; ++b)
 #pragma unroll
-      for (int c = 0; c < 4; ++c) { acc[a][b][c] = 0.f; outv[a][b][c] = 0.f; }
+      for (int c = 0; c < 4; ++c) { acc[0][a][b][c] = 0.f; acc[1][a][b][c] = 0.f; outv[a][b][c] = 0.f; }
 
   int seg = 0;
   int seg_end = min((g0 + 1) * p.gi, it1) - it0;     // local iteration where the segment ends
@@ -245,7 +230,7 @@ __global__ void __launch_bounds__(128) gl_gemv_stream_kernel(const __grid_consta
   auto flush = [&](int sgi) {
     // out += alpha[col] * acc + beta[col] * xsum[m]
     float al[4], be[4];
-    const int mcol = warp * 32 + 4 * cr;                           // this lane's columns inside the CTA tile
+    const int mcol = warp * 32 + 4 * r;                            // this lane's columns inside the CTA tile
     if (p.W_group_mode >= 2) {
       const uint2 v = *reinterpret_cast<const uint2*>(ms + sgi * cta_cols + mcol);
       al[0] = XTr::to_float((uint16_t)(v.x & 0xffffu)); al[1] = XTr::to_float((uint16_t)(v.x >> 16));
@@ -272,72 +257,107 @@ __global__ void __launch_bounds__(128) gl_gemv_stream_kernel(const __grid_consta
       const float xs0 = xsum[sgi * 8 * MT + mt * 8 + 2 * t], xs1 = xsum[sgi * 8 * MT + mt * 8 + 2 * t + 1];
 #pragma unroll
       for (int a = 0; a < 2; ++a) {
-        outv[a][mt][0] += al[2 * a] * acc[a][mt][0] + be[2 * a] * xs0;
-        outv[a][mt][1] += al[2 * a] * acc[a][mt][1] + be[2 * a] * xs1;
-        outv[a][mt][2] += al[2 * a + 1] * acc[a][mt][2] + be[2 * a + 1] * xs0;
-        outv[a][mt][3] += al[2 * a + 1] * acc[a][mt][3] + be[2 * a + 1] * xs1;
-        acc[a][mt][0] = acc[a][mt][1] = acc[a][mt][2] = acc[a][mt][3] = 0.f;
+        outv[a][mt][0] += al[2 * a] * (acc[0][a][mt][0] + acc[1][a][mt][0]) + be[2 * a] * xs0;
+        outv[a][mt][1] += al[2 * a] * (acc[0][a][mt][1] + acc[1][a][mt][1]) + be[2 * a] * xs1;
+        outv[a][mt][2] += al[2 * a + 1] * (acc[0][a][mt][2] + acc[1][a][mt][2]) + be[2 * a + 1] * xs0;
+        outv[a][mt][3] += al[2 * a + 1] * (acc[0][a][mt][3] + acc[1][a][mt][3]) + be[2 * a + 1] * xs1;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) { acc[0][a][mt][c] = 0.f; acc[1][a][mt][c] = 0.f; }
       }
     }
   };
 
-  bool aborted = false;
-  if (strip_ok) {
-    for (int st = 0; st < nst; ++st) {
-      const int s = st % S;
-      if (!gltc::mbar_wait(bars + s, (uint32_t)((st / S) & 1), &s_abort, p.status, 1)) { aborted = true; break; }
-      const unsigned char* tile = wtiles + s * kStageBytes;
+  for (int itb = 0; itb < nit; itb += U) {
 #pragma unroll
-      for (int i = 0; i < kItersPerStage; ++i) {
-        const int it = st * kItersPerStage + i;
-        if (it < nit) {
-          const int row = 4 * i + t;
-          const uint4 wv = *reinterpret_cast<const uint4*>(tile + row * 128 + ((cr ^ (row & 7)) << 4));
-          const uint32_t w[4] = {wv.x, wv.y, wv.z, wv.w};
+    for (int u = 0; u < U; ++u) {
+      nxt[u] = make_int4(0, 0, 0, 0);
+      if (ncol_ok && itb + U + u < nit) nxt[u] = ldg_stream(wp + (size_t)(itb + U + u) * wstep);
+    }
 #pragma unroll
-          for (int hh = 0; hh < H; ++hh) {
-            uint4 xb[MT];
+    for (int u = 0; u < U; ++u) {
+      const int it = itb + u;
+      if (it < nit) {
+        const uint32_t w[4] = {(uint32_t)cur[u].x, (uint32_t)cur[u].y, (uint32_t)cur[u].z, (uint32_t)cur[u].w};
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {      // batch rows >= M contribute zeros (their outputs are never stored)
-              const int m = mt * 8 + r;
-              xb[mt] = (m < p.M) ? xs[(((it * H + hh) * p.M + m) << 2) + t] : make_uint4(0u, 0u, 0u, 0u);
-            }
+        for (int hh = 0; hh < H; ++hh) {
+          uint4 xb[MT];
 #pragma unroll
-            for (int q = 0; q < 2; ++q) {
-              const int pp = 2 * hh + q;               // MMA index inside the packed row
-              uint32_t f0[4], f1[4];
-#pragma unroll
-              for (int c = 0; c < 4; ++c) {
-                f0[c] = ((w[c] >> (NB * (2 * pp))) & FMASK) | XTr::MAGIC;       // fields 2pp, 2pp+HALF
-                f1[c] = ((w[c] >> (NB * (2 * pp + 1))) & FMASK) | XTr::MAGIC;   // fields 2pp+1, 2pp+1+HALF
-              }
-#pragma unroll
-              for (int mt = 0; mt < MT; ++mt) {
-                const uint32_t b0 = q ? xb[mt].z : xb[mt].x, b1 = q ? xb[mt].w : xb[mt].y;
-                mma16816<XT>(acc[0][mt], f0[0], f0[1], f1[0], f1[1], b0, b1);
-                mma16816<XT>(acc[1][mt], f0[2], f0[3], f1[2], f1[3], b0, b1);
-              }
-            }
+          for (int mt = 0; mt < MT; ++mt) {      // batch rows >= M contribute zeros (their outputs are never stored)
+            const int m = mt * 8 + r;
+            xb[mt] = (m < p.M) ? xs[(((it * H + hh) * p.M + m) << 2) + t] : make_uint4(0u, 0u, 0u, 0u);
           }
-          if (it + 1 == seg_end) {
-            flush(seg);
-            ++seg;
-            seg_end = min((g0 + seg + 1) * p.gi, it1) - it0;
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            const int pp = 2 * hh + q;               // MMA index inside the packed row
+            uint32_t f0[4], f1[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              f0[c] = ((w[c] >> (NB * (2 * pp))) & FMASK) | XTr::MAGIC;       // fields 2pp, 2pp+HALF
+              f1[c] = ((w[c] >> (NB * (2 * pp + 1))) & FMASK) | XTr::MAGIC;   // fields 2pp+1, 2pp+1+HALF
+            }
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+              const uint32_t b0 = q ? xb[mt].z : xb[mt].x, b1 = q ? xb[mt].w : xb[mt].y;
+              mma16816<XT>(acc[q][0][mt], f0[0], f0[1], f1[0], f1[1], b0, b1);
+              mma16816<XT>(acc[q][1][mt], f0[2], f0[3], f1[2], f1[3], b0, b1);
+            }
           }
         }
-      }
-      __syncwarp();
-      if (lane == 0 && st + S < nst) {               // the stage has been read by every lane: re-arm it
-        gltc::mbar_expect_tx(bars + s, kStageBytes);
-        gltc::tma_load_2d(wtiles + s * kStageBytes, &tmW, bars + s, wcol0, (it0 + (st + S) * kItersPerStage) * 4);
+        if (it + 1 == seg_end) {
+          flush(seg);
+          ++seg;
+          seg_end = min((g0 + seg + 1) * p.gi, it1) - it0;
+        }
       }
     }
+#pragma unroll
+    for (int u = 0; u < U; ++u) cur[u] = nxt[u];
   }
-  (void)aborted;
 
   // ---- epilogue -------------------------------------------------------------------------------
   // lane owns columns n0..n0+3 and batch rows m = mt*8 + 2t, 2t+1:
   //   outv[a][mt][0] = (col 2a, m=2t)  [1] = (col 2a, 2t+1)  [2] = (col 2a+1, 2t)  [3] = (col 2a+1, 2t+1)
+  if (p.cluster > 1) {
+    // Split-K inside a thread-block cluster: every CTA parks its fp32 partial tile in its own shared memory,
+    // then CTA `rank` adds a slice of the columns over all ranks (fixed order) through distributed shared memory.
+    float* part = reinterpret_cast<float*>(xs);
+    __syncthreads();                                 // xs is dead
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int m = mt * 8 + 2 * t + j;
+        if (m < p.M)
+          *reinterpret_cast<float4*>(part + m * cta_cols + warp * 32 + 4 * r) =
+              make_float4(outv[0][mt][j], outv[0][mt][2 + j], outv[1][mt][j], outv[1][mt][2 + j]);
+      }
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const int slice = cta_cols / p.cluster;          // columns reduced by this CTA
+    const uint32_t part_s = gltc::smem_u32(part);
+    for (int i = threadIdx.x; i < p.M * slice; i += blockDim.x) {
+      const int m = i / slice, c = rank * slice + i % slice;
+      const int n = blockIdx.x * cta_cols + c;
+      float v = 0.f;
+      for (int q = 0; q < p.cluster; ++q) {
+        uint32_t ra;
+        float pv;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(part_s + (uint32_t)(m * cta_cols + c) * 4u), "r"(q));
+        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pv) : "r"(ra) : "memory");
+        v += pv;
+      }
+      if (n < p.N) {
+        if (p.channel_scale_mode == 1) v *= XTr::to_float(reinterpret_cast<const uint16_t*>(p.scales)[n]);
+        if (p.bias != nullptr) v += gl_load_as_float(p.bias, n, p.out_dtype);
+        gl_store_out(p.out, (int64_t)m * p.N + n, v, p.out_dtype);
+      }
+    }
+    // nobody may leave while a peer still reads its shared memory
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    return;
+  }
+
   const bool multi = p.splitK > 1;
   if (multi) {
     if (ncol_ok) {
@@ -406,7 +426,7 @@ __global__ void __launch_bounds__(128) gl_gemv_stream_kernel(const __grid_consta
     }
 }
 
-struct GemvPlan { int warps_n, splitK, MT, stages, slice_iters, max_seg, tiles; size_t smem; };
+struct GemvPlan { int warps_n, splitK, cluster, MT, slice_iters, max_seg, tiles; size_t smem; };
 
 // Tile parameters: built-in heuristic, overridden by a config-cache entry for the GEMV_REVSPLITK /
 // GEMV_SPLITK / GEMV family under the reference's signature "(Mb, N, K, group_size, e, type_id)" with
@@ -428,8 +448,7 @@ static void plan_for(const gl_matmul_args* a, GemvPlan* pl) {
   pl->MT = a->M <= 8 ? 1 : (a->M <= 16 ? 2 : 4);
   const int H = e / 8;
   int warps_n = a->N <= 32 ? 1 : 2;
-  int stages = 6;
-  int split_req = 0;
+  int split_req = 0, cluster_req = -1;
   {
     const int idt = (a->input_dtype == GL_BF16) ? GL_FP16 : a->input_dtype;
     char sig[128];
@@ -440,66 +459,74 @@ static void plan_for(const gl_matmul_args* a, GemvPlan* pl) {
       if (js) {
         split_req = json_int(js, "split_k", 0);
         warps_n = json_int(js, "warps_n", warps_n);
-        stages = json_int(js, "stages", stages);
+        cluster_req = json_int(js, "cluster", -1);
         break;
       }
     }
   }
   if (warps_n < 1) warps_n = 1;
   if (warps_n > 4) warps_n = 4;
-  if (stages < 2) stages = 2;
-  if (stages > 16) stages = 16;
   pl->warps_n = warps_n;
-  pl->stages = stages;
   pl->tiles = (int)gl_cdiv(a->N, 32 * warps_n);
-  // shared memory per iteration of the slice: x fragments + per-unit sums
-  const int per_iter_bytes = H * a->M * 4 * 16;
-  const int ring_bytes = warps_n * stages * (kStageBytes + 8);
-  const int max_iters_smem = (100 * 1024 - ring_bytes) / per_iter_bytes;
-  const int sms = gl_num_sms();
-  int want = split_req > 0 ? split_req : (int)gl_cdiv((int64_t)sms * 8, pl->tiles);
+  const int per_iter_bytes = H * a->M * 4 * 16;       // x fragments per iteration of the slice
+  const int max_iters_smem = (96 * 1024) / per_iter_bytes;
   int min_split = (int)gl_cdiv(T, max_iters_smem > 1 ? max_iters_smem : 1);
-  int splitK = want > min_split ? want : min_split;
-  if (splitK > T / 2) splitK = T / 2 > 0 ? T / 2 : 1;
+  int splitK;
+  if (split_req > 0) splitK = split_req;
+  else {
+    // default: 8 slices (one thread-block cluster per column tile) when the machine is filled that way
+    splitK = 8;
+    while (splitK > 1 && (T / splitK < 4)) splitK >>= 1;
+    const int sms = gl_num_sms();
+    if ((int64_t)pl->tiles * splitK < (int64_t)sms * 2) splitK = (int)gl_cdiv((int64_t)sms * 4, pl->tiles);
+  }
   if (splitK < min_split) splitK = min_split;
+  if (splitK > T) splitK = T > 0 ? T : 1;
   if (splitK < 1) splitK = 1;
-  if (split_req <= 0 && splitK > 64) splitK = 64 > min_split ? 64 : min_split;
   pl->splitK = splitK;
+  const bool pow2 = (splitK & (splitK - 1)) == 0;
+  pl->cluster = (cluster_req != 0 && pow2 && splitK <= 8 && splitK > 1 && (32 * warps_n) % splitK == 0) ? splitK : 1;
   pl->slice_iters = (int)gl_cdiv(T, splitK) + 1;
   const int gi = a->group_size / (4 * e);
   pl->max_seg = pl->slice_iters / (gi > 0 ? gi : 1) + 2;
-  pl->smem = 1024 + (size_t)ring_bytes + 16 + (size_t)pl->slice_iters * per_iter_bytes +
-             (size_t)pl->max_seg * (8 * pl->MT * 4 + 2 * warps_n * 32 * 2) + 16;
+  const size_t xs_bytes = (size_t)pl->slice_iters * per_iter_bytes;
+  const size_t part_bytes = ((size_t)a->M * 32 * warps_n * 4 + 15) / 16 * 16;
+  pl->smem = (xs_bytes > part_bytes ? xs_bytes : part_bytes) + (size_t)pl->max_seg * (8 * pl->MT * 4 + 2 * warps_n * 32 * 2) + 32;
 }
 
 template <int NB, typename XT, int MT>
-static int launch_t(const CUtensorMap& tm, const GemvParams& p, dim3 grid, dim3 block, size_t smem, cudaStream_t st) {
-  auto kern = gl_gemv_stream_kernel<NB, XT, MT>;
+static int launch_t(const GemvParams& p, dim3 grid, dim3 block, size_t smem, cudaStream_t st) {
+  auto kern = gl_gemv_stream_kernel<NB, XT, MT, 8>;
   if (smem > 48 * 1024) GL_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr; cfg.numAttrs = 1;
-  GL_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, tm, p));
+  int na = 1;
+  if (p.cluster > 1) {
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 1; attr[1].val.clusterDim.y = (unsigned)p.cluster; attr[1].val.clusterDim.z = 1;
+    na = 2;
+  }
+  cfg.attrs = attr; cfg.numAttrs = na;
+  GL_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, p));
   return GL_OK;
 }
 template <int NB, typename XT>
-static int launch_mt(int MT, const CUtensorMap& tm, const GemvParams& p, dim3 grid, dim3 block, size_t smem, cudaStream_t st) {
-  if (MT == 1) return launch_t<NB, XT, 1>(tm, p, grid, block, smem, st);
-  if (MT == 2) return launch_t<NB, XT, 2>(tm, p, grid, block, smem, st);
-  return launch_t<NB, XT, 4>(tm, p, grid, block, smem, st);
+static int launch_mt(int MT, const GemvParams& p, dim3 grid, dim3 block, size_t smem, cudaStream_t st) {
+  if (MT == 1) return launch_t<NB, XT, 1>(p, grid, block, smem, st);
+  if (MT == 2) return launch_t<NB, XT, 2>(p, grid, block, smem, st);
+  return launch_t<NB, XT, 4>(p, grid, block, smem, st);
 }
 template <typename XT>
-static int launch_nb(int NB, int MT, const CUtensorMap& tm, const GemvParams& p, dim3 grid, dim3 block, size_t smem, cudaStream_t st) {
-  if (NB == 4) return launch_mt<4, XT>(MT, tm, p, grid, block, smem, st);
-  if (NB == 2) return launch_mt<2, XT>(MT, tm, p, grid, block, smem, st);
-  return launch_mt<1, XT>(MT, tm, p, grid, block, smem, st);
+static int launch_nb(int NB, int MT, const GemvParams& p, dim3 grid, dim3 block, size_t smem, cudaStream_t st) {
+  if (NB == 4) return launch_mt<4, XT>(MT, p, grid, block, smem, st);
+  if (NB == 2) return launch_mt<2, XT>(MT, p, grid, block, smem, st);
+  return launch_mt<1, XT>(MT, p, grid, block, smem, st);
 }
 
 }  // namespace
-
 int gl_gemv_stream_supported(const gl_matmul_args* a) {
   const int e = a->elements_per_sample;
   if (a->M < 1 || a->M > 32) return 0;
@@ -538,7 +565,7 @@ uint64_t gl_matmul_counter_bytes(void) { return (uint64_t)kMaxTiles * sizeof(uns
 uint64_t gl_gemv_stream_workspace(const gl_matmul_args* a) {
   GemvPlan pl;
   plan_for(a, &pl);
-  return gl_matmul_counter_bytes() + (pl.splitK > 1 ? (uint64_t)pl.splitK * a->M * a->N * sizeof(float) : 0);
+  return gl_matmul_counter_bytes() + ((pl.splitK > 1 && pl.cluster == 1) ? (uint64_t)pl.splitK * a->M * a->N * sizeof(float) : 0);
 }
 
 int gl_gemv_stream_launch(const gl_matmul_args* a, cudaStream_t st) {
@@ -550,10 +577,8 @@ int gl_gemv_stream_launch(const gl_matmul_args* a, cudaStream_t st) {
             (unsigned long long)need, (unsigned long long)a->workspace_bytes);
   if ((uintptr_t)a->workspace & 15) GL_FAIL(GL_E_INVALID, "gl_matmul: workspace must be 16-byte aligned");
   const int e = a->elements_per_sample;
-  CUtensorMap tm;
-  if (int rc = gl_make_tmap_2d(&tm, a->w, 3, (uint64_t)a->N, (uint64_t)(a->K / e), (uint64_t)a->N * 4, 32, kStageRows, true)) return rc;
   GemvParams p;
-  p.x = a->x; p.scales = a->scales; p.zeros = a->zeros; p.bias = a->bias;
+  p.x = a->x; p.w = reinterpret_cast<const int32_t*>(a->w); p.scales = a->scales; p.zeros = a->zeros; p.bias = a->bias;
   p.out = a->out;
   p.counters = reinterpret_cast<unsigned int*>(a->workspace);
   p.status = reinterpret_cast<int*>(reinterpret_cast<char*>(a->workspace) + (size_t)kMaxTiles * sizeof(unsigned int));
@@ -562,12 +587,12 @@ int gl_gemv_stream_launch(const gl_matmul_args* a, cudaStream_t st) {
   p.T = a->K / (4 * e);
   p.gi = a->group_size / (4 * e);
   p.splitK = pl.splitK;
-  p.stages = pl.stages;
+  p.cluster = pl.cluster;
   p.W_group_mode = a->W_group_mode; p.channel_scale_mode = a->channel_scale_mode; p.zero_is_scalar = a->zero_is_scalar;
   p.out_dtype = a->out_dtype;
   p.max_slice_iters = pl.slice_iters;
   p.max_seg = pl.max_seg;
   dim3 grid(pl.tiles, pl.splitK), block(32 * pl.warps_n);
-  if (a->x_dtype == GL_BF16) return launch_nb<__nv_bfloat16>(a->W_nbits, pl.MT, tm, p, grid, block, pl.smem, st);
-  return launch_nb<__half>(a->W_nbits, pl.MT, tm, p, grid, block, pl.smem, st);
+  if (a->x_dtype == GL_BF16) return launch_nb<__nv_bfloat16>(a->W_nbits, pl.MT, p, grid, block, pl.smem, st);
+  return launch_nb<__half>(a->W_nbits, pl.MT, p, grid, block, pl.smem, st);
 }

@@ -1,0 +1,102 @@
+"""CPU: pins the oracle against outputs of the reference's own Triton kernels and torch quantisers captured on
+a B200 (tests/golden/triton_golden.npz, made by make_golden_triton.py + reduce_triton_golden.py).
+
+Matmul outputs of the reference carry its own rounding (bf16 dequantisation, bf16 atomics), so they are compared
+with the tolerance the operator is specified with: relative Frobenius 1e-2 (fp16 / bf16), 3e-2 (FP8 / FP4).
+Quantiser outputs are integers / bytes: equal except where the reference's approximate fp32 division
+(Triton's default) lands on the other side of a rounding boundary, bounded here at 0.2 % of the elements."""
+import numpy as np
+import torch
+
+from oracle import oracle
+from tests import golden_inputs as gi
+from tests.util import rel_fro
+
+
+def _mismatch(a, b):
+    return float((np.asarray(a) != np.asarray(b)).mean())
+
+
+def test_a16wn_oracle_matches_reference_kernels():
+    gold = gi.load()
+    checked = 0
+    for seed, N, K, nbits, gs, dtype, Ms in gi.A16_CASES:
+        for M in Ms:
+            x, W_q, s, z, _ = gi.a16_inputs(seed, N, K, nbits, gs, dtype, M)
+            zp = (-z.float() * s.float()).to(dtype)                       # pack(): fma mode
+            y = oracle.matmul_int(x, W_q.t().long(), s.view(N, -1).t(), zp.view(N, -1).t(), 4, 0, gs, x_dtype=dtype).numpy()
+            for fam in ("GEMV", "GEMV_REVSPLITK", "GEMV_SPLITK", "GEMM_SPLITK", "GEMM"):
+                key = "a16_s%d_M%d_%s" % (seed, M, fam)
+                if key in gold.files:
+                    ref = gold[key]
+                    assert rel_fro(y[: ref.shape[0]], ref) < 1e-2, (key, rel_fro(y[: ref.shape[0]], ref))
+                    checked += 1
+    assert checked >= 30
+
+
+def test_activation_quantisers_match_reference_kernels():
+    gold = gi.load()
+    xs, _ = gi.quant_inputs(gold)
+    for M, K, x in xs:
+        xf = x.float().numpy()
+        tag = "xq_M%d_K%d_" % (M, K)
+        q, s = oracle.scale_activations_per_token(xf, "fp8")
+        assert np.allclose(s, gold[tag + "fp8_s"], rtol=3e-7, atol=0) and _mismatch(q, gold[tag + "fp8_q"]) < 2e-3
+        q, s = oracle.scale_activations_per_token(xf, "int8")
+        assert np.allclose(s, gold[tag + "int8_s"], rtol=3e-7, atol=0) and _mismatch(q, gold[tag + "int8_q"]) < 2e-3
+        q, s = oracle.scale_activations_mxfp4(xf)
+        assert np.array_equal(s, gold[tag + "mxfp4_s"]) and np.array_equal(q, gold[tag + "mxfp4_q"])
+        q, s = oracle.scale_activations_mxfp8(xf)
+        assert np.array_equal(s, gold[tag + "mxfp8_s"]) and _mismatch(q, gold[tag + "mxfp8_q"]) < 2e-3
+        q, s, meta = oracle.scale_activations_nvfp4(xf)
+        assert abs(float(meta) / float(gold[tag + "nvfp4_meta"][0]) - 1) < 1e-6
+        assert _mismatch(s, gold[tag + "nvfp4_s"]) < 2e-3 and _mismatch(q, gold[tag + "nvfp4_q"]) < 2e-3
+
+
+def test_weight_quantisers_match_reference_torch():
+    gold = gi.load()
+    _, W = gi.quant_inputs(gold)
+    codes, sc = oracle.quantize_mxfp4_weights(W.float().numpy())
+    assert np.array_equal(sc[:64], gold["wq_mxfp4_scales"]) and _mismatch(codes[:64], gold["wq_mxfp4_codes"]) < 2e-3
+    meta = gold["wq_nvfp4_meta"][0]
+    codes, sc, _ = oracle.quantize_nvfp4_weights(W.float().numpy(), meta=meta)
+    assert abs(float(oracle.quantize_nvfp4_weights(W.float().numpy())[2]) / float(meta) - 1) < 1e-6
+    assert _mismatch(sc[:64], gold["wq_nvfp4_scales"]) < 2e-3 and _mismatch(codes[:64], gold["wq_nvfp4_codes"]) < 2e-3
+
+
+def test_a8w8_and_mxfp4_oracle_match_reference_kernels():
+    gold = gi.load()
+    # FP8 / INT8 dynamic: per-channel weight quantisation (helper.py:619-686) + per-token activations
+    for name in ("fp8", "int8"):
+        W, xs = gi.lin_inputs(gold, name)
+        qmax = 448.0 if name == "fp8" else 127.0
+        Wf = W.float()
+        sw = (Wf.abs().amax(1, keepdim=True) / qmax).clamp_(min=1e-6)
+        Wq = (Wf / sw).clamp_(-qmax - (0 if name == "fp8" else 1), qmax)
+        Wd = Wq.to(torch.float8_e4m3fn).float().double().numpy() if name == "fp8" else Wq.round().double().numpy()
+        for M, x in xs.items():
+            xq, sx = oracle.scale_activations_per_token(x.float().numpy(), name)
+            Xd = oracle.e4m3_decode(xq).astype(np.float64) if name == "fp8" else xq.astype(np.float64)
+            y = (Xd @ Wd.T) * sx.astype(np.float64) * sw.double().numpy().reshape(1, -1)
+            for fam in ("GEMV_SPLITK", "GEMM_SPLITK", "GEMM"):
+                key = "lin_%s_M%d_%s" % (name, M, fam)
+                if key in gold.files:
+                    ref = gold[key]
+                    assert rel_fro(y[: ref.shape[0]], ref) < 3e-2, (key, rel_fro(y[: ref.shape[0]], ref))
+    # MXFP4 x MXFP4
+    W, xs = gi.lin_inputs(gold, "mxfp4")
+    codes, sw = oracle.quantize_mxfp4_weights(W.float().numpy())
+    wq = oracle.pack_fp4_codes(codes)
+    n = 0
+    for M, x in xs.items():
+        xq, sx = oracle.scale_activations_mxfp4(x.float().numpy())
+        y = oracle.matmul_mx(xq, sx, wq, sw, 32)
+        for fam in ("GEMM_SPLITK", "GEMM"):
+            key = "lin_mxfp4_M%d_%s" % (M, fam)
+            if key in gold.files:
+                ref = gold[key]
+                assert rel_fro(y[: ref.shape[0]], ref) < 3e-2, (key, rel_fro(y[: ref.shape[0]], ref))
+                n += 1
+    assert n >= 4
+    # NVFP4: the reference's kernels do not compile with Triton 3.6 on sm_100 (recorded in the fixture)
+    assert any("nvfp4" in str(e) for e in gold["reference_errors"])
