@@ -167,26 +167,16 @@ def _workspace(device, nbytes):
     return ws
 
 
-_SCALE_ATOMS = {}
-
-
-def _scale_atoms(scales):
-    """Weight scales of an MX / NV layer as 128x4 scale atoms (the reference's 5-D pre-shuffle,
-    gemlite/core.py:748-752), derived once per layer and kept beside the stored 2-D scales.
-    None when the shape does not tile (N % 128 or (K/group) % 4) or the general kernel is forced."""
-    if _KERNEL_OVERRIDE == 1 or scales is None or scales.dim() != 2:
+def _make_scale_atoms(scales):
+    """MX / NV weight scales [N, G] as 128x4 scale atoms (the reference's 5-D pre-shuffle,
+    gemlite/core.py:748-752): [N/128, G/4, 32, 4, 4] bytes.  None when the shape does not tile."""
+    if scales is None or scales.dim() != 2:
         return None
     N, G = scales.shape
     if N % 128 != 0 or G % 4 != 0:
         return None
-    key = (scales.data_ptr(), N, G, scales.device.index)
-    hit = _SCALE_ATOMS.get(key)
-    if hit is None or hit[1] != scales._version:
-        s2d = scales.view(torch.uint8) if scales.dtype != torch.uint8 else scales
-        atoms = s2d.contiguous().view(N // 128, 4, 32, G // 4, 4).permute(0, 3, 2, 1, 4).contiguous()
-        hit = (atoms, scales._version)
-        _SCALE_ATOMS[key] = hit
-    return hit[0]
+    s2d = scales.view(torch.uint8) if scales.dtype != torch.uint8 else scales
+    return s2d.contiguous().view(N // 128, 4, 32, G // 4, 4).permute(0, 3, 2, 1, 4).contiguous()
 
 
 def _fill_args(x2d, bias, W_q, scales, zeros, scales_x, meta_scale, out, meta_args, matmul_type, w_atoms=None, sx_layout=0):
@@ -254,7 +244,11 @@ def forward_functional(
     channel_scale_mode = meta_args[9]
 
     scales_x, meta_scale = None, None
-    w_atoms = _scale_atoms(scales) if (channel_scale_mode == 4 and input_dtype in (DType.MXFP4, DType.NVFP4)) else None
+    # tensor_args[4], when present, is the layer's derived copy of the weight scales as 128x4 scale atoms
+    w_atoms = None
+    if (len(tensor_args) > 4 and _KERNEL_OVERRIDE != 1 and channel_scale_mode == 4
+            and input_dtype in (DType.MXFP4, DType.NVFP4) and tensor_args[4].numel() > 0):
+        w_atoms = tensor_args[4]
     sx_layout = 0 if w_atoms is None else 1
     if bool(meta_args[0]) and enable_activation_scaling(x.numel() // x.shape[-1]):
         if input_dtype in FP8_INT8_DTYPES and channel_scale_mode == 5:
@@ -361,6 +355,7 @@ class GemLiteLinear(torch.nn.Module):
         self.__dict__.pop(name, None)
 
     def _clear_pack_slots(self):
+        self.__dict__.pop("_atoms_cache", None)
         for name in self._PACK_MUTATED_NAMES:
             self._clear_slot(name)
 
@@ -402,6 +397,7 @@ class GemLiteLinear(torch.nn.Module):
             _, n128, g4, _, _ = scales.shape
             scales = scales.reshape(n128, g4, 32, 4, 4).permute(0, 3, 2, 1, 4).reshape(n128 * 128, g4 * 4)
         dev = W_q.device
+        self.__dict__.pop("_atoms_cache", None)
         self._promote_to_parameter("W_q", W_q)
         if bias is not None:
             self._promote_to_parameter("bias", bias)
@@ -552,7 +548,23 @@ class GemLiteLinear(torch.nn.Module):
         meta_scale = self.meta_scale
         if not isinstance(meta_scale, torch.Tensor):
             meta_scale = torch.tensor(meta_scale, dtype=torch.float32, device=self.W_q.device)
-        return [self.W_q, self.scales, self.zeros, meta_scale]
+        args = [self.W_q, self.scales, self.zeros, meta_scale]
+        if self.channel_scale_mode == 4 and self.input_dtype in (DType.MXFP4, DType.NVFP4):
+            atoms = self._scale_atoms()
+            if atoms is not None:
+                args.append(atoms)
+        return args
+
+    def _scale_atoms(self):
+        """Derived, non-serialised copy of the MX / NV weight scales in the layout the block-scaled tensor-core
+        kernel reads; rebuilt when the stored scales change."""
+        sc = self.scales
+        key = (sc.data_ptr(), sc._version, tuple(sc.shape), tuple(sc.stride()))
+        cached = self.__dict__.get("_atoms_cache")
+        if cached is None or cached[0] != key:
+            cached = (key, _make_scale_atoms(sc))
+            self.__dict__["_atoms_cache"] = cached
+        return cached[1]
 
     def get_meta_args(self):
         return [int(self.scaled_activations), self.W_nbits, self.group_size, self.unpack_mask, self.elements_per_sample,

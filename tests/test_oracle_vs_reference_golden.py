@@ -29,7 +29,16 @@ def test_a16wn_oracle_matches_reference_kernels():
                 key = "a16_s%d_M%d_%s" % (seed, M, fam)
                 if key in gold.files:
                     ref = gold[key]
-                    assert rel_fro(y[: ref.shape[0]], ref) < 1e-2, (key, rel_fro(y[: ref.shape[0]], ref))
+                    if fam == "GEMV_SPLITK" and gs < 128:
+                        # With autotune off the reference's gemv_splitK kernel uses one K block wider than a group of
+                        # 64 and returns values 75-85 % away from its own GEMM family on these cases (it is only
+                        # auto-dispatched for 8-bit weights, core.py:163-168); not a usable pin.
+                        assert rel_fro(ref, gold["a16_s%d_M%d_GEMM" % (seed, M)]) > 0.5
+                        continue
+                    # the reference's GEMV families add output-dtype partial sums with atomics
+                    # (gemv_revsplitK_kernels.py:439-443): their own deviation from fp64 reaches 1.4e-2
+                    tol = 3e-2 if fam.startswith("GEMV") else 1e-2
+                    assert rel_fro(y[: ref.shape[0]], ref) < tol, (key, rel_fro(y[: ref.shape[0]], ref))
                     checked += 1
     assert checked >= 30
 
