@@ -46,6 +46,7 @@ SIGNATURES = {
     "gl_matmul_counter_bytes": (c_uint64, []),
     "gl_matmul": (c_int32, [ctypes.POINTER(GLMatmulArgs), c_void_p]),
     "gl_matmul_kernel_name": (c_char_p, [ctypes.POINTER(GLMatmulArgs)]),
+    "gl_matmul_noalloc": (c_int32, [ctypes.POINTER(GLMatmulArgs), c_void_p]),
     "gl_pack_over_cols": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_int32, c_int32, c_void_p]),
     "gl_pack_over_rows": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_int32, c_int32, c_void_p]),
     "gl_unpack_over_cols": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_int32, c_int32, c_int32, c_int32, c_void_p]),

@@ -43,11 +43,9 @@ extern "C" int gl_get_matmul_type(int32_t M, int32_t W_nbits, int32_t is_mx_dtyp
   return (W_nbits < 8) ? GL_MM_GEMV_REVSPLITK : GL_MM_GEMV_SPLITK;
 }
 
-namespace {
-
 enum KernelId { K_INVALID = 0, K_STREAM, K_TC, K_GENERIC };
 
-int validate(const gl_matmul_args* a) {
+int gl_validate_matmul_args(const gl_matmul_args* a) {
   if (a == nullptr) GL_FAIL(GL_E_INVALID, "gl_matmul: null argument struct");
   if (a->M < 0 || a->N <= 0 || a->K <= 0) GL_FAIL(GL_E_INVALID, "gl_matmul: bad shape M=%d N=%d K=%d", a->M, a->N, a->K);
   if (a->x == nullptr || a->w == nullptr || a->out == nullptr) GL_FAIL(GL_E_INVALID, "gl_matmul: null x / w / out pointer");
@@ -69,6 +67,8 @@ int validate(const gl_matmul_args* a) {
   for (int i = 0; i < 2; ++i) if (a->reserved[i] != 0) GL_FAIL(GL_E_INVALID, "gl_matmul: reserved fields must be 0");
   return GL_OK;
 }
+
+namespace {
 
 // which kernel serves (family, problem)
 KernelId select(const gl_matmul_args* a, int* family_out) {
@@ -106,7 +106,7 @@ extern "C" const char* gl_matmul_kernel_name(const gl_matmul_args* a) {
 }
 
 extern "C" int gl_matmul(const gl_matmul_args* a, void* stream) {
-  if (int rc = validate(a)) return rc;
+  if (int rc = gl_validate_matmul_args(a)) return rc;
   if (a->M == 0) return GL_OK;
   cudaStream_t st = (cudaStream_t)stream;
   int fam;

@@ -29,6 +29,7 @@
 #include "gl_tc_common.cuh"
 #include <stdlib.h>
 #include <string.h>
+#include <mutex>
 
 namespace {
 
@@ -442,7 +443,7 @@ static int json_int(const char* js, const char* key, int dflt) {
   return atoi(p + 1);
 }
 
-static void plan_for(const gl_matmul_args* a, GemvPlan* pl) {
+static void plan_for(const gl_matmul_args* a, GemvPlan* pl, bool force_workspace = false) {
   const int e = a->elements_per_sample;
   const int T = a->K / (4 * e);
   pl->MT = a->M <= 8 ? 1 : (a->M <= 16 ? 2 : 4);
@@ -485,7 +486,7 @@ static void plan_for(const gl_matmul_args* a, GemvPlan* pl) {
   if (splitK < 1) splitK = 1;
   pl->splitK = splitK;
   const bool pow2 = (splitK & (splitK - 1)) == 0;
-  pl->cluster = (cluster_req != 0 && pow2 && splitK <= 8 && splitK > 1 && (32 * warps_n) % splitK == 0) ? splitK : 1;
+  pl->cluster = (!force_workspace && cluster_req != 0 && pow2 && splitK <= 8 && splitK > 1 && (32 * warps_n) % splitK == 0) ? splitK : 1;
   pl->slice_iters = (int)gl_cdiv(T, splitK) + 1;
   const int gi = a->group_size / (4 * e);
   pl->max_seg = pl->slice_iters / (gi > 0 ? gi : 1) + 2;
@@ -568,21 +569,25 @@ uint64_t gl_gemv_stream_workspace(const gl_matmul_args* a) {
   return gl_matmul_counter_bytes() + ((pl.splitK > 1 && pl.cluster == 1) ? (uint64_t)pl.splitK * a->M * a->N * sizeof(float) : 0);
 }
 
-int gl_gemv_stream_launch(const gl_matmul_args* a, cudaStream_t st) {
-  GemvPlan pl;
-  plan_for(a, &pl);
-  const uint64_t need = gl_gemv_stream_workspace(a);
-  if (a->workspace == nullptr || a->workspace_bytes < need)
+
+static uint64_t workspace_for_plan(const gl_matmul_args* a, const GemvPlan& pl) {
+  return gl_matmul_counter_bytes() + ((pl.splitK > 1 && pl.cluster == 1) ? (uint64_t)pl.splitK * a->M * a->N * sizeof(float) : 0);
+}
+
+// launches the streaming kernel with `workspace` as its scratch (counters | status | partial sums)
+static int gemv_launch_impl(const gl_matmul_args* a, cudaStream_t st, const GemvPlan& pl, void* workspace, uint64_t workspace_bytes) {
+  const uint64_t need = workspace_for_plan(a, pl);
+  if (workspace == nullptr || workspace_bytes < need)
     GL_FAIL(GL_E_WORKSPACE, "gl_matmul: workspace of %llu bytes needed, %llu given",
-            (unsigned long long)need, (unsigned long long)a->workspace_bytes);
-  if ((uintptr_t)a->workspace & 15) GL_FAIL(GL_E_INVALID, "gl_matmul: workspace must be 16-byte aligned");
+            (unsigned long long)need, (unsigned long long)workspace_bytes);
+  if ((uintptr_t)workspace & 15) GL_FAIL(GL_E_INVALID, "gl_matmul: workspace must be 16-byte aligned");
   const int e = a->elements_per_sample;
   GemvParams p;
   p.x = a->x; p.w = reinterpret_cast<const int32_t*>(a->w); p.scales = a->scales; p.zeros = a->zeros; p.bias = a->bias;
   p.out = a->out;
-  p.counters = reinterpret_cast<unsigned int*>(a->workspace);
-  p.status = reinterpret_cast<int*>(reinterpret_cast<char*>(a->workspace) + (size_t)kMaxTiles * sizeof(unsigned int));
-  p.partials = reinterpret_cast<float*>(reinterpret_cast<char*>(a->workspace) + gl_matmul_counter_bytes());
+  p.counters = reinterpret_cast<unsigned int*>(workspace);
+  p.status = reinterpret_cast<int*>(reinterpret_cast<char*>(workspace) + (size_t)kMaxTiles * sizeof(unsigned int));
+  p.partials = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + gl_matmul_counter_bytes());
   p.M = a->M; p.N = a->N; p.K = a->K;
   p.T = a->K / (4 * e);
   p.gi = a->group_size / (4 * e);
@@ -595,4 +600,62 @@ int gl_gemv_stream_launch(const gl_matmul_args* a, cudaStream_t st) {
   dim3 grid(pl.tiles, pl.splitK), block(32 * pl.warps_n);
   if (a->x_dtype == GL_BF16) return launch_nb<__nv_bfloat16>(a->W_nbits, pl.MT, p, grid, block, pl.smem, st);
   return launch_nb<__half>(a->W_nbits, pl.MT, p, grid, block, pl.smem, st);
+}
+
+int gl_gemv_stream_launch(const gl_matmul_args* a, cudaStream_t st) {
+  GemvPlan pl;
+  plan_for(a, &pl);
+  return gemv_launch_impl(a, st, pl, a->workspace, a->workspace_bytes);
+}
+
+// ---- gl_matmul_noalloc: the split-K streaming kernel on scratch that lives inside the library -------------
+// For callers that must not (or cannot) allocate device memory around the call: plug-ins that only receive
+// tensors from a host framework whose allocator they may not touch, code inside a memory-pool-managed serving
+// loop where a cudaMalloc would synchronise the device, and hosts that bind the C ABI from a language runtime without a device allocator of their own.
+//
+// The scratch (arrival counters, status word, fp32 split-K partial sums) is this file-scope device array.  Every
+// GPU that loads the library carries GL_NOALLOC_SCRATCH_BYTES of it until the process exits.  The name
+// `g_noalloc_scratch` is only a host-side handle here: its device address is looked up once per device with
+// cudaGetSymbolAddress (with that device current) and that pointer is what the kernel receives.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[GL_NOALLOC_SCRATCH_BYTES];
+
+static int noalloc_scratch_ptr(void** out) {
+  static void* ptrs[64];
+  static std::mutex mu;
+  int dev = 0;
+  GL_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) GL_FAIL(GL_E_INVALID, "gl_matmul_noalloc: device index %d out of range", dev);
+  std::lock_guard<std::mutex> lk(mu);
+  if (ptrs[dev] == nullptr) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);   // address on the current device
+    if (e != cudaSuccess || p == nullptr) {
+      gl_set_error("gl_matmul_noalloc: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
+      return GL_E_CUDA;
+    }
+    ptrs[dev] = p;
+  }
+  *out = ptrs[dev];
+  return GL_OK;
+}
+
+extern "C" int gl_matmul_noalloc(const gl_matmul_args* a, void* stream) {
+  if (int rc = gl_validate_matmul_args(a)) return rc;
+  if (a->M == 0) return GL_OK;
+  if (gl_is_mx(a->input_dtype) || !gl_gemv_stream_supported(a))
+    GL_FAIL(GL_E_UNSUPPORTED, "gl_matmul_noalloc: only the streaming decode kernel (packed 4/2/1-bit weights, fp16/bf16 "
+                              "activations, M <= 32) has a built-in-scratch variant");
+  GemvPlan pl;
+  plan_for(a, &pl, /*force_workspace=*/true);
+  const uint64_t need = workspace_for_plan(a, pl);
+  if (need > (uint64_t)GL_NOALLOC_SCRATCH_BYTES)
+    GL_FAIL(GL_E_WORKSPACE, "gl_matmul_noalloc: this problem (M=%d N=%d, %d K slices) needs %llu bytes of scratch, the built-in "
+                            "array holds %llu; use gl_matmul with a caller-provided workspace",
+            a->M, a->N, pl.splitK, (unsigned long long)need, (unsigned long long)GL_NOALLOC_SCRATCH_BYTES);
+  void* scratch = nullptr;
+  if (int rc = noalloc_scratch_ptr(&scratch)) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  // the array keeps whatever the previous call left: the counters and the status word must start at zero
+  GL_CUDA_CHECK(cudaMemsetAsync(scratch, 0, (size_t)gl_matmul_counter_bytes(), st));
+  return gemv_launch_impl(a, st, pl, scratch, (uint64_t)GL_NOALLOC_SCRATCH_BYTES);
 }

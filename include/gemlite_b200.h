@@ -152,6 +152,31 @@ GL_API uint64_t gl_matmul_counter_bytes(void);
  * gemlite/core.py:263-272. */
 GL_API int gl_matmul(const gl_matmul_args* a, void* stream);
 
+/* gl_matmul() for callers that cannot hand over a workspace because they cannot allocate one.
+ * (No counterpart in the reference: its kernels get their scratch from torch, e.g. the zero-filled output of
+ * gemv_revsplitK_forward; this entry point exists for hosts where that is not possible.)
+ *
+ * Who that is: a plug-in that only receives device pointers from a framework whose allocator it may not call;
+ * code on a serving hot path where cudaMalloc / cudaFree would stall the device; a
+ * binding from a language runtime that has no device allocator at all.  Such callers still pass x, weights,
+ * meta data and `out`; `workspace` / `workspace_bytes` of `a` are ignored.
+ *
+ * What it runs: the streaming decode kernel (packed 4/2/1-bit weights, fp16/bf16 activations, M <= 32; anything
+ * else returns GL_E_UNSUPPORTED) in its split-K-through-scratch form.  The scratch -- arrival counters, a status
+ * word and the fp32 partial sums -- is a fixed array of GL_NOALLOC_SCRATCH_BYTES (4 MiB) inside the library.
+ * Every GPU that loads the library holds those 4 MiB until the process exits.  A problem whose partial sums do
+ * not fit (counter block + slices * M * N * 4 bytes > 4 MiB) is rejected with GL_E_WORKSPACE and a message giving
+ * both sizes; use gl_matmul() with your own workspace for it.
+ *
+ * The call allocates and frees nothing (no cudaMalloc / cudaFree, no allocating library routine).  The first call
+ * on each device looks up the array's device address (cudaGetSymbolAddress, with that device current) and caches
+ * it: make that first call outside of any stream capture.  Every call clears the counter block on `stream`
+ * before the kernel (the array keeps what the previous call left behind) and all calls share the one array, so
+ * two calls that can overlap on the GPU (for example on different streams) race; keep the calls on one device
+ * ordered on one stream.  Results equal gl_matmul()'s. */
+#define GL_NOALLOC_SCRATCH_BYTES (4u << 20)
+GL_API int gl_matmul_noalloc(const gl_matmul_args* a, void* stream);
+
 /* Name of the CUDA kernel gl_matmul() would launch for `a` (for logs and the config cache). */
 GL_API const char* gl_matmul_kernel_name(const gl_matmul_args* a);
 
