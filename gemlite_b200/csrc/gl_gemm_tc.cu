@@ -54,12 +54,22 @@ template <> struct KindTraits<KIND_NVF4>   { static constexpr int ELEMS_PER_ROW 
 constexpr uint32_t next_pow2_cols(uint32_t c) { return c <= 32 ? 32 : c <= 64 ? 64 : c <= 128 ? 128 : c <= 256 ? 256 : 512; }
 
 // ---- epilogue shared by all formats ---------------------------------------------------------------
+// per-column epilogue constants of the tile, staged once in shared memory (fp32): channel scale and bias
+__device__ __forceinline__ void stage_epilogue_consts(const TcParams& p, float* sw_s, float* b_s, int n0, int BN) {
+  for (int c = threadIdx.x; c < BN; c += blockDim.x) {
+    const int n = n0 + c;
+    sw_s[c] = (p.scales_w != nullptr && n < p.N) ? gl_load_as_float(p.scales_w, n, p.scales_w_dtype) : 1.f;
+    b_s[c] = (p.bias != nullptr && n < p.N) ? gl_load_as_float(p.bias, n, p.out_dtype) : 0.f;
+  }
+}
+
 template <bool INT_ACC>
-__device__ __forceinline__ void epilogue_tile(const TcParams& p, uint32_t tmem_d, int m0, int n0, int BN, int epi_warp, int lane) {
+__device__ __forceinline__ void epilogue_tile(const TcParams& p, uint32_t tmem_d, int m0, int n0, int BN, int epi_warp, int lane,
+                                              const float* sw_s, const float* b_s) {
   const int quad = epi_warp & 3;                       // TMEM lane quadrant this warp may read
   const int m = m0 + quad * 32 + lane;
-  const float sx = (p.scales_x != nullptr && m < p.M) ? p.scales_x[m] : 1.f;
-  const float ms = (p.meta_scale != nullptr) ? *p.meta_scale : 1.f;
+  float rowscale = (p.scales_x != nullptr && m < p.M) ? p.scales_x[m] : 1.f;
+  if (p.meta_scale != nullptr) rowscale *= *p.meta_scale;
   for (int c0 = 0; c0 < BN; c0 += 32) {
     if (n0 + c0 >= p.N) break;                         // warp-uniform
     uint32_t rr[32];
@@ -67,15 +77,15 @@ __device__ __forceinline__ void epilogue_tile(const TcParams& p, uint32_t tmem_d
     if (m >= p.M) continue;
     float v[32];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      float a = INT_ACC ? (float)(int32_t)rr[i] : __uint_as_float(rr[i]);
-      a *= ms;
-      const int n = n0 + c0 + i;
-      float sw = 1.f;
-      if (p.scales_w != nullptr && n < p.N) sw = gl_load_as_float(p.scales_w, n, p.scales_w_dtype);
-      a *= sx * sw;
-      if (p.bias != nullptr && n < p.N) a += gl_load_as_float(p.bias, n, p.out_dtype);
-      v[i] = a;
+    for (int q = 0; q < 8; ++q) {
+      const float4 sw = *reinterpret_cast<const float4*>(sw_s + c0 + 4 * q);
+      const float4 bb = *reinterpret_cast<const float4*>(b_s + c0 + 4 * q);
+      const float s4[4] = {sw.x, sw.y, sw.z, sw.w}, b4[4] = {bb.x, bb.y, bb.z, bb.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float a = INT_ACC ? (float)(int32_t)rr[4 * q + j] : __uint_as_float(rr[4 * q + j]);
+        v[4 * q + j] = fmaf(a * rowscale, s4[j], b4[j]);
+      }
     }
     const int nb = n0 + c0;
     const size_t o = (size_t)m * p.N + nb;
@@ -126,11 +136,14 @@ __global__ void __launch_bounds__(192, 1) gl_gemm_tc_kernel(const __grid_constan
   uint64_t* empty = full + STAGES;
   uint64_t* tmem_full = empty + STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
+  float* sw_s = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(tmem_slot + 1) + 15) & ~(uintptr_t)15);
+  float* b_s = sw_s + BN;
   __shared__ int s_abort;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (p.M + 127) / 128;
   const int m0 = (blockIdx.x % tiles_m) * 128, n0 = (blockIdx.x / tiles_m) * BN;
+  stage_epilogue_consts(p, sw_s, b_s, n0, BN);
 
   if (threadIdx.x == 0) {
     s_abort = 0;
@@ -216,7 +229,7 @@ __global__ void __launch_bounds__(192, 1) gl_gemm_tc_kernel(const __grid_constan
   } else {
     if (mbar_wait(tmem_full, 0u, &s_abort, p.status, 4)) {
       tc_fence_after();
-      epilogue_tile<KIND == KIND_I8>(p, tmem_base, m0, n0, BN, warp, lane);
+      epilogue_tile<KIND == KIND_I8>(p, tmem_base, m0, n0, BN, warp, lane, sw_s, b_s);
     }
   }
   tc_fence_before();
@@ -257,11 +270,14 @@ __global__ void __launch_bounds__(448, 1) gl_gemm_tc_a16wn_kernel(const __grid_c
   uint64_t* empty = bready + STAGES;                                            // MMAs of the stage retired
   uint64_t* tmem_full = empty + STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
+  float* sw_s = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(tmem_slot + 1) + 15) & ~(uintptr_t)15);
+  float* b_s = sw_s + BN;
   __shared__ int s_abort;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (p.M + 127) / 128;
   const int m0 = (blockIdx.x % tiles_m) * 128, n0 = (blockIdx.x / tiles_m) * BN;
+  stage_epilogue_consts(p, sw_s, b_s, n0, BN);
 
   if (threadIdx.x == 0) {
     s_abort = 0;
@@ -308,7 +324,7 @@ __global__ void __launch_bounds__(448, 1) gl_gemm_tc_a16wn_kernel(const __grid_c
   } else if (warp < 2 + kNumEpiWarps) {
     if (mbar_wait(tmem_full, 0u, &s_abort, p.status, 4)) {
       tc_fence_after();
-      epilogue_tile<false>(p, tmem_base, m0, n0, BN, warp, lane);
+      epilogue_tile<false>(p, tmem_base, m0, n0, BN, warp, lane, sw_s, b_s);
     }
   } else {
     // dequant warps: warp dw owns 32 columns (BN = 256) or 32 columns x half of the packed rows (BN = 128)
@@ -397,7 +413,7 @@ template <int KIND, int BN, int STAGES>
 static int launch_tma_kernel(const CUtensorMap& tmA, const CUtensorMap& tmB, const TcParams& p, cudaStream_t st) {
   using KT = KindTraits<KIND>;
   constexpr size_t stage = 128 * 128 + BN * 128 + KT::SF_ATOMS * 512 * (1 + BN / 128);
-  const size_t smem = 1024 + STAGES * stage + (2 * STAGES + 1) * 8 + 16;
+  const size_t smem = 1024 + STAGES * stage + (2 * STAGES + 1) * 8 + 32 + 2 * BN * 4 + 16;
   auto kern = gl_gemm_tc_kernel<KIND, BN, STAGES>;
   if (int rc = set_smem(kern, smem)) return rc;
   const int tiles = ((p.M + 127) / 128) * ((p.N + BN - 1) / BN);
@@ -410,7 +426,7 @@ template <typename XT, int NB, int BN, int STAGES>
 static int launch_a16_kernel(const CUtensorMap& tmA, const CUtensorMap& tmW, const TcParams& p, cudaStream_t st) {
   constexpr int WROWS = 64 / (32 / NB);
   constexpr size_t stage = 128 * 128 + BN * 128 + ((WROWS * BN * 4 + 1023) / 1024) * 1024;
-  const size_t smem = 1024 + STAGES * stage + (4 * STAGES + 1) * 8 + 16;
+  const size_t smem = 1024 + STAGES * stage + (4 * STAGES + 1) * 8 + 32 + 2 * BN * 4 + 16;
   auto kern = gl_gemm_tc_a16wn_kernel<XT, NB, BN, STAGES>;
   if (int rc = set_smem(kern, smem)) return rc;
   const int tiles = ((p.M + 127) / 128) * ((p.N + BN - 1) / BN);
