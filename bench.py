@@ -308,6 +308,12 @@ def main():
 
     if rank == 0 and not args.no_sweep:
         result["sweep"] = sweep(device, layers, stream, hbm_peak, bf16_peak)
+        del layers, arg_structs, outs
+        torch.cuda.empty_cache()
+        try:
+            result["sweep_gemm"] = sweep_gemm(device)
+        except Exception as e:  # the extra formats must not lose the headline numbers
+            result["sweep_gemm"] = [{"error": str(e)[:200]}]
     if rank == 0 and not args.no_cpu and world >= 1:
         try:
             result["cpu_baseline"] = cpu_path_sample(seconds=12.0)
@@ -358,6 +364,67 @@ def sweep(device, layers, stream, hbm_peak, bf16_peak):
                         "TFLOPs": flops / us / 1e6, "kernel": L.gl_matmul_kernel_name(ctypes.byref(structs[0])).decode()})
         except Exception as e:
             res.append({"format": "A16W4", "M": M, "error": str(e)[:200]})
+    return res
+
+
+def sweep_gemm(device):
+    """The other benchmark configurations through the public API (GemLiteLinear.forward incl. the fused
+    activation quantiser): FP8 4096->14336, MXFP4 / NVFP4 16384x16384, A16W4 8192x8192 at prefill size.
+    L2 is flushed between timed calls; min of 10 calls; TFLOP/s = 2 M N K / time.  `ref_triton_ms` is the
+    reference's own Triton kernel timed on a B200 when the golden fixtures were captured."""
+    from gemlite_b200 import helper
+    ref = {}
+    try:
+        ref = json.load(open(os.path.join(ROOT, "tests", "golden", "triton_timings.json")))["timings"]
+    except Exception:
+        pass
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.int8, device=device)
+    dense_peak = {"A16W4": 2250.0, "FP8": 4500.0, "MXFP4": 9000.0, "NVFP4": 9000.0}     # nominal dense TFLOP/s
+
+    def timed(fn, reps=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize(device)
+        best = 1e9
+        for _ in range(reps):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(); b.record()
+            torch.cuda.synchronize(device)
+            best = min(best, a.elapsed_time(b))
+        return best
+
+    def make(fmt):
+        g = torch.Generator(device=device).manual_seed(7)
+        if fmt == "A16W4":
+            N = K = 8192
+            W_q = torch.randint(0, 16, (N, K), generator=g, device=device, dtype=torch.int32).to(torch.uint8)
+            sc = (torch.randn(N * K // 128, 1, generator=g, device=device).abs() * 0.02).to(torch.bfloat16)
+            z = (torch.rand(N * K // 128, 1, generator=g, device=device) * 15).to(torch.bfloat16)
+            return helper.A16W4_HQQ_INT(device=str(device), dtype=torch.bfloat16).from_weights(W_q, sc, z), K, N
+        K, N = (4096, 14336) if fmt == "FP8" else (16384, 16384)
+        lin = torch.nn.Linear(K, N, bias=False, dtype=torch.bfloat16, device=device)
+        lin.weight.data.normal_(0, 0.02, generator=g)
+        P = {"FP8": helper.A8W8_FP8_dynamic, "MXFP4": helper.A4W4_MXFP_dynamic, "NVFP4": helper.A4W4_NVFP_dynamic}[fmt]
+        return P(device=str(device), dtype=torch.bfloat16).from_linear(lin), K, N
+
+    res = []
+    for fmt, Ms in (("A16W4", (64, 4096)), ("FP8", (1, 4096)), ("MXFP4", (1, 4096)), ("NVFP4", (1, 4096))):
+        try:
+            layer, K, N = make(fmt)
+            for M in Ms:
+                x = torch.randn(M, K, dtype=torch.bfloat16, device=device)
+                ms = timed(lambda: layer(x))
+                tf = 2.0 * M * N * K / ms / 1e9
+                row = {"format": fmt, "M": M, "N": N, "K": K, "ms": ms, "TFLOPs": tf, "frac_dense_nominal": tf / dense_peak[fmt]}
+                r = ref.get("%s_%dx%d_M%d" % (fmt, K if fmt == "FP8" else N, N if fmt == "FP8" else K, M))
+                if r:
+                    row["ref_triton_ms"] = r["min_ms"]
+                res.append(row)
+            del layer
+            torch.cuda.empty_cache()
+        except Exception as e:
+            res.append({"format": fmt, "error": str(e)[:200]})
     return res
 
 

@@ -98,7 +98,7 @@ extern "C" const char* gl_matmul_kernel_name(const gl_matmul_args* a) {
   if (a == nullptr) return "invalid";
   int fam;
   switch (select(a, &fam)) {
-    case K_STREAM: return "gl_gemv_stream_kernel";
+    case K_STREAM: return gl_gemv_stream_kernel_name(a);
     case K_TC: return "gl_gemm_tc_kernel";
     case K_GENERIC: return "gl_generic_kernel";
     default: return "invalid";

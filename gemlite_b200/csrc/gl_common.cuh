@@ -39,6 +39,7 @@ int gl_num_sms();
 // ---- family launchers (each returns GL_OK / GL_E_*; GL_E_UNSUPPORTED = "not my case") -----
 int gl_gemv_stream_supported(const gl_matmul_args* a);
 uint64_t gl_gemv_stream_workspace(const gl_matmul_args* a);
+const char* gl_gemv_stream_kernel_name(const gl_matmul_args* a);
 int gl_gemv_stream_launch(const gl_matmul_args* a, cudaStream_t st);
 int gl_generic_launch(const gl_matmul_args* a, cudaStream_t st);
 int gl_validate_matmul_args(const gl_matmul_args* a);

@@ -535,6 +535,6 @@ int gl_gemm_tc_launch(const gl_matmul_args* a, cudaStream_t st) {
   p.meta_scale = (path == TC_NVFP4) ? a->meta_scale : nullptr;
   if (int rc = gl_make_tmap_2d(&tmA, a->x, 0, (uint64_t)a->K / 2, (uint64_t)a->M, (uint64_t)a->K / 2, 128, 128, true)) return rc;
   if (int rc = gl_make_tmap_2d(&tmB, a->w, 0, (uint64_t)a->K / 2, (uint64_t)a->N, (uint64_t)a->K / 2, 128, (uint32_t)BN, true)) return rc;
-  if (path == TC_MXFP4) return BN == 256 ? launch_tma_kernel<KIND_MXF4, 256, 3>(tmA, tmB, p, st) : launch_tma_kernel<KIND_MXF4, 128, 5>(tmA, tmB, p, st);
-  return BN == 256 ? launch_tma_kernel<KIND_NVF4, 256, 3>(tmA, tmB, p, st) : launch_tma_kernel<KIND_NVF4, 128, 5>(tmA, tmB, p, st);
+  if (path == TC_MXFP4) return BN == 256 ? launch_tma_kernel<KIND_MXF4, 256, 4>(tmA, tmB, p, st) : launch_tma_kernel<KIND_MXF4, 128, 6>(tmA, tmB, p, st);
+  return BN == 256 ? launch_tma_kernel<KIND_NVF4, 256, 4>(tmA, tmB, p, st) : launch_tma_kernel<KIND_NVF4, 128, 6>(tmA, tmB, p, st);
 }

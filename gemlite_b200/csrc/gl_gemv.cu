@@ -47,6 +47,7 @@ struct GemvParams {
   int W_group_mode, channel_scale_mode, zero_is_scalar;
   int out_dtype;
   int max_slice_iters, max_seg;
+  int s_in, c_in;   // warp-independent kernel: K slices and 32-column groups inside a CTA
 };
 
 template <typename XT> struct XTraits;
@@ -427,7 +428,279 @@ __global__ void __launch_bounds__(128) gl_gemv_stream_kernel(const GemvParams p)
     }
 }
 
-struct GemvPlan { int warps_n, splitK, cluster, MT, slice_iters, max_seg, tiles; size_t smem; };
+// ---- warp-independent kernel ---------------------------------------------------------------------------
+// The same arithmetic with every trip count fixed and no CTA-wide barrier before the final reduction.
+// A CTA is s_in x c_in warps: c_in column groups of 32 columns times s_in consecutive K slices; the grid's y
+// dimension adds `cluster` outer slices that are summed through distributed shared memory.  A warp owns one
+// (slice, 32 columns) pair end to end: it issues its first weight loads and scale/zero copies before the
+// dependency wait, converts its own per-group constants, and only shares the staged activations of its slice
+// with the c_in - 1 warps beside it (named barrier).  The per-group sums of x come out of the tensor core as well
+// (an all-ones A operand), so staging is a permuted copy.
+// Preconditions (checked by the planner): N % (32 c_in) == 0; T % (s_in cluster) == 0; every slice is a whole
+// number of 8-iteration batches and either holds whole groups or lies inside one group.
+template <typename XT>
+__device__ __forceinline__ void mma16816z(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1);
+template <>
+__device__ __forceinline__ void mma16816z<__nv_bfloat16>(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  const float z = 0.f;
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+               : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(z));
+}
+template <>
+__device__ __forceinline__ void mma16816z<__half>(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  const float z = 0.f;
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+               : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(z));
+}
+template <typename XT> struct OnesPair;
+template <> struct OnesPair<__nv_bfloat16> { static constexpr uint32_t V = 0x3F803F80u; };
+template <> struct OnesPair<__half> { static constexpr uint32_t V = 0x3C003C00u; };
+
+// GI: iterations per quantisation group when it divides 8 (1, 2, 4); 0 = a multiple of 8 (p.gi), flushed at run time
+template <int NB, typename XT, int MT, int GI>
+__global__ void __launch_bounds__(MT == 1 ? 512 : 256, 1) gl_gemv_warp_kernel(const GemvParams p) {
+  constexpr int E = 32 / NB, H = E / 8, HALF = E / 2, U = 8;
+  constexpr uint32_t FMASK = ((1u << NB) - 1u) * 0x00010001u;
+  constexpr uint32_t ONES = OnesPair<XT>::V;
+  using XTr = XTraits<XT>;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int r = lane >> 2, t = lane & 3;
+  const int s_in = p.s_in, c_in = p.c_in;
+  const int sl = warp / c_in, wc = warp - sl * c_in;       // slice and column group of this warp inside the CTA
+  const int nit = p.T / (s_in * p.cluster);                // iterations per slice (exact)
+  const int it0 = (blockIdx.y * s_in + sl) * nit;
+  const int g0 = it0 / p.gi;
+  const int nseg = (nit + p.gi - 1) / p.gi;                // whole groups, or 1 when the slice lies inside a group
+  const int ccols = c_in * 32;
+
+  // shared: x fragments [slice] | per-warp {alpha, beta, raw scales, raw zeros, zero unit} | partial tiles [slice]
+  const int xs_slice_units = nit * H * p.M * 4;
+  uint4* xs = reinterpret_cast<uint4*>(smem_raw) + (size_t)sl * xs_slice_units;
+  unsigned char* wbase = smem_raw + (size_t)s_in * xs_slice_units * 16 + (size_t)warp * (nseg * 32 * 12 + 16);
+  float* alpha = reinterpret_cast<float*>(wbase);
+  float* beta = alpha + nseg * 32;
+  uint16_t* ms = reinterpret_cast<uint16_t*>(beta + nseg * 32);
+  uint16_t* mz = ms + nseg * 32;
+  uint4* zero_unit = reinterpret_cast<uint4*>(mz + nseg * 32);
+  float* part = reinterpret_cast<float*>(smem_raw + (size_t)s_in * xs_slice_units * 16 +
+                                         (size_t)s_in * c_in * (nseg * 32 * 12 + 16));     // [slice][M][ccols]
+
+  // ---- before the dependency wait: first batch of weights, raw scales / zeros of this warp's groups -------
+  const int n0 = blockIdx.x * ccols + wc * 32 + 4 * r;
+  const int32_t* wp = p.w + (size_t)(it0 * 4 + t) * p.N + n0;
+  const size_t wstep = (size_t)4 * p.N;
+  int4 bufA[U], bufB[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) bufA[u] = ldg_stream(wp + (size_t)u * wstep);
+  {
+    const bool need_s = p.W_group_mode >= 2;
+    const bool need_z = (p.W_group_mode == 1 || p.W_group_mode >= 3) && !p.zero_is_scalar;
+    for (int i = lane; i < nseg * 8; i += 32) {                    // 8-byte pieces (4 columns)
+      const int sg = i >> 3, pc = i & 7;
+      const size_t goff = (size_t)(g0 + sg) * p.N + blockIdx.x * ccols + wc * 32 + pc * 4;
+      if (need_s)
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(gltc::smem_u32(ms + sg * 32 + pc * 4)),
+                     "l"(reinterpret_cast<const uint16_t*>(p.scales) + goff) : "memory");
+      if (need_z)
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(gltc::smem_u32(mz + sg * 32 + pc * 4)),
+                     "l"(reinterpret_cast<const uint16_t*>(p.zeros) + goff) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  if (lane == 0) *zero_unit = make_uint4(0u, 0u, 0u, 0u);
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  // ---- stage this slice of x in B-fragment order (shared by the c_in warps of the slice) -------------------
+  {
+    const uint16_t* xg = reinterpret_cast<const uint16_t*>(p.x) + (size_t)it0 * 4 * E;
+    const int row_units = nit * 4 * H;                             // 16-byte units per batch row
+    const int tg = wc * 32 + lane, tgn = ccols;
+    for (int m = 0; m < p.M; ++m) {
+      const uint16_t* xr = xg + (size_t)m * p.K;
+      for (int u = tg; u < row_units; u += tgn) {
+        const int row = u / H, hh = u - row * H;                   // packed row inside the slice, piece of the row
+        const uint2 lo = *reinterpret_cast<const uint2*>(xr + row * E + 4 * hh);
+        const uint2 hi = *reinterpret_cast<const uint2*>(xr + row * E + HALF + 4 * hh);
+        uint4 o;
+        o.x = __byte_perm(lo.x, hi.x, 0x5410); o.y = __byte_perm(lo.x, hi.x, 0x7632);
+        o.z = __byte_perm(lo.y, hi.y, 0x5410); o.w = __byte_perm(lo.y, hi.y, 0x7632);
+        xs[((((row >> 2) * H + hh) * p.M + m) << 2) + (row & 3)] = o;
+      }
+    }
+  }
+  asm volatile("cp.async.wait_all;" ::: "memory");
+  __syncwarp();
+  {                                                   // per-group fp32 constants: out += alpha * acc + beta * xsum
+    const float zs = p.zero_is_scalar ? (float)(*reinterpret_cast<const int32_t*>(p.zeros)) : 0.f;
+    for (int i = lane; i < nseg * 32; i += 32) {
+      float al = 1.f, z = zs;
+      if (p.W_group_mode >= 2) al = XTr::to_float(ms[i]);
+      if ((p.W_group_mode == 1 || p.W_group_mode >= 3) && !p.zero_is_scalar) z = XTr::to_float(mz[i]);
+      float be;
+      if (p.W_group_mode == 4)      be = z - XTr::BIAS * al;
+      else if (p.W_group_mode == 3) be = -(XTr::BIAS + z) * al;
+      else if (p.W_group_mode == 1) be = -(XTr::BIAS + z);
+      else                          be = -XTr::BIAS * al;
+      alpha[i] = al;
+      beta[i] = be;
+    }
+  }
+  if (c_in > 1) asm volatile("bar.sync %0, %1;" ::"r"(1 + sl), "r"(ccols) : "memory");
+  else __syncwarp();
+
+  // ---- main loop ----------------------------------------------------------------------------------------------
+  const uint4* xptr[MT];
+  int xstride[MT], pstride[MT];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt) {                    // batch rows >= M read the zero unit with stride 0
+    const int m = mt * 8 + r;
+    const bool ok = m < p.M;
+    xptr[mt] = ok ? xs + ((m << 2) + t) : zero_unit;
+    xstride[mt] = ok ? H * p.M * 4 : 0;
+    pstride[mt] = ok ? p.M * 4 : 0;
+  }
+  float acc[2][MT][4], accS[MT][4], outv[2][MT][4];
+#pragma unroll
+  for (int b = 0; b < MT; ++b)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) { acc[0][b][c] = acc[1][b][c] = 0.f; accS[b][c] = 0.f; outv[0][b][c] = outv[1][b][c] = 0.f; }
+  int seg = 0;
+
+  auto flush = [&](int sgi, bool clear) {
+    const float4 al4 = *reinterpret_cast<const float4*>(alpha + sgi * 32 + 4 * r);
+    const float4 be4 = *reinterpret_cast<const float4*>(beta + sgi * 32 + 4 * r);
+    const float al[4] = {al4.x, al4.y, al4.z, al4.w}, be[4] = {be4.x, be4.y, be4.z, be4.w};
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      const float x0 = accS[mt][0], x1 = accS[mt][1];             // sums of x over the group, batch rows 2t, 2t+1
+#pragma unroll
+      for (int a = 0; a < 2; ++a) {
+        outv[a][mt][0] += al[2 * a] * acc[a][mt][0] + be[2 * a] * x0;
+        outv[a][mt][1] += al[2 * a] * acc[a][mt][1] + be[2 * a] * x1;
+        outv[a][mt][2] += al[2 * a + 1] * acc[a][mt][2] + be[2 * a + 1] * x0;
+        outv[a][mt][3] += al[2 * a + 1] * acc[a][mt][3] + be[2 * a + 1] * x1;
+        if (clear) { acc[a][mt][0] = acc[a][mt][1] = acc[a][mt][2] = acc[a][mt][3] = 0.f; }
+      }
+      if (clear) { accS[mt][0] = accS[mt][1] = accS[mt][2] = accS[mt][3] = 0.f; }
+    }
+  };
+
+  auto process = [&](const int4 (&buf)[U], int itb) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint32_t w[4] = {(uint32_t)buf[u].x, (uint32_t)buf[u].y, (uint32_t)buf[u].z, (uint32_t)buf[u].w};
+#pragma unroll
+      for (int hh = 0; hh < H; ++hh) {
+        uint4 xb[MT];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) xb[mt] = xptr[mt][(itb + u) * xstride[mt] + hh * pstride[mt]];
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const int pp = 2 * hh + q;
+          uint32_t f0[4], f1[4];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            f0[c] = ((w[c] >> (NB * (2 * pp))) & FMASK) | XTr::MAGIC;
+            f1[c] = ((w[c] >> (NB * (2 * pp + 1))) & FMASK) | XTr::MAGIC;
+          }
+          const bool first = (GI > 0) && ((u % (GI > 0 ? GI : 1)) == 0) && hh == 0 && q == 0;   // compile-time
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            const uint32_t b0 = q ? xb[mt].z : xb[mt].x, b1 = q ? xb[mt].w : xb[mt].y;
+            if (first) {
+              mma16816z<XT>(acc[0][mt], f0[0], f0[1], f1[0], f1[1], b0, b1);
+              mma16816z<XT>(acc[1][mt], f0[2], f0[3], f1[2], f1[3], b0, b1);
+              mma16816z<XT>(accS[mt], ONES, ONES, ONES, ONES, b0, b1);
+            } else {
+              mma16816<XT>(acc[0][mt], f0[0], f0[1], f1[0], f1[1], b0, b1);
+              mma16816<XT>(acc[1][mt], f0[2], f0[3], f1[2], f1[3], b0, b1);
+              mma16816<XT>(accS[mt], ONES, ONES, ONES, ONES, b0, b1);
+            }
+          }
+        }
+      }
+      if (GI > 0) {
+        if ((u % (GI > 0 ? GI : 1)) == (GI > 0 ? GI : 1) - 1) { flush(seg, false); ++seg; }
+      }
+    }
+    if (GI == 0) {                                   // group = several whole batches (or the whole slice)
+      const int done = itb + U;
+      if (done % p.gi == 0 || done == nit) { flush(seg, true); ++seg; }
+    }
+  };
+
+  const int nb = nit / U;
+  for (int b = 0; b < nb; b += 2) {
+    if (b + 1 < nb) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) bufB[u] = ldg_stream(wp + (size_t)((b + 1) * U + u) * wstep);
+    }
+    process(bufA, b * U);
+    if (b + 2 < nb) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) bufA[u] = ldg_stream(wp + (size_t)((b + 2) * U + u) * wstep);
+    }
+    if (b + 1 < nb) process(bufB, (b + 1) * U);
+  }
+
+  // ---- reduction over the CTA's slices, then over the cluster ---------------------------------------------------
+  {
+    float* mine = part + (size_t)sl * p.M * ccols + wc * 32 + 4 * r;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int m = mt * 8 + 2 * t + j;
+        if (m < p.M)
+          *reinterpret_cast<float4*>(mine + m * ccols) = make_float4(outv[0][mt][j], outv[0][mt][2 + j], outv[1][mt][j], outv[1][mt][2 + j]);
+      }
+  }
+  __syncthreads();
+  const int tile_elems = p.M * ccols;
+  if (p.cluster == 1) {
+    for (int i = threadIdx.x; i < tile_elems; i += blockDim.x) {
+      float v = part[i];
+      for (int q = 1; q < s_in; ++q) v += part[q * tile_elems + i];
+      const int m = i / ccols, n = blockIdx.x * ccols + (i - m * ccols);
+      if (p.channel_scale_mode == 1) v *= XTr::to_float(reinterpret_cast<const uint16_t*>(p.scales)[n]);
+      if (p.bias != nullptr) v += gl_load_as_float(p.bias, n, p.out_dtype);
+      gl_store_out(p.out, (int64_t)m * p.N + n, v, p.out_dtype);
+    }
+    return;
+  }
+  for (int i = threadIdx.x; i < tile_elems; i += blockDim.x) {      // fold the CTA's slices into slice 0
+    float v = part[i];
+    for (int q = 1; q < s_in; ++q) v += part[q * tile_elems + i];
+    part[i] = v;
+  }
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  {
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const int slice = ccols / p.cluster;
+    const uint32_t part_s = gltc::smem_u32(part);
+    for (int i = threadIdx.x; i < p.M * slice; i += blockDim.x) {
+      const int m = i / slice, c = rank * slice + (i - m * slice);
+      const int n = blockIdx.x * ccols + c;
+      float v = 0.f;
+      for (int q = 0; q < p.cluster; ++q) {
+        uint32_t ra;
+        float pv;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(part_s + (uint32_t)(m * ccols + c) * 4u), "r"(q));
+        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pv) : "r"(ra) : "memory");
+        v += pv;
+      }
+      if (p.channel_scale_mode == 1) v *= XTr::to_float(reinterpret_cast<const uint16_t*>(p.scales)[n]);
+      if (p.bias != nullptr) v += gl_load_as_float(p.bias, n, p.out_dtype);
+      gl_store_out(p.out, (int64_t)m * p.N + n, v, p.out_dtype);
+    }
+  }
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+struct GemvPlan { int warps_n, splitK, cluster, MT, slice_iters, max_seg, tiles, fast, gi, s_in, c_in; size_t smem; };
 
 // Tile parameters: built-in heuristic, overridden by a config-cache entry for the GEMV_REVSPLITK /
 // GEMV_SPLITK / GEMV family under the reference's signature "(Mb, N, K, group_size, e, type_id)" with
@@ -443,6 +716,54 @@ static int json_int(const char* js, const char* key, int dflt) {
   return atoi(p + 1);
 }
 
+// Plan for the warp-independent kernel; returns false when its preconditions do not hold.
+static bool plan_warp(const gl_matmul_args* a, GemvPlan* pl, const char* js) {
+  const int e = a->elements_per_sample;
+  if (!(a->W_nbits == 4 || a->W_nbits == 2) || a->M > 16 || a->N % 32 != 0 || a->K % (4 * e) != 0) return false;
+  if (a->group_size % (4 * e) != 0) return false;
+  const int T = a->K / (4 * e), H = e / 8, gi = a->group_size / (4 * e);
+  const int colgroups = a->N / 32;
+  if (!(gi == 1 || gi == 2 || gi == 4 || gi % 8 == 0)) return false;
+  auto slice_ok = [&](int S) {
+    if (S < 1 || T % S != 0) return false;
+    const int nit = T / S;
+    if (nit < 8 || nit % 8 != 0) return false;
+    return gi <= 4 ? (nit % gi == 0) : (nit % gi == 0 || gi % nit == 0);
+  };
+  int c_in = a->M <= 2 ? 1 : (a->M <= 4 ? 2 : (a->M <= 8 ? 4 : 8));
+  int s_in = 0, cluster = 0;
+  if (js) {
+    c_in = json_int(js, "c_in", c_in);
+    s_in = json_int(js, "s_in", 0);
+    cluster = json_int(js, "cluster_k", 0);
+  }
+  while (c_in > 1 && colgroups % c_in != 0) c_in >>= 1;
+  if (c_in < 1 || c_in > 16 || colgroups % c_in != 0) return false;
+  if (s_in <= 0 || cluster <= 0) {
+    const int64_t warp_slots = (int64_t)gl_num_sms() * 16;
+    int S = 1;
+    while (S < 128 && (int64_t)colgroups * (S * 2) * 10 <= warp_slots * 11) S <<= 1;
+    while (S > 1 && !slice_ok(S)) S >>= 1;
+    if (!slice_ok(S)) return false;
+    const int cta_warps = c_in >= 8 ? 8 : 8;
+    s_in = cta_warps / c_in; if (s_in < 1) s_in = 1; if (s_in > S) s_in = S;
+    cluster = S / s_in;
+    while (cluster > 8 && s_in * c_in < (a->M <= 8 ? 16 : 8)) { s_in <<= 1; cluster >>= 1; }
+  }
+  if (cluster < 1 || cluster > 8 || (cluster & (cluster - 1)) != 0 || s_in < 1 || s_in * c_in > (a->M <= 8 ? 16 : 8)) return false;
+  if (c_in > 1 && s_in > 15) return false;                          // one named barrier per slice
+  if (!slice_ok(s_in * cluster) || (32 * c_in) % cluster != 0) return false;
+  const int nit = T / (s_in * cluster), nseg = (nit + gi - 1) / gi;
+  const size_t smem = (size_t)s_in * nit * H * a->M * 64 + (size_t)s_in * c_in * (nseg * 32 * 12 + 16) +
+                      (size_t)s_in * a->M * c_in * 32 * 4 + 16;
+  if (smem > 200 * 1024) return false;
+  pl->fast = 1; pl->gi = gi; pl->s_in = s_in; pl->c_in = c_in; pl->cluster = cluster; pl->splitK = cluster;
+  pl->MT = a->M <= 8 ? 1 : 2;
+  pl->warps_n = s_in * c_in; pl->tiles = colgroups / c_in; pl->smem = smem;
+  pl->slice_iters = nit; pl->max_seg = nseg;
+  return true;
+}
+
 static void plan_for(const gl_matmul_args* a, GemvPlan* pl, bool force_workspace = false) {
   const int e = a->elements_per_sample;
   const int T = a->K / (4 * e);
@@ -450,6 +771,7 @@ static void plan_for(const gl_matmul_args* a, GemvPlan* pl, bool force_workspace
   const int H = e / 8;
   int warps_n = a->N <= 32 ? 1 : 2;
   int split_req = 0, cluster_req = -1;
+  const char* cfg_js = nullptr;
   {
     const int idt = (a->input_dtype == GL_BF16) ? GL_FP16 : a->input_dtype;
     char sig[128];
@@ -458,6 +780,7 @@ static void plan_for(const gl_matmul_args* a, GemvPlan* pl, bool force_workspace
     for (int f = 0; f < 3; ++f) {
       const char* js = gl_cfg_get(fams[f], sig);
       if (js) {
+        cfg_js = js;
         split_req = json_int(js, "split_k", 0);
         warps_n = json_int(js, "warps_n", warps_n);
         cluster_req = json_int(js, "cluster", -1);
@@ -465,6 +788,10 @@ static void plan_for(const gl_matmul_args* a, GemvPlan* pl, bool force_workspace
       }
     }
   }
+  pl->fast = 0; pl->s_in = pl->c_in = 1;
+  // "kernel": 1 in a cache entry pins the general kernel; entries that carry split_k / warps_n tune that kernel
+  const bool general_req = cfg_js && (json_int(cfg_js, "kernel", 0) == 1 || split_req > 0);
+  if (!force_workspace && !general_req && plan_warp(a, pl, cfg_js)) return;
   if (warps_n < 1) warps_n = 1;
   if (warps_n > 4) warps_n = 4;
   pl->warps_n = warps_n;
@@ -493,6 +820,8 @@ static void plan_for(const gl_matmul_args* a, GemvPlan* pl, bool force_workspace
   const size_t xs_bytes = (size_t)pl->slice_iters * per_iter_bytes;
   const size_t part_bytes = ((size_t)a->M * 32 * warps_n * 4 + 15) / 16 * 16;
   pl->smem = (xs_bytes > part_bytes ? xs_bytes : part_bytes) + (size_t)pl->max_seg * (8 * pl->MT * 4 + 2 * warps_n * 32 * 2) + 32;
+  pl->gi = gi;
+  pl->fast = 0;
 }
 
 template <int NB, typename XT, int MT>
@@ -514,6 +843,37 @@ static int launch_t(const GemvParams& p, dim3 grid, dim3 block, size_t smem, cud
   GL_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, p));
   return GL_OK;
 }
+template <typename K>
+static int launch_kernel(K kern, const GemvParams& p, dim3 grid, dim3 block, size_t smem, cudaStream_t st) {
+  if (smem > 48 * 1024) GL_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  int na = 1;
+  if (p.cluster > 1) {
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 1; attr[1].val.clusterDim.y = (unsigned)p.cluster; attr[1].val.clusterDim.z = 1;
+    na = 2;
+  }
+  cfg.attrs = attr; cfg.numAttrs = na;
+  GL_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, p));
+  return GL_OK;
+}
+template <int NB, typename XT, int MT>
+static int launch_fast_gi(int gi, const GemvParams& p, dim3 grid, dim3 block, size_t smem, cudaStream_t st) {
+  if (gi == 1) return launch_kernel(gl_gemv_warp_kernel<NB, XT, MT, 1>, p, grid, block, smem, st);
+  if (gi == 2) return launch_kernel(gl_gemv_warp_kernel<NB, XT, MT, 2>, p, grid, block, smem, st);
+  if (gi == 4) return launch_kernel(gl_gemv_warp_kernel<NB, XT, MT, 4>, p, grid, block, smem, st);
+  return launch_kernel(gl_gemv_warp_kernel<NB, XT, MT, 0>, p, grid, block, smem, st);
+}
+template <typename XT>
+static int launch_fast(int NB, int MT, int gi, const GemvParams& p, dim3 grid, dim3 block, size_t smem, cudaStream_t st) {
+  if (NB == 4) return MT == 1 ? launch_fast_gi<4, XT, 1>(gi, p, grid, block, smem, st) : launch_fast_gi<4, XT, 2>(gi, p, grid, block, smem, st);
+  return MT == 1 ? launch_fast_gi<2, XT, 1>(gi, p, grid, block, smem, st) : launch_fast_gi<2, XT, 2>(gi, p, grid, block, smem, st);
+}
+
 template <int NB, typename XT>
 static int launch_mt(int MT, const GemvParams& p, dim3 grid, dim3 block, size_t smem, cudaStream_t st) {
   if (MT == 1) return launch_t<NB, XT, 1>(p, grid, block, smem, st);
@@ -597,9 +957,20 @@ static int gemv_launch_impl(const gl_matmul_args* a, cudaStream_t st, const Gemv
   p.out_dtype = a->out_dtype;
   p.max_slice_iters = pl.slice_iters;
   p.max_seg = pl.max_seg;
+  p.s_in = pl.s_in; p.c_in = pl.c_in;
   dim3 grid(pl.tiles, pl.splitK), block(32 * pl.warps_n);
+  if (pl.fast) {
+    if (a->x_dtype == GL_BF16) return launch_fast<__nv_bfloat16>(a->W_nbits, pl.MT, pl.gi, p, grid, block, pl.smem, st);
+    return launch_fast<__half>(a->W_nbits, pl.MT, pl.gi, p, grid, block, pl.smem, st);
+  }
   if (a->x_dtype == GL_BF16) return launch_nb<__nv_bfloat16>(a->W_nbits, pl.MT, p, grid, block, pl.smem, st);
   return launch_nb<__half>(a->W_nbits, pl.MT, p, grid, block, pl.smem, st);
+}
+
+const char* gl_gemv_stream_kernel_name(const gl_matmul_args* a) {
+  GemvPlan pl;
+  plan_for(a, &pl);
+  return pl.fast ? "gl_gemv_warp_kernel" : "gl_gemv_stream_kernel";
 }
 
 int gl_gemv_stream_launch(const gl_matmul_args* a, cudaStream_t st) {

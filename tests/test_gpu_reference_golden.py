@@ -1,0 +1,57 @@
+"""GPU: the CUDA kernels against outputs of the reference's own Triton kernels captured on a B200
+(tests/golden/triton_golden.npz), on inputs regenerated from the seeds stored with the fixture.
+
+Tolerances are the operator's: relative Frobenius 1e-2 for fp16 / bf16 A16Wn, 3e-2 for FP8 / INT8 / FP4.  The
+reference's GEMV families add output-dtype partial sums with atomics (gemv_revsplitK_kernels.py:439-443) and sit
+up to 1.4e-2 from fp64 themselves, so they are pinned at 3e-2; its gemv_splitK outputs for groups narrower than
+its K block are excluded (they disagree with the reference's own GEMM family by more than 50 %)."""
+import numpy as np
+import pytest
+import torch
+
+from tests import golden_inputs as gi
+from tests.util import rel_fro
+
+pytestmark = pytest.mark.gpu
+
+
+def test_a16wn_kernels_match_reference_triton_outputs(lib):
+    from gemlite_b200 import helper
+    gold = gi.load()
+    checked = 0
+    for seed, N, K, nbits, gs, dtype, Ms in gi.A16_CASES:
+        for M in Ms:
+            x, W_q, s, z, _ = gi.a16_inputs(seed, N, K, nbits, gs, dtype, M)
+            layer = helper.A16Wn_HQQ_INT(device="cuda:0", dtype=dtype, W_nbits=nbits).from_weights(W_q.cuda(), s.cuda(), z.cuda())
+            y = layer(x.cuda()).float().cpu().numpy()
+            for fam in ("GEMV", "GEMV_REVSPLITK", "GEMV_SPLITK", "GEMM_SPLITK", "GEMM"):
+                key = "a16_s%d_M%d_%s" % (seed, M, fam)
+                if key not in gold.files or (fam == "GEMV_SPLITK" and gs < 128):
+                    continue
+                ref = gold[key]
+                tol = 3e-2 if fam.startswith("GEMV") else 1e-2
+                assert rel_fro(y[: ref.shape[0]], ref) < tol, (key, rel_fro(y[: ref.shape[0]], ref))
+                checked += 1
+    assert checked >= 30
+
+
+@pytest.mark.parametrize("name", ["fp8", "int8", "mxfp4"])
+def test_dynamic_formats_match_reference_triton_outputs(lib, name):
+    from gemlite_b200 import helper
+    gold = gi.load()
+    W, xs = gi.lin_inputs(gold, name)
+    N, K = W.shape
+    lin = torch.nn.Linear(K, N, bias=False, dtype=torch.bfloat16, device="cuda:0")
+    lin.weight.data.copy_(W)
+    P = {"fp8": helper.A8W8_FP8_dynamic, "int8": helper.A8W8_INT8_dynamic, "mxfp4": helper.A4W4_MXFP_dynamic}[name]
+    layer = P(device="cuda:0", dtype=torch.bfloat16).from_linear(lin)
+    n = 0
+    for M, x in xs.items():
+        y = layer(x.cuda()).float().cpu().numpy()
+        for fam in ("GEMV_SPLITK", "GEMM_SPLITK", "GEMM"):
+            key = "lin_%s_M%d_%s" % (name, M, fam)
+            if key in gold.files:
+                ref = gold[key]
+                assert rel_fro(y[: ref.shape[0]], ref) < 3e-2, (key, rel_fro(y[: ref.shape[0]], ref))
+                n += 1
+    assert n >= 2
