@@ -21,6 +21,7 @@
 //           factors are copied shared -> TMEM with tcgen05.cp from 128-row x 4-scale atoms (512 bytes)
 #include "gl_tc_common.cuh"
 #include <string.h>
+#include <stdlib.h>
 
 using namespace gltc;
 

@@ -456,6 +456,13 @@ template <typename XT> struct OnesPair;
 template <> struct OnesPair<__nv_bfloat16> { static constexpr uint32_t V = 0x3F803F80u; };
 template <> struct OnesPair<__half> { static constexpr uint32_t V = 0x3C003C00u; };
 
+// (v & mask) | magic as one three-input logic op with both constants in registers
+__device__ __forceinline__ uint32_t and_or(uint32_t v, uint32_t mask, uint32_t magic) {
+  uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(v), "r"(mask), "r"(magic));
+  return d;
+}
+
 // GI: iterations per quantisation group when it divides 8 (1, 2, 4); 0 = a multiple of 8 (p.gi), flushed at run time
 template <int NB, typename XT, int MT, int GI>
 __global__ void __launch_bounds__(MT == 1 ? 512 : 256, 1) gl_gemv_warp_kernel(const GemvParams p) {
@@ -490,9 +497,9 @@ __global__ void __launch_bounds__(MT == 1 ? 512 : 256, 1) gl_gemv_warp_kernel(co
   const int n0 = blockIdx.x * ccols + wc * 32 + 4 * r;
   const int32_t* wp = p.w + (size_t)(it0 * 4 + t) * p.N + n0;
   const size_t wstep = (size_t)4 * p.N;
-  int4 bufA[U], bufB[U];
+  int4 buf[U];
 #pragma unroll
-  for (int u = 0; u < U; ++u) bufA[u] = ldg_stream(wp + (size_t)u * wstep);
+  for (int u = 0; u < U; ++u) buf[u] = ldg_stream(wp + (size_t)u * wstep);
   {
     const bool need_s = p.W_group_mode >= 2;
     const bool need_z = (p.W_group_mode == 1 || p.W_group_mode >= 3) && !p.zero_is_scalar;
@@ -551,13 +558,17 @@ __global__ void __launch_bounds__(MT == 1 ? 512 : 256, 1) gl_gemv_warp_kernel(co
   else __syncwarp();
 
   // ---- main loop ----------------------------------------------------------------------------------------------
-  const uint4* xptr[MT];
+  const uint4* xcur[MT];
   int xstride[MT], pstride[MT];
+  // constants kept in registers: the unpack mask / magic, and four separate copies of the all-ones A operand
+  // (an MMA operand is a register quad; one shared register would be copied into a quad before every MMA)
+  uint32_t fmask = FMASK, magic = XTr::MAGIC, ones0 = ONES, ones1 = ONES, ones2 = ONES, ones3 = ONES;
+  asm volatile("" : "+r"(fmask), "+r"(magic), "+r"(ones0), "+r"(ones1), "+r"(ones2), "+r"(ones3));
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt) {                    // batch rows >= M read the zero unit with stride 0
     const int m = mt * 8 + r;
     const bool ok = m < p.M;
-    xptr[mt] = ok ? xs + ((m << 2) + t) : zero_unit;
+    xcur[mt] = ok ? xs + ((m << 2) + t) : zero_unit;
     xstride[mt] = ok ? H * p.M * 4 : 0;
     pstride[mt] = ok ? p.M * 4 : 0;
   }
@@ -587,7 +598,10 @@ __global__ void __launch_bounds__(MT == 1 ? 512 : 256, 1) gl_gemv_warp_kernel(co
     }
   };
 
-  auto process = [&](const int4 (&buf)[U], int itb) {
+  // One rolling set of U loads per lane: as soon as an iteration's words have been unpacked, the same registers
+  // are re-loaded with the words of iteration + U, so U x 512 bytes per warp stay in flight at all times.
+  const int32_t* wnext = wp + (size_t)U * wstep;
+  auto process = [&](int itb, bool reload) {
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const uint32_t w[4] = {(uint32_t)buf[u].x, (uint32_t)buf[u].y, (uint32_t)buf[u].z, (uint32_t)buf[u].w};
@@ -595,15 +609,15 @@ __global__ void __launch_bounds__(MT == 1 ? 512 : 256, 1) gl_gemv_warp_kernel(co
       for (int hh = 0; hh < H; ++hh) {
         uint4 xb[MT];
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) xb[mt] = xptr[mt][(itb + u) * xstride[mt] + hh * pstride[mt]];
+        for (int mt = 0; mt < MT; ++mt) xb[mt] = xcur[mt][hh * pstride[mt]];
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
           const int pp = 2 * hh + q;
           uint32_t f0[4], f1[4];
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
-            f0[c] = ((w[c] >> (NB * (2 * pp))) & FMASK) | XTr::MAGIC;
-            f1[c] = ((w[c] >> (NB * (2 * pp + 1))) & FMASK) | XTr::MAGIC;
+            f0[c] = and_or(w[c] >> (NB * (2 * pp)), fmask, magic);
+            f1[c] = and_or(w[c] >> (NB * (2 * pp + 1)), fmask, magic);
           }
           const bool first = (GI > 0) && ((u % (GI > 0 ? GI : 1)) == 0) && hh == 0 && q == 0;   // compile-time
 #pragma unroll
@@ -612,15 +626,18 @@ __global__ void __launch_bounds__(MT == 1 ? 512 : 256, 1) gl_gemv_warp_kernel(co
             if (first) {
               mma16816z<XT>(acc[0][mt], f0[0], f0[1], f1[0], f1[1], b0, b1);
               mma16816z<XT>(acc[1][mt], f0[2], f0[3], f1[2], f1[3], b0, b1);
-              mma16816z<XT>(accS[mt], ONES, ONES, ONES, ONES, b0, b1);
+              mma16816z<XT>(accS[mt], ones0, ones1, ones2, ones3, b0, b1);
             } else {
               mma16816<XT>(acc[0][mt], f0[0], f0[1], f1[0], f1[1], b0, b1);
               mma16816<XT>(acc[1][mt], f0[2], f0[3], f1[2], f1[3], b0, b1);
-              mma16816<XT>(accS[mt], ONES, ONES, ONES, ONES, b0, b1);
+              mma16816<XT>(accS[mt], ones0, ones1, ones2, ones3, b0, b1);
             }
           }
         }
       }
+      if (reload) { buf[u] = ldg_stream(wnext); wnext += wstep; }
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) xcur[mt] += xstride[mt];
       if (GI > 0) {
         if ((u % (GI > 0 ? GI : 1)) == (GI > 0 ? GI : 1) - 1) { flush(seg, false); ++seg; }
       }
@@ -632,18 +649,8 @@ __global__ void __launch_bounds__(MT == 1 ? 512 : 256, 1) gl_gemv_warp_kernel(co
   };
 
   const int nb = nit / U;
-  for (int b = 0; b < nb; b += 2) {
-    if (b + 1 < nb) {
-#pragma unroll
-      for (int u = 0; u < U; ++u) bufB[u] = ldg_stream(wp + (size_t)((b + 1) * U + u) * wstep);
-    }
-    process(bufA, b * U);
-    if (b + 2 < nb) {
-#pragma unroll
-      for (int u = 0; u < U; ++u) bufA[u] = ldg_stream(wp + (size_t)((b + 2) * U + u) * wstep);
-    }
-    if (b + 1 < nb) process(bufB, (b + 1) * U);
-  }
+  for (int b = 0; b + 1 < nb; ++b) process(b * U, true);
+  process((nb - 1) * U, false);
 
   // ---- reduction over the CTA's slices, then over the cluster ---------------------------------------------------
   {
@@ -730,7 +737,7 @@ static bool plan_warp(const gl_matmul_args* a, GemvPlan* pl, const char* js) {
     if (nit < 8 || nit % 8 != 0) return false;
     return gi <= 4 ? (nit % gi == 0) : (nit % gi == 0 || gi % nit == 0);
   };
-  int c_in = a->M <= 2 ? 1 : (a->M <= 4 ? 2 : (a->M <= 8 ? 4 : 8));
+  int c_in = a->M <= 2 ? 1 : (a->M <= 8 ? 4 : 8);
   int s_in = 0, cluster = 0;
   if (js) {
     c_in = json_int(js, "c_in", c_in);
@@ -740,13 +747,18 @@ static bool plan_warp(const gl_matmul_args* a, GemvPlan* pl, const char* js) {
   while (c_in > 1 && colgroups % c_in != 0) c_in >>= 1;
   if (c_in < 1 || c_in > 16 || colgroups % c_in != 0) return false;
   if (s_in <= 0 || cluster <= 0) {
-    const int64_t warp_slots = (int64_t)gl_num_sms() * 16;
-    int S = 1;
-    while (S < 128 && (int64_t)colgroups * (S * 2) * 10 <= warp_slots * 11) S <<= 1;
-    while (S > 1 && !slice_ok(S)) S >>= 1;
-    if (!slice_ok(S)) return false;
-    const int cta_warps = c_in >= 8 ? 8 : 8;
-    s_in = cta_warps / c_in; if (s_in < 1) s_in = 1; if (s_in > S) s_in = S;
+    // slices: fewest "waves x (iterations per warp + fixed per-warp cost)" over the power-of-two splits that fit
+    const int64_t warp_slots = (int64_t)gl_num_sms() * (a->M <= 8 ? 16 : 8);
+    int S = 0;
+    int64_t best_cost = 0;
+    for (int cand = 1; cand <= 64; cand <<= 1) {
+      if (!slice_ok(cand)) continue;
+      const int64_t waves = ((int64_t)colgroups * cand + warp_slots - 1) / warp_slots;
+      const int64_t cost = waves * (T / cand + 12);
+      if (S == 0 || cost < best_cost) { S = cand; best_cost = cost; }
+    }
+    if (S == 0) return false;
+    s_in = 8 / c_in; if (s_in < 1) s_in = 1; if (s_in > S) s_in = S;
     cluster = S / s_in;
     while (cluster > 8 && s_in * c_in < (a->M <= 8 ? 16 : 8)) { s_in <<= 1; cluster >>= 1; }
   }
@@ -957,7 +969,7 @@ static int gemv_launch_impl(const gl_matmul_args* a, cudaStream_t st, const Gemv
   p.out_dtype = a->out_dtype;
   p.max_slice_iters = pl.slice_iters;
   p.max_seg = pl.max_seg;
-  p.s_in = pl.s_in; p.c_in = pl.c_in;
+  p.s_in = pl.s_in; p.c_in = pl.c_in; 
   dim3 grid(pl.tiles, pl.splitK), block(32 * pl.warps_n);
   if (pl.fast) {
     if (a->x_dtype == GL_BF16) return launch_fast<__nv_bfloat16>(a->W_nbits, pl.MT, pl.gi, p, grid, block, pl.smem, st);
