@@ -120,6 +120,10 @@ __device__ __forceinline__ void epilogue_tile(const TcParams& p, uint32_t tmem_d
 }
 
 // ---- both operands by TMA: fp8 / int8 / mxfp4 / nvfp4 ---------------------------------------------
+// Persistent: the grid is one CTA per SM and CTA c computes tiles c, c + gridDim.x, ...  The shared-memory ring
+// runs straight across tile boundaries, so the loads of the next tile are in flight while the current one
+// finishes.  Without scale factors there is room in TMEM for two 256-column accumulators: the epilogue warps drain
+// one while the MMAs fill the other.  (Block-scaled formats keep one accumulator: 256 columns + scale factors.)
 template <int KIND, int BN, int STAGES>
 __global__ void __launch_bounds__(192, 1) gl_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA,
                                                             const __grid_constant__ CUtensorMap tmB, const TcParams p) {
@@ -128,28 +132,28 @@ __global__ void __launch_bounds__(192, 1) gl_gemm_tc_kernel(const __grid_constan
   constexpr int A_BYTES = 128 * 128, B_BYTES = BN * 128;
   constexpr int SFA_BYTES = KT::SF_ATOMS * 512, SFB_BYTES = KT::SF_ATOMS * 512 * (BN / 128);
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
-  constexpr uint32_t SFA_COL = BN, SFB_COL = BN + KT::SF_ATOMS * 4;
-  constexpr uint32_t TMEM_COLS = next_pow2_cols(BN + KT::SF_ATOMS * 4 * (1 + BN / 128));
+  constexpr int ACC_BUFS = MX ? 1 : 2;
+  constexpr uint32_t SFA_COL = ACC_BUFS * BN, SFB_COL = SFA_COL + KT::SF_ATOMS * 4;
+  constexpr uint32_t TMEM_COLS = next_pow2_cols(ACC_BUFS * BN + KT::SF_ATOMS * 4 * (1 + BN / 128));
 
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
   uint64_t* empty = full + STAGES;
-  uint64_t* tmem_full = empty + STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
-  float* sw_s = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(tmem_slot + 1) + 15) & ~(uintptr_t)15);
-  float* b_s = sw_s + BN;
+  uint64_t* tmem_full = empty + STAGES;                 // [ACC_BUFS] accumulator complete
+  uint64_t* tmem_empty = tmem_full + 2;                 // [ACC_BUFS] accumulator drained by the four epilogue warps
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  float* consts = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(tmem_slot + 1) + 15) & ~(uintptr_t)15);   // [4 warps][2][BN]
   __shared__ int s_abort;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (p.M + 127) / 128;
-  const int m0 = (blockIdx.x % tiles_m) * 128, n0 = (blockIdx.x / tiles_m) * BN;
-  stage_epilogue_consts(p, sw_s, b_s, n0, BN);
+  const int tiles = tiles_m * ((p.N + BN - 1) / BN);
 
   if (threadIdx.x == 0) {
     s_abort = 0;
     for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
-    mbar_init(tmem_full, 1);
+    for (int b = 0; b < ACC_BUFS; ++b) { mbar_init(tmem_full + b, 1); mbar_init(tmem_empty + b, kNumEpiWarps); }
     fence_barrier_init();
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
@@ -168,69 +172,97 @@ __global__ void __launch_bounds__(192, 1) gl_gemm_tc_kernel(const __grid_constan
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int kt = 0; kt < p.nkt; ++kt) {
-        const int s = kt % STAGES;
-        if (!mbar_wait(empty + s, (uint32_t)(((kt / STAGES) & 1) ^ 1), &s_abort, p.status, 2)) break;
-        unsigned char* st = smem + s * STAGE_BYTES;
-        uint32_t bytes = A_BYTES + B_BYTES;
-        int atoms = 0;
+      uint32_t it = 0;                                   // K tiles issued so far, over all tiles of this CTA
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * 128, n0 = (tile / tiles_m) * BN;
         const int valid_nb = min(BN / 128, (p.N - n0 + 127) / 128);   // 128-column blocks of this tile that exist
-        if (MX) {
-          atoms = min(KT::SF_ATOMS, p.sf_kblocks - kt * KT::SF_ATOMS);
-          bytes += (uint32_t)atoms * 512u * (1 + valid_nb);
-        }
-        mbar_expect_tx(full + s, bytes);
-        tma_load_2d(st, &tmA, full + s, kt * 128, m0);
-        tma_load_2d(st + A_BYTES, &tmB, full + s, kt * 128, n0);
-        if (MX) {
-          const size_t koff = (size_t)kt * KT::SF_ATOMS;
-          bulk_load_1d(st + A_BYTES + B_BYTES, p.sfa + ((size_t)(m0 / 128) * p.sf_kblocks + koff) * 512, (uint32_t)atoms * 512u, full + s);
-          for (int nb = 0; nb < valid_nb; ++nb)
-            bulk_load_1d(st + A_BYTES + B_BYTES + SFA_BYTES + nb * KT::SF_ATOMS * 512,
-                         p.sfb + ((size_t)(n0 / 128 + nb) * p.sf_kblocks + koff) * 512, (uint32_t)atoms * 512u, full + s);
+        for (int kt = 0; kt < p.nkt; ++kt, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(empty + s, ((it / STAGES) & 1u) ^ 1u, &s_abort, p.status, 2)) { ok = false; break; }
+          unsigned char* st = smem + s * STAGE_BYTES;
+          uint32_t bytes = A_BYTES + B_BYTES;
+          int atoms = 0;
+          if (MX) {
+            atoms = min(KT::SF_ATOMS, p.sf_kblocks - kt * KT::SF_ATOMS);
+            bytes += (uint32_t)atoms * 512u * (1 + valid_nb);
+          }
+          mbar_expect_tx(full + s, bytes);
+          tma_load_2d(st, &tmA, full + s, kt * 128, m0);
+          tma_load_2d(st + A_BYTES, &tmB, full + s, kt * 128, n0);
+          if (MX) {
+            const size_t koff = (size_t)kt * KT::SF_ATOMS;
+            bulk_load_1d(st + A_BYTES + B_BYTES, p.sfa + ((size_t)(m0 / 128) * p.sf_kblocks + koff) * 512, (uint32_t)atoms * 512u, full + s);
+            for (int nb = 0; nb < valid_nb; ++nb)
+              bulk_load_1d(st + A_BYTES + B_BYTES + SFA_BYTES + nb * KT::SF_ATOMS * 512,
+                           p.sfb + ((size_t)(n0 / 128 + nb) * p.sf_kblocks + koff) * 512, (uint32_t)atoms * 512u, full + s);
+          }
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
+      uint32_t it = 0, local = 0;                        // K tiles consumed; tiles of this CTA started
       bool ok = true;
-      for (int kt = 0; kt < p.nkt && ok; ++kt) {
-        const int s = kt % STAGES;
-        if (!mbar_wait(full + s, (uint32_t)((kt / STAGES) & 1), &s_abort, p.status, 3)) { ok = false; break; }
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
+        const uint32_t ab = local % ACC_BUFS;
+        // the epilogue must have drained this accumulator (first use of each passes at once)
+        if (!mbar_wait(tmem_empty + ab, ((local / ACC_BUFS) & 1u) ^ 1u, &s_abort, p.status, 6)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t sa = smem_u32(smem + s * STAGE_BYTES), sb = sa + A_BYTES;
-        if (MX) {
+        const uint32_t d_tmem = tmem_base + ab * BN;
+        for (int kt = 0; kt < p.nkt; ++kt, ++it) {
+          const int s = it % STAGES;
+          if (!mbar_wait(full + s, (it / STAGES) & 1u, &s_abort, p.status, 3)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * STAGE_BYTES), sb = sa + A_BYTES;
+          if (MX) {
 #pragma unroll
-          for (int a = 0; a < KT::SF_ATOMS; ++a) {
-            tmem_cp_sf(tmem_base + SFA_COL + a * 4, smem_desc_sf(sb + B_BYTES + a * 512));
+            for (int a = 0; a < KT::SF_ATOMS; ++a) {
+              tmem_cp_sf(tmem_base + SFA_COL + a * 4, smem_desc_sf(sb + B_BYTES + a * 512));
 #pragma unroll
-            for (int nb = 0; nb < BN / 128; ++nb)
-              tmem_cp_sf(tmem_base + SFB_COL + a * 4 * (BN / 128) + nb * 4, smem_desc_sf(sb + B_BYTES + SFA_BYTES + (nb * KT::SF_ATOMS + a) * 512));
+              for (int nb = 0; nb < BN / 128; ++nb)
+                tmem_cp_sf(tmem_base + SFB_COL + a * 4 * (BN / 128) + nb * 4, smem_desc_sf(sb + B_BYTES + SFA_BYTES + (nb * KT::SF_ATOMS + a) * 512));
+            }
           }
-        }
-        const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sb);
+          const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sb);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const uint32_t accum = (kt > 0 || j > 0) ? 1u : 0u;
-          if constexpr (KIND == KIND_MXF4) {
-            const uint32_t sfid = (uint32_t)(2 * (j & 1));
-            mma_ss_block_scaled<KIND>(tmem_base, da + 2 * j, db + 2 * j, p.idesc | (sfid << 29) | (sfid << 4),
-                                      tmem_base + SFA_COL + (j >> 1) * 4, tmem_base + SFB_COL + (j >> 1) * 4 * (BN / 128), accum);
-          } else if constexpr (KIND == KIND_NVF4) {
-            mma_ss_block_scaled<KIND>(tmem_base, da + 2 * j, db + 2 * j, p.idesc,
-                                      tmem_base + SFA_COL + j * 4, tmem_base + SFB_COL + j * 4 * (BN / 128), accum);
-          } else {
-            mma_ss<KIND>(tmem_base, da + 2 * j, db + 2 * j, p.idesc, accum);
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t accum = (kt > 0 || j > 0) ? 1u : 0u;
+            if constexpr (KIND == KIND_MXF4) {
+              const uint32_t sfid = (uint32_t)(2 * (j & 1));
+              mma_ss_block_scaled<KIND>(d_tmem, da + 2 * j, db + 2 * j, p.idesc | (sfid << 29) | (sfid << 4),
+                                        tmem_base + SFA_COL + (j >> 1) * 4, tmem_base + SFB_COL + (j >> 1) * 4 * (BN / 128), accum);
+            } else if constexpr (KIND == KIND_NVF4) {
+              mma_ss_block_scaled<KIND>(d_tmem, da + 2 * j, db + 2 * j, p.idesc,
+                                        tmem_base + SFA_COL + j * 4, tmem_base + SFB_COL + j * 4 * (BN / 128), accum);
+            } else {
+              mma_ss<KIND>(d_tmem, da + 2 * j, db + 2 * j, p.idesc, accum);
+            }
           }
+          tc_commit(empty + s);
         }
-        tc_commit(empty + s);
+        if (ok) tc_commit(tmem_full + ab);
       }
-      if (ok) tc_commit(tmem_full);
     }
   } else {
-    if (mbar_wait(tmem_full, 0u, &s_abort, p.status, 4)) {
+    float* sw_s = consts + (warp - 2) * 2 * BN;          // this warp's copy of the tile's per-column constants
+    float* b_s = sw_s + BN;
+    uint32_t local = 0;
+    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
+      const int m0 = (tile % tiles_m) * 128, n0 = (tile / tiles_m) * BN;
+      const uint32_t ab = local % ACC_BUFS;
+      for (int c = lane; c < BN; c += 32) {
+        const int n = n0 + c;
+        sw_s[c] = (p.scales_w != nullptr && n < p.N) ? gl_load_as_float(p.scales_w, n, p.scales_w_dtype) : 1.f;
+        b_s[c] = (p.bias != nullptr && n < p.N) ? gl_load_as_float(p.bias, n, p.out_dtype) : 0.f;
+      }
+      __syncwarp();
+      if (!mbar_wait(tmem_full + ab, (local / ACC_BUFS) & 1u, &s_abort, p.status, 4)) break;
       tc_fence_after();
-      epilogue_tile<KIND == KIND_I8>(p, tmem_base, m0, n0, BN, warp, lane, sw_s, b_s);
+      epilogue_tile<KIND == KIND_I8>(p, tmem_base + ab * BN, m0, n0, BN, warp, lane, sw_s, b_s);
+      tc_fence_before();                                  // this warp's TMEM reads are complete (tcgen05.wait::ld inside)
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tmem_empty + ab);
     }
   }
   tc_fence_before();
@@ -414,11 +446,12 @@ template <int KIND, int BN, int STAGES>
 static int launch_tma_kernel(const CUtensorMap& tmA, const CUtensorMap& tmB, const TcParams& p, cudaStream_t st) {
   using KT = KindTraits<KIND>;
   constexpr size_t stage = 128 * 128 + BN * 128 + KT::SF_ATOMS * 512 * (1 + BN / 128);
-  const size_t smem = 1024 + STAGES * stage + (2 * STAGES + 1) * 8 + 32 + 2 * BN * 4 + 16;
+  const size_t smem = 1024 + STAGES * stage + (2 * STAGES + 4) * 8 + 32 + 4 * 2 * BN * 4 + 16;
   auto kern = gl_gemm_tc_kernel<KIND, BN, STAGES>;
   if (int rc = set_smem(kern, smem)) return rc;
   const int tiles = ((p.M + 127) / 128) * ((p.N + BN - 1) / BN);
-  kern<<<tiles, 192, smem, st>>>(tmA, tmB, p);
+  const int grid = tiles < gl_num_sms() ? tiles : gl_num_sms();
+  kern<<<grid, 192, smem, st>>>(tmA, tmB, p);
   GL_LAUNCH_CHECK("gl_gemm_tc_kernel");
   return GL_OK;
 }
