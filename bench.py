@@ -30,6 +30,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 N_FEAT = K_FEAT = 8192
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel, from the ncu capture summarised in
+# profiles/gemv_a16w4_m1_8192x8192.md (algorithmic bytes: 35,700,736)
+NCU_DRAM_BYTES_PER_LAUNCH = 35734272
 GROUP = 128
 LAYERS = 32
 
@@ -158,7 +161,8 @@ def build_layers(device, n_layers, M_max, nbits=4, group=GROUP, N=N_FEAT, K=K_FE
 
 
 def time_graph(fn, steps, warmup, stream):
-    """Capture fn() once, replay warmup + steps times; returns ms per step (CUDA events on `stream`)."""
+    """Run fn() twice eagerly, capture it once in a CUDA graph on `stream`, replay it `warmup` times and return
+    the graph; the caller times `steps` replays with CUDA events on the same stream."""
     with torch.cuda.stream(stream):
         for _ in range(2):
             fn()
@@ -192,7 +196,8 @@ def main():
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        import datetime
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=datetime.timedelta(seconds=180))
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
 
@@ -301,7 +306,7 @@ def main():
                 "eager_ms_per_step": ms_eager, "eager_value": total_bytes / (ms_eager * 1e-3) / 1e9, "finite": finite},
         "gpu_launches": args.steps * LAYERS,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                     "traffic": None, "peak_kind": peak_kind, "frac_of_nominal_8000": achieved / 8000.0,
+                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH, "peak_kind": peak_kind, "frac_of_nominal_8000": achieved / 8000.0,
                      "bytes_per_launch": bytes_per_launch},
         "clocks": clocks,
     }
@@ -320,10 +325,74 @@ def main():
         except Exception as e:  # the CPU sample must not lose the GPU numbers
             result["cpu_baseline"] = {"value": None, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port", "sample": "failed: %s" % e}
     if dist is not None:
+        try:
+            tp = tensor_parallel_step(device, rank, world, dist)
+            if rank == 0:
+                result["tensor_parallel"] = tp
+        except Exception as e:  # the weak-scaling line above stands on its own
+            if rank == 0:
+                result["tensor_parallel"] = {"error": str(e)[:200]}
         dist.barrier()
         dist.destroy_process_group()
     if rank == 0:
         print(json.dumps(result))
+
+
+def tensor_parallel_step(device, rank, world, dist, steps=30):
+    """Decode step (M = 1) through the seven A16W4 linears of one Llama-70B decoder layer, tensor-parallel over
+    all ranks: column-parallel qkv and gate/up, row-parallel o_proj and down_proj with one NCCL all-reduce each.
+    Device time per step, max over ranks."""
+    from gemlite_b200 import tp
+    hidden, inter, heads, kv_heads, head_dim = 8192, 28672, 64, 8, 128
+    blk = tp.LlamaLinears(hidden, inter, heads, kv_heads, head_dim, world, rank, device, seed=11)
+    x = torch.randn(1, hidden, device=device, dtype=torch.bfloat16) * 0.1
+    for _ in range(5):
+        y = blk(x)
+    dist.barrier()
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        y = blk(x)
+    e1.record()
+    torch.cuda.synchronize(device)
+    ms_eager = e0.elapsed_time(e1) / steps
+    # the same step captured once in a CUDA graph (NCCL all-reduces included) and replayed: device-bound time
+    ms_graph, graph = None, None
+    side = torch.cuda.Stream(device)
+    try:
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                y = blk(x)
+        side.synchronize()
+    except Exception:
+        graph = None
+    # replay only if every rank captured: a rank replaying all-reduces alone would wait for ever
+    ok = torch.tensor([0.0 if graph is None else 1.0], device=device, dtype=torch.float64)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if ok.item() == 1.0:
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                graph.replay()
+            side.synchronize()
+            dist.barrier()
+            e0.record(side)
+            for _ in range(steps):
+                graph.replay()
+            e1.record(side)
+            side.synchronize()
+        ms_graph = e0.elapsed_time(e1) / steps
+    t = torch.tensor([ms_eager, ms_graph if ms_graph is not None else 0.0], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_eager = t[0].item()
+    ms_graph = t[1].item() if ms_graph is not None else None
+    weights = (heads + 2 * kv_heads) * head_dim * hidden + hidden * heads * head_dim + 3 * inter * hidden   # elements
+    return {"workload": "Llama-70B decoder-layer linears, A16W4 gs128, M=1, tp%d" % world,
+            "ms_per_step": ms_graph if ms_graph is not None else ms_eager, "ms_per_step_eager": ms_eager,
+            "timing": "CUDA graph replay" if ms_graph is not None else "eager", "all_reduces_per_step": 2, "finite": bool(torch.isfinite(y.float()).all()),
+            "packed_weight_GB_per_step_all_ranks": weights / 2 / 1e9}
 
 
 def sweep(device, layers, stream, hbm_peak, bf16_peak):
@@ -409,14 +478,35 @@ def sweep_gemm(device):
         return P(device=str(device), dtype=torch.bfloat16).from_linear(lin), K, N
 
     res = []
+    stream = torch.cuda.Stream(device)
     for fmt, Ms in (("A16W4", (64, 4096)), ("FP8", (1, 4096)), ("MXFP4", (1, 4096)), ("NVFP4", (1, 4096))):
         try:
             layer, K, N = make(fmt)
+            wbytes = N * K // (1 if fmt == "FP8" else 2)
             for M in Ms:
                 x = torch.randn(M, K, dtype=torch.bfloat16, device=device)
-                ms = timed(lambda: layer(x))
+                row = {"format": fmt, "M": M, "N": N, "K": K}
+                if M <= 16:
+                    # decode size: host launch overhead would hide the kernel, so the forwards of several distinct
+                    # layers (together larger than L2) are captured in one CUDA graph and replayed
+                    n_layers = max(2, -(-160 * 1024 * 1024 // wbytes))
+                    layers = [layer] + [make(fmt)[0] for _ in range(n_layers - 1)]
+                    graph = time_graph(lambda: [l(x) for l in layers], 10, 3, stream)
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    with torch.cuda.stream(stream):
+                        e0.record(stream)
+                        for _ in range(10):
+                            graph.replay()
+                        e1.record(stream)
+                        stream.synchronize()
+                    ms = e0.elapsed_time(e1) / 10 / n_layers
+                    row.update({"ms": ms, "GBps": wbytes / ms / 1e6, "timing": "CUDA graph over %d distinct layers" % n_layers})
+                    del layers, graph
+                else:
+                    ms = timed(lambda: layer(x))
+                    row["ms"] = ms
                 tf = 2.0 * M * N * K / ms / 1e9
-                row = {"format": fmt, "M": M, "N": N, "K": K, "ms": ms, "TFLOPs": tf, "frac_dense_nominal": tf / dense_peak[fmt]}
+                row.update({"TFLOPs": tf, "frac_dense_nominal": tf / dense_peak[fmt]})
                 r = ref.get("%s_%dx%d_M%d" % (fmt, K if fmt == "FP8" else N, N if fmt == "FP8" else K, M))
                 if r:
                     row["ref_triton_ms"] = r["min_ms"]

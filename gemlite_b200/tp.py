@@ -95,10 +95,11 @@ class LlamaLinears(torch.nn.Module):
         self.q_local = n_heads * head_dim // world
         self.kv_local = n_kv_heads * head_dim // world
         self.inter_local = intermediate // world
-        g = torch.Generator().manual_seed(seed)
+        gen_dev = torch.device(device)
+        g = torch.Generator(device=gen_dev).manual_seed(seed)   # same seed on every rank: all ranks shard the same matrices
 
         def w(n, k):
-            return (torch.randn(n, k, generator=g) * 0.02).to(dtype)
+            return (torch.randn(n, k, generator=g, device=gen_dev) * 0.02).to(dtype)
 
         def col(*mats):   # each matrix is column-sharded on its own, the shards are fused per rank
             parts = [quantize_affine_minmax(m, 4, group_size) for m in mats]
