@@ -44,6 +44,7 @@ int gl_gemv_stream_launch(const gl_matmul_args* a, cudaStream_t st);
 int gl_generic_launch(const gl_matmul_args* a, cudaStream_t st);
 int gl_validate_matmul_args(const gl_matmul_args* a);
 int gl_gemm_tc_supported(const gl_matmul_args* a);
+uint64_t gl_gemm_tc_workspace(const gl_matmul_args* a);
 int gl_gemm_tc_launch(const gl_matmul_args* a, cudaStream_t st);
 
 #ifdef __CUDACC__

@@ -21,6 +21,7 @@
 //           factors are copied shared -> TMEM with tcgen05.cp from 128-row x 4-scale atoms (512 bytes)
 #include "gl_tc_common.cuh"
 #include <string.h>
+#include <type_traits>
 #include <stdlib.h>
 
 using namespace gltc;
@@ -28,7 +29,9 @@ using namespace gltc;
 namespace {
 
 constexpr int kNumEpiWarps = 4;
-constexpr int kNumDeqWarps = 8;
+// dequantiser warps of the A16Wn kernel (16 for 256-column tiles measured no faster: the stage is bound by
+// shared-memory traffic, 112 KB per 128 x 256 x 64 step, not by the unpack instructions)
+constexpr int deq_warps(int) { return 8; }
 
 struct TcParams {
   int M, N, K, nkt;
@@ -39,6 +42,8 @@ struct TcParams {
   const void* scales_w; int scales_w_dtype;     // [N] channel scales or null
   const float* meta_scale;                      // tensor scale (NVFP4) or null
   int* status;
+  // split-K (A16Wn, few tiles): fp32 partial tiles [splits][M][N] and one arrival counter per tile in the workspace
+  int splits; float* partials; unsigned int* counters;
   // block-scaled formats: scale-factor atoms [rows/128][kblocks][512 B]
   const uint8_t* sfa; const uint8_t* sfb; int sf_kblocks;
   // A16Wn
@@ -64,6 +69,45 @@ __device__ __forceinline__ void stage_epilogue_consts(const TcParams& p, float* 
   }
 }
 
+// one row's 32-column chunk: out = v * rowscale * s_w + bias, cast and stored (vector stores when the chunk is whole)
+__device__ __forceinline__ void finish_row_chunk(const TcParams& p, int m, int nb, float (&v)[32], float rowscale, const float* sw, const float* bs) {
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    const float4 s4v = *reinterpret_cast<const float4*>(sw + 4 * q);
+    const float4 b4v = *reinterpret_cast<const float4*>(bs + 4 * q);
+    const float s4[4] = {s4v.x, s4v.y, s4v.z, s4v.w}, b4[4] = {b4v.x, b4v.y, b4v.z, b4v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[4 * q + j] = fmaf(v[4 * q + j] * rowscale, s4[j], b4[j]);
+  }
+  const size_t o = (size_t)m * p.N + nb;
+  const bool full = (nb + 32 <= p.N);
+  if (p.out_dtype == GL_BF16 || p.out_dtype == GL_FP16) {
+    if (full && (p.N % 8 == 0)) {
+      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.out) + o);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (p.out_dtype == GL_BF16) { __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * q + 2 * j], v[8 * q + 2 * j + 1]); w[j] = *reinterpret_cast<uint32_t*>(&h); }
+          else { __half2 h = __floats2half2_rn(v[8 * q + 2 * j], v[8 * q + 2 * j + 1]); w[j] = *reinterpret_cast<uint32_t*>(&h); }
+        }
+        dst[q] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    } else {
+      for (int i = 0; i < 32 && nb + i < p.N; ++i) gl_store_out(p.out, o + i, v[i], p.out_dtype);
+    }
+  } else {
+    if (full && (p.N % 4 == 0)) {
+      float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + o);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+    } else {
+      for (int i = 0; i < 32 && nb + i < p.N; ++i) reinterpret_cast<float*>(p.out)[o + i] = v[i];
+    }
+  }
+}
+
 template <bool INT_ACC>
 __device__ __forceinline__ void epilogue_tile(const TcParams& p, uint32_t tmem_d, int m0, int n0, int BN, int epi_warp, int lane,
                                               const float* sw_s, const float* b_s) {
@@ -78,44 +122,56 @@ __device__ __forceinline__ void epilogue_tile(const TcParams& p, uint32_t tmem_d
     if (m >= p.M) continue;
     float v[32];
 #pragma unroll
-    for (int q = 0; q < 8; ++q) {
-      const float4 sw = *reinterpret_cast<const float4*>(sw_s + c0 + 4 * q);
-      const float4 bb = *reinterpret_cast<const float4*>(b_s + c0 + 4 * q);
-      const float s4[4] = {sw.x, sw.y, sw.z, sw.w}, b4[4] = {bb.x, bb.y, bb.z, bb.w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float a = INT_ACC ? (float)(int32_t)rr[4 * q + j] : __uint_as_float(rr[4 * q + j]);
-        v[4 * q + j] = fmaf(a * rowscale, s4[j], b4[j]);
-      }
-    }
+    for (int i = 0; i < 32; ++i) v[i] = INT_ACC ? (float)(int32_t)rr[i] : __uint_as_float(rr[i]);
+    finish_row_chunk(p, m, n0 + c0, v, rowscale, sw_s + c0, b_s + c0);
+  }
+}
+
+// split-K: this CTA's fp32 partial tile goes to the workspace [split][M][N] ...
+__device__ __forceinline__ void epilogue_store_partial(const TcParams& p, uint32_t tmem_d, int m0, int n0, int BN, int epi_warp, int lane, int split) {
+  const int quad = epi_warp & 3;
+  const int m = m0 + quad * 32 + lane;
+  float* part = p.partials + ((size_t)split * p.M + m) * p.N;
+  for (int c0 = 0; c0 < BN; c0 += 32) {
+    if (n0 + c0 >= p.N) break;
+    uint32_t rr[32];
+    tmem_ld_32x32(tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, rr);
+    if (m >= p.M) continue;
     const int nb = n0 + c0;
-    const size_t o = (size_t)m * p.N + nb;
-    const bool full = (nb + 32 <= p.N);
-    if (p.out_dtype == GL_BF16 || p.out_dtype == GL_FP16) {
-      if (full && (p.N % 8 == 0)) {
-        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.out) + o);
+    if (nb + 32 <= p.N && p.N % 4 == 0) {
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          uint32_t w[4];
+      for (int q = 0; q < 8; ++q)
+        __stcg(reinterpret_cast<float4*>(part + nb) + q, make_float4(__uint_as_float(rr[4 * q]), __uint_as_float(rr[4 * q + 1]), __uint_as_float(rr[4 * q + 2]), __uint_as_float(rr[4 * q + 3])));
+    } else {
+      for (int i = 0; i < 32 && nb + i < p.N; ++i) __stcg(part + nb + i, __uint_as_float(rr[i]));
+    }
+  }
+}
+// ... and the CTA that arrives last at the tile's counter adds the partial tiles in split order and finishes the rows
+__device__ __forceinline__ void epilogue_reduce_partials(const TcParams& p, int m0, int n0, int BN, int epi_warp, int lane,
+                                                         const float* sw_s, const float* b_s) {
+  const int quad = epi_warp & 3;
+  const int m = m0 + quad * 32 + lane;
+  if (m >= p.M) return;
+  for (int c0 = 0; c0 < BN; c0 += 32) {
+    const int nb = n0 + c0;
+    if (nb >= p.N) break;
+    float v[32];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            if (p.out_dtype == GL_BF16) { __nv_bfloat162 h = __floats2bfloat162_rn(v[8 * q + 2 * j], v[8 * q + 2 * j + 1]); w[j] = *reinterpret_cast<uint32_t*>(&h); }
-            else { __half2 h = __floats2half2_rn(v[8 * q + 2 * j], v[8 * q + 2 * j + 1]); w[j] = *reinterpret_cast<uint32_t*>(&h); }
-          }
-          dst[q] = make_uint4(w[0], w[1], w[2], w[3]);
+    for (int i = 0; i < 32; ++i) v[i] = 0.f;
+    for (int sidx = 0; sidx < p.splits; ++sidx) {
+      const float* part = p.partials + ((size_t)sidx * p.M + m) * p.N + nb;
+      if (nb + 32 <= p.N && p.N % 4 == 0) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const float4 t = __ldcg(reinterpret_cast<const float4*>(part) + q);
+          v[4 * q] += t.x; v[4 * q + 1] += t.y; v[4 * q + 2] += t.z; v[4 * q + 3] += t.w;
         }
       } else {
-        for (int i = 0; i < 32 && nb + i < p.N; ++i) gl_store_out(p.out, o + i, v[i], p.out_dtype);
-      }
-    } else {
-      if (full && (p.N % 4 == 0)) {
-        float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + o);
-#pragma unroll
-        for (int q = 0; q < 8; ++q) dst[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-      } else {
-        for (int i = 0; i < 32 && nb + i < p.N; ++i) reinterpret_cast<float*>(p.out)[o + i] = v[i];
+        for (int i = 0; i < 32 && nb + i < p.N; ++i) v[i] += __ldcg(part + i);
       }
     }
+    finish_row_chunk(p, m, nb, v, 1.f, sw_s + c0, b_s + c0);
   }
 }
 
@@ -284,7 +340,7 @@ template <> struct H2<__half> {
 };
 
 template <typename XT, int NB, int BN, int STAGES>
-__global__ void __launch_bounds__(448, 1) gl_gemm_tc_a16wn_kernel(const __grid_constant__ CUtensorMap tmA,
+__global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_kernel(const __grid_constant__ CUtensorMap tmA,
                                                                   const __grid_constant__ CUtensorMap tmW, const TcParams p) {
   constexpr int E = 32 / NB;                           // k values per packed word
   constexpr int WROWS = 64 / E;                        // packed rows per 64-wide K tile (8 for 4-bit)
@@ -310,11 +366,16 @@ __global__ void __launch_bounds__(448, 1) gl_gemm_tc_a16wn_kernel(const __grid_c
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (p.M + 127) / 128;
   const int m0 = (blockIdx.x % tiles_m) * 128, n0 = (blockIdx.x / tiles_m) * BN;
+  // K tiles of this CTA: blockIdx.y picks one of p.splits equal ranges (the last one may be shorter)
+  const int kt_per = (p.nkt + p.splits - 1) / p.splits;
+  const int kt0 = blockIdx.y * kt_per;
+  const int nloc = min(kt_per, p.nkt - kt0);
+  __shared__ int s_last;
   stage_epilogue_consts(p, sw_s, b_s, n0, BN);
 
   if (threadIdx.x == 0) {
     s_abort = 0;
-    for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(wfull + s, 1); mbar_init(bready + s, kNumDeqWarps); mbar_init(empty + s, 1); }
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(wfull + s, 1); mbar_init(bready + s, deq_warps(BN)); mbar_init(empty + s, 1); }
     mbar_init(tmem_full, 1);
     fence_barrier_init();
     prefetch_tmap(&tmA);
@@ -328,9 +389,9 @@ __global__ void __launch_bounds__(448, 1) gl_gemm_tc_a16wn_kernel(const __grid_c
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int kt = 0; kt < p.nkt; ++kt) {
-        const int s = kt % STAGES;
-        if (!mbar_wait(empty + s, (uint32_t)(((kt / STAGES) & 1) ^ 1), &s_abort, p.status, 2)) break;
+      for (int i = 0; i < nloc; ++i) {
+        const int s = i % STAGES, kt = kt0 + i;
+        if (!mbar_wait(empty + s, (uint32_t)(((i / STAGES) & 1) ^ 1), &s_abort, p.status, 2)) break;
         unsigned char* st = smem + s * STAGE_BYTES;
         mbar_expect_tx(wfull + s, W_BYTES);
         tma_load_2d(st + A_BYTES + B_BYTES, &tmW, wfull + s, n0, kt * WROWS);
@@ -341,15 +402,15 @@ __global__ void __launch_bounds__(448, 1) gl_gemm_tc_a16wn_kernel(const __grid_c
   } else if (warp == 1) {
     if (lane == 0) {
       bool ok = true;
-      for (int kt = 0; kt < p.nkt && ok; ++kt) {
-        const int s = kt % STAGES;
-        const uint32_t ph = (uint32_t)((kt / STAGES) & 1);
+      for (int i = 0; i < nloc && ok; ++i) {
+        const int s = i % STAGES;
+        const uint32_t ph = (uint32_t)((i / STAGES) & 1);
         if (!mbar_wait(full + s, ph, &s_abort, p.status, 3) || !mbar_wait(bready + s, ph, &s_abort, p.status, 5)) { ok = false; break; }
         tc_fence_after();
         const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
         const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sa + A_BYTES);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) mma_ss<KIND_F16>(tmem_base, da + 2 * j, db + 2 * j, p.idesc, (kt > 0 || j > 0) ? 1u : 0u);
+        for (int j = 0; j < 4; ++j) mma_ss<KIND_F16>(tmem_base, da + 2 * j, db + 2 * j, p.idesc, (i > 0 || j > 0) ? 1u : 0u);
         tc_commit(empty + s);
       }
       if (ok) tc_commit(tmem_full);
@@ -357,13 +418,29 @@ __global__ void __launch_bounds__(448, 1) gl_gemm_tc_a16wn_kernel(const __grid_c
   } else if (warp < 2 + kNumEpiWarps) {
     if (mbar_wait(tmem_full, 0u, &s_abort, p.status, 4)) {
       tc_fence_after();
-      epilogue_tile<false>(p, tmem_base, m0, n0, BN, warp, lane, sw_s, b_s);
+      if (p.splits == 1) {
+        epilogue_tile<false>(p, tmem_base, m0, n0, BN, warp, lane, sw_s, b_s);
+      } else {
+        epilogue_store_partial(p, tmem_base, m0, n0, BN, warp, lane, blockIdx.y);
+        __threadfence();
+        asm volatile("bar.sync 1, %0;" ::"n"(kNumEpiWarps * 32) : "memory");        // the four epilogue warps
+        if (warp == 2 && lane == 0) {
+          const unsigned int prev = atomicAdd(p.counters + blockIdx.x, 1u);
+          s_last = (prev == (unsigned int)(p.splits - 1)) ? 1 : 0;
+          if (s_last) p.counters[blockIdx.x] = 0u;                                 // ready for the next launch
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(kNumEpiWarps * 32) : "memory");
+        if (s_last) {
+          __threadfence();
+          epilogue_reduce_partials(p, m0, n0, BN, warp, lane, sw_s, b_s);
+        }
+      }
     }
   } else {
     // dequant warps: warp dw owns 32 columns (BN = 256) or 32 columns x half of the packed rows (BN = 128)
     const int dw = warp - 2 - kNumEpiWarps;
     constexpr int CBLOCKS = BN / 32;                       // 32-column blocks in the tile
-    constexpr int RSPLIT = kNumDeqWarps / CBLOCKS;         // warps sharing one column block (1 or 2)
+    constexpr int RSPLIT = deq_warps(BN) / CBLOCKS;        // warps sharing one column block (1 or 2)
     constexpr int RPW = WROWS / RSPLIT;                    // packed rows per warp
     const int nl = (dw % CBLOCKS) * 32 + lane;             // column inside the tile
     const int c_begin = (dw / CBLOCKS) * RPW;
@@ -375,56 +452,78 @@ __global__ void __launch_bounds__(448, 1) gl_gemm_tc_a16wn_kernel(const __grid_c
     int g_cur = -1;
     h2 s2 = H2<XT>::from_float(1.f), z2 = H2<XT>::from_float(0.f);
     if (p.zero_is_scalar && p.gzeros) z2 = H2<XT>::from_float((float)(*reinterpret_cast<const int32_t*>(p.gzeros)));
-    for (int kt = 0; kt < p.nkt; ++kt) {
-      const int s = kt % STAGES;
-      if (!mbar_wait(wfull + s, (uint32_t)((kt / STAGES) & 1), &s_abort, p.status, 6)) break;
+    const bool need_s = p.W_group_mode >= 2, need_z = (p.W_group_mode == 1 || p.W_group_mode >= 3) && !p.zero_is_scalar;
+    const int n_groups = (p.K + p.group_size - 1) / p.group_size;
+    XT s_next = XT(1.f), z_next = XT(0.f);
+    if (n_ok) {                                          // the first group of this CTA's K range
+      const size_t g_first = (size_t)((kt0 * 64) / p.group_size);
+      if (need_s) s_next = reinterpret_cast<const XT*>(p.gscales)[g_first * p.N + n];
+      if (need_z) z_next = reinterpret_cast<const XT*>(p.gzeros)[g_first * p.N + n];
+    }
+    for (int i = 0; i < nloc; ++i) {
+      const int s = i % STAGES, kt = kt0 + i;
+      if (!mbar_wait(wfull + s, (uint32_t)((i / STAGES) & 1), &s_abort, p.status, 6)) break;
       const int g = (kt * 64) / p.group_size;
       if (g != g_cur) {
+        // this group's scale / zero were requested one group ahead; request the next group's now so that their
+        // latency (a first touch in DRAM for every CTA that shares the column tile) is off the critical path
         g_cur = g;
-        if (n_ok) {
-          if (p.W_group_mode >= 2) { const XT v = reinterpret_cast<const XT*>(p.gscales)[(size_t)g * p.N + n]; s2 = h2(v, v); }
-          if ((p.W_group_mode == 1 || p.W_group_mode >= 3) && !p.zero_is_scalar) { const XT v = reinterpret_cast<const XT*>(p.gzeros)[(size_t)g * p.N + n]; z2 = h2(v, v); }
+        s2 = h2(s_next, s_next);
+        if (!p.zero_is_scalar) z2 = h2(z_next, z_next);
+        const int gn = g + 1;
+        if (n_ok && gn < n_groups) {
+          if (need_s) s_next = reinterpret_cast<const XT*>(p.gscales)[(size_t)gn * p.N + n];
+          if (need_z) z_next = reinterpret_cast<const XT*>(p.gzeros)[(size_t)gn * p.N + n];
         }
       }
       unsigned char* st = smem + s * STAGE_BYTES;
       const uint32_t* wst = reinterpret_cast<const uint32_t*>(st + A_BYTES + B_BYTES);
       unsigned char* brow = st + A_BYTES + nl * 128;
-      const int wgm = p.W_group_mode;
+      // the mode is decided once per K tile, outside the unrolled loops: a branch per pair would serialise them
+      auto unpack_tile = [&](auto fma_tag) {
+        constexpr bool FMA = decltype(fma_tag)::value;
+        const h2 zs2 = (p.W_group_mode == 1 || p.W_group_mode == 3) ? z2 : H2<XT>::from_float(0.f);
+        const h2 ss2 = (p.W_group_mode >= 2) ? s2 : H2<XT>::from_float(1.f);
+        uint32_t wv[RPW];                                    // all packed words first: the stores below may alias them for the compiler
 #pragma unroll
-      for (int cc = 0; cc < RPW; ++cc) {
-        const int c = c_begin + cc;                        // packed row inside the K tile
-        const uint32_t w = wst[c * BN + nl];
-        // pair a = (field a, field a + HALF), dequantised exactly as dequantize() does in the scale dtype
-        uint32_t P[HALF];
+        for (int cc = 0; cc < RPW; ++cc) wv[cc] = wst[(c_begin + cc) * BN + nl];
 #pragma unroll
-        for (int a = 0; a < HALF; ++a) {
-          uint32_t bits = ((w >> (NB * a)) & FMASK) | kMagic;
-          h2 q = __hsub2(*reinterpret_cast<h2*>(&bits), magic);            // exact integer code
-          if (wgm == 4) q = __hfma2(q, s2, z2);
-          else if (wgm == 3) q = __hmul2(__hsub2(q, z2), s2);
-          else if (wgm == 2) q = __hmul2(q, s2);
-          else if (wgm == 1) q = __hsub2(q, z2);
-          P[a] = *reinterpret_cast<uint32_t*>(&q);
-        }
-        // natural k order: low halves are fields 0..HALF-1, high halves fields HALF..2*HALF-1
-        uint32_t L[HALF / 2], Hh[HALF / 2];
+        for (int cc = 0; cc < RPW; ++cc) {
+          const int c = c_begin + cc;                        // packed row inside the K tile
+          const uint32_t w = wv[cc];
+          // pair a = (field a, field a + HALF), dequantised exactly as dequantize() does in the scale dtype
+          uint32_t P[HALF];
 #pragma unroll
-        for (int j = 0; j < HALF / 2; ++j) {
-          L[j] = __byte_perm(P[2 * j], P[2 * j + 1], 0x5410);
-          Hh[j] = __byte_perm(P[2 * j], P[2 * j + 1], 0x7632);
-        }
-        const int chunk0 = c * (E / 8);
-        if constexpr (NB == 4) {
-          *reinterpret_cast<uint4*>(brow + (((chunk0) ^ (nl & 7)) << 4)) = make_uint4(L[0], L[1], Hh[0], Hh[1]);
-        } else {
-          constexpr int CH = HALF / 8;                     // chunks per half (1 for 2-bit, 2 for 1-bit)
+          for (int a = 0; a < HALF; ++a) {
+            uint32_t bits = ((w >> (NB * a)) & FMASK) | kMagic;
+            h2 q = __hsub2(*reinterpret_cast<h2*>(&bits), magic);            // exact integer code
+            // mode 4: q*s + z' in one rounding; the other modes as (q - z) * s with z = 0 / s = 1 where absent:
+            // the same roundings as the reference's dequantize() (triton_kernels/utils.py:73-105)
+            if (FMA) q = __hfma2(q, s2, z2);
+            else q = __hmul2(__hsub2(q, zs2), ss2);
+            P[a] = *reinterpret_cast<uint32_t*>(&q);
+          }
+          // natural k order: low halves are fields 0..HALF-1, high halves fields HALF..2*HALF-1
+          uint32_t L[HALF / 2], Hh[HALF / 2];
 #pragma unroll
-          for (int ch = 0; ch < CH; ++ch) {
-            *reinterpret_cast<uint4*>(brow + (((chunk0 + ch) ^ (nl & 7)) << 4)) = make_uint4(L[4 * ch], L[4 * ch + 1], L[4 * ch + 2], L[4 * ch + 3]);
-            *reinterpret_cast<uint4*>(brow + (((chunk0 + CH + ch) ^ (nl & 7)) << 4)) = make_uint4(Hh[4 * ch], Hh[4 * ch + 1], Hh[4 * ch + 2], Hh[4 * ch + 3]);
+          for (int j = 0; j < HALF / 2; ++j) {
+            L[j] = __byte_perm(P[2 * j], P[2 * j + 1], 0x5410);
+            Hh[j] = __byte_perm(P[2 * j], P[2 * j + 1], 0x7632);
+          }
+          const int chunk0 = c * (E / 8);
+          if constexpr (NB == 4) {
+            *reinterpret_cast<uint4*>(brow + (((chunk0) ^ (nl & 7)) << 4)) = make_uint4(L[0], L[1], Hh[0], Hh[1]);
+          } else {
+            constexpr int CH = HALF / 8;                     // chunks per half (1 for 2-bit, 2 for 1-bit)
+#pragma unroll
+            for (int ch = 0; ch < CH; ++ch) {
+              *reinterpret_cast<uint4*>(brow + (((chunk0 + ch) ^ (nl & 7)) << 4)) = make_uint4(L[4 * ch], L[4 * ch + 1], L[4 * ch + 2], L[4 * ch + 3]);
+              *reinterpret_cast<uint4*>(brow + (((chunk0 + CH + ch) ^ (nl & 7)) << 4)) = make_uint4(Hh[4 * ch], Hh[4 * ch + 1], Hh[4 * ch + 2], Hh[4 * ch + 3]);
+            }
           }
         }
-      }
+      };
+      if (p.W_group_mode == 4) unpack_tile(std::true_type{}); else unpack_tile(std::false_type{});
       fence_proxy_async_smem();                            // generic-proxy stores -> visible to the tensor core
       __syncwarp();
       if (lane == 0) mbar_arrive(bready + s);
@@ -464,7 +563,7 @@ static int launch_a16_kernel(const CUtensorMap& tmA, const CUtensorMap& tmW, con
   auto kern = gl_gemm_tc_a16wn_kernel<XT, NB, BN, STAGES>;
   if (int rc = set_smem(kern, smem)) return rc;
   const int tiles = ((p.M + 127) / 128) * ((p.N + BN - 1) / BN);
-  kern<<<tiles, 448, smem, st>>>(tmA, tmW, p);
+  kern<<<dim3(tiles, p.splits), (6 + deq_warps(BN)) * 32, smem, st>>>(tmA, tmW, p);
   GL_LAUNCH_CHECK("gl_gemm_tc_a16wn_kernel");
   return GL_OK;
 }
@@ -516,21 +615,54 @@ static TcPath classify(const gl_matmul_args* a) {
 
 int gl_gemm_tc_supported(const gl_matmul_args* a) { return classify(a) != TC_NONE; }
 
+static int tc_tile_n(const gl_matmul_args* a) {
+  return (a->N >= 256 && ((int64_t)((a->M + 127) / 128) * ((a->N + 255) / 256) >= 96)) ? 256 : 128;
+}
+
+// K splits of the A16Wn kernel: when the tiles alone leave more than half of the SMs idle, the K range is divided
+// so that about one CTA per SM runs; every split gets at least 8 K tiles and none is empty
+static int a16_splits(const gl_matmul_args* a) {
+  const int BN = tc_tile_n(a);
+  const int64_t tiles = (int64_t)((a->M + 127) / 128) * ((a->N + BN - 1) / BN);
+  const int nkt = (a->K + 63) / 64, sms = gl_num_sms();
+  if (tiles * 2 > sms || tiles > 16384 || nkt < 16) return 1;
+  int s = (int)(sms / tiles);
+  if (s > 8) s = 8;
+  if (s > nkt / 8) s = nkt / 8;
+  if (s < 1) s = 1;
+  while (s > 1 && (s - 1) * ((nkt + s - 1) / s) >= nkt) --s;
+  return s;
+}
+
+uint64_t gl_gemm_tc_workspace(const gl_matmul_args* a) {
+  uint64_t need = gl_matmul_counter_bytes();
+  if (classify(a) == TC_A16WN) {
+    const int s = a16_splits(a);
+    if (s > 1) need += (uint64_t)s * a->M * a->N * sizeof(float);
+  }
+  return need;
+}
+
 int gl_gemm_tc_launch(const gl_matmul_args* a, cudaStream_t st) {
   const TcPath path = classify(a);
   if (path == TC_NONE) GL_FAIL(GL_E_UNSUPPORTED, "gl_matmul: no tensor-core kernel for this problem");
-  if (a->workspace == nullptr || a->workspace_bytes < gl_matmul_counter_bytes())
-    GL_FAIL(GL_E_WORKSPACE, "gl_matmul: workspace of %llu bytes needed", (unsigned long long)gl_matmul_counter_bytes());
+  if (a->workspace == nullptr || a->workspace_bytes < gl_gemm_tc_workspace(a))
+    GL_FAIL(GL_E_WORKSPACE, "gl_matmul: workspace of %llu bytes needed", (unsigned long long)gl_gemm_tc_workspace(a));
+  if ((uintptr_t)a->workspace & 15) GL_FAIL(GL_E_INVALID, "gl_matmul: workspace must be 16-byte aligned");
   TcParams p;
   memset(&p, 0, sizeof(p));
+  p.splits = 1;
   p.M = a->M; p.N = a->N; p.K = a->K;
   p.out = a->out; p.out_dtype = a->out_dtype; p.bias = a->bias;
   p.status = reinterpret_cast<int*>(reinterpret_cast<char*>(a->workspace) + gl_matmul_counter_bytes() - 256);
   p.meta_scale = nullptr;
-  const int BN = (a->N >= 256 && ((int64_t)((a->M + 127) / 128) * ((a->N + 255) / 256) >= 96)) ? 256 : 128;
+  const int BN = tc_tile_n(a);
   CUtensorMap tmA, tmB;
   if (path == TC_A16WN) {
     p.nkt = (a->K + 63) / 64;
+    p.splits = a16_splits(a);
+    p.counters = reinterpret_cast<unsigned int*>(a->workspace);
+    p.partials = reinterpret_cast<float*>(reinterpret_cast<char*>(a->workspace) + gl_matmul_counter_bytes());
     p.idesc = gl_idesc(1, a->x_dtype == GL_BF16 ? 1 : 0, a->x_dtype == GL_BF16 ? 1 : 0, 128, BN);
     if (a->channel_scale_mode == 1) { p.scales_w = a->scales; p.scales_w_dtype = a->meta_dtype; }
     p.gscales = a->scales; p.gzeros = a->zeros; p.group_size = a->group_size; p.W_group_mode = a->W_group_mode; p.zero_is_scalar = a->zero_is_scalar;
