@@ -448,7 +448,7 @@ def sweep_gemm(device):
     except Exception:
         pass
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.int8, device=device)
-    dense_peak = {"A16W4": 2250.0, "FP8": 4500.0, "MXFP4": 9000.0, "NVFP4": 9000.0}     # nominal dense TFLOP/s
+    dense_peak = {"A16W4": 2250.0, "A16W2": 2250.0, "FP8": 4500.0, "MXFP4": 9000.0, "NVFP4": 9000.0}     # nominal dense TFLOP/s
 
     def timed(fn, reps=10):
         for _ in range(3):
@@ -465,12 +465,14 @@ def sweep_gemm(device):
 
     def make(fmt):
         g = torch.Generator(device=device).manual_seed(7)
-        if fmt == "A16W4":
+        if fmt in ("A16W4", "A16W2"):
             N = K = 8192
-            W_q = torch.randint(0, 16, (N, K), generator=g, device=device, dtype=torch.int32).to(torch.uint8)
-            sc = (torch.randn(N * K // 128, 1, generator=g, device=device).abs() * 0.02).to(torch.bfloat16)
-            z = (torch.rand(N * K // 128, 1, generator=g, device=device) * 15).to(torch.bfloat16)
-            return helper.A16W4_HQQ_INT(device=str(device), dtype=torch.bfloat16).from_weights(W_q, sc, z), K, N
+            nbits, gs = (4, 128) if fmt == "A16W4" else (2, 64)
+            W_q = torch.randint(0, 2 ** nbits, (N, K), generator=g, device=device, dtype=torch.int32).to(torch.uint8)
+            sc = (torch.randn(N * K // gs, 1, generator=g, device=device).abs() * 0.02).to(torch.bfloat16)
+            z = (torch.rand(N * K // gs, 1, generator=g, device=device) * (2 ** nbits - 1)).to(torch.bfloat16)
+            b = (torch.randn(N, generator=g, device=device) * 0.01).to(torch.bfloat16)
+            return helper.A16Wn_HQQ_INT(device=str(device), dtype=torch.bfloat16, W_nbits=nbits).from_weights(W_q, sc, z, bias=b), K, N
         K, N = (4096, 14336) if fmt == "FP8" else (16384, 16384)
         lin = torch.nn.Linear(K, N, bias=False, dtype=torch.bfloat16, device=device)
         lin.weight.data.normal_(0, 0.02, generator=g)
@@ -479,15 +481,16 @@ def sweep_gemm(device):
 
     res = []
     stream = torch.cuda.Stream(device)
-    for fmt, Ms in (("A16W4", (64, 4096)), ("FP8", (1, 4096)), ("MXFP4", (1, 4096)), ("NVFP4", (1, 4096))):
+    for fmt, Ms in (("A16W4", (64, 256, 1024, 4096, 8192)), ("A16W2", (1, 16, 64, 256, 1024, 4096, 8192)), ("FP8", (1, 16, 128, 1024, 4096)),
+                    ("MXFP4", (1, 64, 512, 4096, 16384)), ("NVFP4", (1, 64, 512, 4096, 16384))):
         try:
             layer, K, N = make(fmt)
-            wbytes = N * K // (1 if fmt == "FP8" else 2)
+            wbytes = N * K // {"FP8": 1, "A16W2": 4}.get(fmt, 2)
             for M in Ms:
                 x = torch.randn(M, K, dtype=torch.bfloat16, device=device)
                 row = {"format": fmt, "M": M, "N": N, "K": K}
-                if M <= 16:
-                    # decode size: host launch overhead would hide the kernel, so the forwards of several distinct
+                if M <= 512:
+                    # small batch: host launch overhead would hide the kernels, so the forwards of several distinct
                     # layers (together larger than L2) are captured in one CUDA graph and replayed
                     n_layers = max(2, -(-160 * 1024 * 1024 // wbytes))
                     layers = [layer] + [make(fmt)[0] for _ in range(n_layers - 1)]

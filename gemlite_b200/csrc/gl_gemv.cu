@@ -493,6 +493,7 @@ __global__ void __launch_bounds__(MT == 1 ? 512 : 256, 1) gl_gemv_warp_kernel(co
   float* part = reinterpret_cast<float*>(smem_raw + (size_t)s_in * xs_slice_units * 16 +
                                          (size_t)s_in * c_in * (nseg * 32 * 12 + 16));     // [slice][M][ccols]
 
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the next layer may start its own weight loads
   // ---- before the dependency wait: first batch of weights, raw scales / zeros of this warp's groups -------
   const int n0 = blockIdx.x * ccols + wc * 32 + 4 * r;
   const int32_t* wp = p.w + (size_t)(it0 * 4 + t) * p.N + n0;
@@ -516,7 +517,24 @@ __global__ void __launch_bounds__(MT == 1 ? 512 : 256, 1) gl_gemv_warp_kernel(co
     asm volatile("cp.async.commit_group;" ::: "memory");
   }
   if (lane == 0) *zero_unit = make_uint4(0u, 0u, 0u, 0u);
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  // still before the dependency wait (this only touches the layer's own weights): convert the group constants
+  asm volatile("cp.async.wait_all;" ::: "memory");
+  __syncwarp();
+  {                                                   // per-group fp32 constants: out += alpha * acc + beta * xsum
+    const float zs = p.zero_is_scalar ? (float)(*reinterpret_cast<const int32_t*>(p.zeros)) : 0.f;
+    for (int i = lane; i < nseg * 32; i += 32) {
+      float al = 1.f, z = zs;
+      if (p.W_group_mode >= 2) al = XTr::to_float(ms[i]);
+      if ((p.W_group_mode == 1 || p.W_group_mode >= 3) && !p.zero_is_scalar) z = XTr::to_float(mz[i]);
+      float be;
+      if (p.W_group_mode == 4)      be = z - XTr::BIAS * al;
+      else if (p.W_group_mode == 3) be = -(XTr::BIAS + z) * al;
+      else if (p.W_group_mode == 1) be = -(XTr::BIAS + z);
+      else                          be = -XTr::BIAS * al;
+      alpha[i] = al;
+      beta[i] = be;
+    }
+  }
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
   // ---- stage this slice of x in B-fragment order (shared by the c_in warps of the slice) -------------------
@@ -535,23 +553,6 @@ __global__ void __launch_bounds__(MT == 1 ? 512 : 256, 1) gl_gemv_warp_kernel(co
         o.z = __byte_perm(lo.y, hi.y, 0x5410); o.w = __byte_perm(lo.y, hi.y, 0x7632);
         xs[((((row >> 2) * H + hh) * p.M + m) << 2) + (row & 3)] = o;
       }
-    }
-  }
-  asm volatile("cp.async.wait_all;" ::: "memory");
-  __syncwarp();
-  {                                                   // per-group fp32 constants: out += alpha * acc + beta * xsum
-    const float zs = p.zero_is_scalar ? (float)(*reinterpret_cast<const int32_t*>(p.zeros)) : 0.f;
-    for (int i = lane; i < nseg * 32; i += 32) {
-      float al = 1.f, z = zs;
-      if (p.W_group_mode >= 2) al = XTr::to_float(ms[i]);
-      if ((p.W_group_mode == 1 || p.W_group_mode >= 3) && !p.zero_is_scalar) z = XTr::to_float(mz[i]);
-      float be;
-      if (p.W_group_mode == 4)      be = z - XTr::BIAS * al;
-      else if (p.W_group_mode == 3) be = -(XTr::BIAS + z) * al;
-      else if (p.W_group_mode == 1) be = -(XTr::BIAS + z);
-      else                          be = -XTr::BIAS * al;
-      alpha[i] = al;
-      beta[i] = be;
     }
   }
   if (c_in > 1) asm volatile("bar.sync %0, %1;" ::"r"(1 + sl), "r"(ccols) : "memory");
@@ -955,6 +956,7 @@ static int gemv_launch_impl(const gl_matmul_args* a, cudaStream_t st, const Gemv
   if ((uintptr_t)workspace & 15) GL_FAIL(GL_E_INVALID, "gl_matmul: workspace must be 16-byte aligned");
   const int e = a->elements_per_sample;
   GemvParams p;
+  memset(&p, 0, sizeof(p));
   p.x = a->x; p.w = reinterpret_cast<const int32_t*>(a->w); p.scales = a->scales; p.zeros = a->zeros; p.bias = a->bias;
   p.out = a->out;
   p.counters = reinterpret_cast<unsigned int*>(workspace);
@@ -969,7 +971,7 @@ static int gemv_launch_impl(const gl_matmul_args* a, cudaStream_t st, const Gemv
   p.out_dtype = a->out_dtype;
   p.max_slice_iters = pl.slice_iters;
   p.max_seg = pl.max_seg;
-  p.s_in = pl.s_in; p.c_in = pl.c_in; 
+  p.s_in = pl.s_in; p.c_in = pl.c_in;
   dim3 grid(pl.tiles, pl.splitK), block(32 * pl.warps_n);
   if (pl.fast) {
     if (a->x_dtype == GL_BF16) return launch_fast<__nv_bfloat16>(a->W_nbits, pl.MT, pl.gi, p, grid, block, pl.smem, st);

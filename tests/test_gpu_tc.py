@@ -161,3 +161,28 @@ def test_scale_atom_layout_matches_reference_shuffle(lib):
     rows[:224] = s0
     want = rows.view(2, 4, 32, 8, 4).permute(0, 3, 2, 1, 4).reshape(2, 8, 512)
     assert torch.equal(s1, want)
+
+
+def test_a16wn_split_k_is_deterministic_and_sized(lib):
+    """Few-tile problems split K over several CTAs per tile; partial tiles are added in split order by the CTA that
+    arrives last, so two runs give identical bits, and the workspace the library asks for covers the partial tiles."""
+    import ctypes
+    from gemlite_b200 import core, helper
+    N, K, M = 1024, 4096, 48
+    x, W_q, s, z, b = make_a16wn(N, K, 4, 128, torch.bfloat16, seed=77, M=M)
+    layer = helper.A16W4_HQQ_INT(device="cuda:0", dtype=torch.bfloat16).from_weights(W_q.cuda(), s.cuda(), z.cuda(), bias=b.cuda())
+    xs = x.cuda()
+    y1 = layer(xs).clone()
+    y2 = layer(xs).clone()
+    assert torch.equal(y1, y2)
+    assert _status_word() == 0
+    want = exact_a16wn(x, W_q, s, z, b, 128)
+    assert rel_fro(y1.float().cpu().numpy(), want) < 1e-2
+    out = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    a = core._fill_args(xs, layer.bias, layer.W_q, layer.scales, layer.zeros, None, None, out, layer.get_meta_args(), -1)
+    assert lib.gl_matmul_kernel_name(ctypes.byref(a)) == b"gl_gemm_tc_kernel"
+    need = lib.gl_matmul_workspace_bytes(ctypes.byref(a))
+    assert need >= lib.gl_matmul_counter_bytes() + 2 * M * N * 4          # at least two partial tiles
+    a.workspace, a.workspace_bytes = core._workspace(torch.device("cuda", 0), int(need)).data_ptr(), int(need) - 16
+    from gemlite_b200 import _lib
+    assert lib.gl_matmul(ctypes.byref(a), torch.cuda.current_stream().cuda_stream) == _lib.GL_E_WORKSPACE   # too small: an error, no fallback
