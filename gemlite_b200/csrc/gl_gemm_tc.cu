@@ -42,6 +42,7 @@ struct TcParams {
   const void* scales_w; int scales_w_dtype;     // [N] channel scales or null
   const float* meta_scale;                      // tensor scale (NVFP4) or null
   int* status;
+  int swap;                                     // operands swapped: kernel rows = output channels, columns = tokens
   // split-K (A16Wn, few tiles): fp32 partial tiles [splits][M][N] and one arrival counter per tile in the workspace
   int splits; float* partials; unsigned int* counters;
   // block-scaled formats: scale-factor atoms [rows/128][kblocks][512 B]
@@ -127,6 +128,35 @@ __device__ __forceinline__ void epilogue_tile(const TcParams& p, uint32_t tmem_d
   }
 }
 
+// Operands swapped (decode sizes): the kernel's rows are output channels and its columns are tokens.  p.M / p.N are
+// the kernel's dimensions (channels / tokens); scales_w and bias go with the row, scales_x with the column.
+template <bool INT_ACC>
+__device__ __forceinline__ void epilogue_tile_swapped(const TcParams& p, uint32_t tmem_d, int m0, int n0, int BN, int epi_warp, int lane) {
+  const int quad = epi_warp & 3;
+  const int ch = m0 + quad * 32 + lane;                // output channel
+  float rs = 1.f, bias = 0.f;
+  if (ch < p.M) {
+    if (p.scales_w != nullptr) rs = gl_load_as_float(p.scales_w, ch, p.scales_w_dtype);
+    if (p.bias != nullptr) bias = gl_load_as_float(p.bias, ch, p.out_dtype);
+  }
+  if (p.meta_scale != nullptr) rs *= *p.meta_scale;
+  for (int c0 = 0; c0 < BN; c0 += 32) {
+    if (n0 + c0 >= p.N) break;                         // warp-uniform
+    uint32_t rr[32];
+    tmem_ld_32x32(tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, rr);
+    if (ch >= p.M) continue;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const int tok = n0 + c0 + i;
+      if (c0 + i < BN && tok < p.N) {
+        const float a = INT_ACC ? (float)(int32_t)rr[i] : __uint_as_float(rr[i]);
+        const float cs = p.scales_x != nullptr ? p.scales_x[tok] : 1.f;
+        gl_store_out(p.out, (int64_t)tok * p.M + ch, fmaf(a * cs, rs, bias), p.out_dtype);
+      }
+    }
+  }
+}
+
 // split-K: this CTA's fp32 partial tile goes to the workspace [split][M][N] ...
 __device__ __forceinline__ void epilogue_store_partial(const TcParams& p, uint32_t tmem_d, int m0, int n0, int BN, int epi_warp, int lane, int split) {
   const int quad = epi_warp & 3;
@@ -176,6 +206,8 @@ __device__ __forceinline__ void epilogue_reduce_partials(const TcParams& p, int 
 }
 
 // ---- both operands by TMA: fp8 / int8 / mxfp4 / nvfp4 ---------------------------------------------
+// Decode sizes run with the operands swapped (p.swap): the weight rows are the MMA's 128-row side and the batch is its
+// 16- or 32-column side, so an MMA costs a fraction of the 128 x 128 one and the kernel streams at memory speed.
 // Persistent: the grid is one CTA per SM and CTA c computes tiles c, c + gridDim.x, ...  The shared-memory ring
 // runs straight across tile boundaries, so the loads of the next tile are in flight while the current one
 // finishes.  Without scale factors there is room in TMEM for two 256-column accumulators: the epilogue warps drain
@@ -186,11 +218,13 @@ __global__ void __launch_bounds__(192, 1) gl_gemm_tc_kernel(const __grid_constan
   using KT = KindTraits<KIND>;
   constexpr bool MX = KT::SF_ATOMS > 0;
   constexpr int A_BYTES = 128 * 128, B_BYTES = BN * 128;
-  constexpr int SFA_BYTES = KT::SF_ATOMS * 512, SFB_BYTES = KT::SF_ATOMS * 512 * (BN / 128);
+  constexpr int NBLK = (BN + 127) / 128;               // 128-row scale-factor blocks of the B tile
+  constexpr int ACC_STRIDE = BN < 32 ? 32 : BN;        // TMEM columns per accumulator (tcgen05.ld reads 32 at a time)
+  constexpr int SFA_BYTES = KT::SF_ATOMS * 512, SFB_BYTES = KT::SF_ATOMS * 512 * NBLK;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
   constexpr int ACC_BUFS = MX ? 1 : 2;
-  constexpr uint32_t SFA_COL = ACC_BUFS * BN, SFB_COL = SFA_COL + KT::SF_ATOMS * 4;
-  constexpr uint32_t TMEM_COLS = next_pow2_cols(ACC_BUFS * BN + KT::SF_ATOMS * 4 * (1 + BN / 128));
+  constexpr uint32_t SFA_COL = ACC_BUFS * ACC_STRIDE, SFB_COL = SFA_COL + KT::SF_ATOMS * 4;
+  constexpr uint32_t TMEM_COLS = next_pow2_cols(ACC_BUFS * ACC_STRIDE + KT::SF_ATOMS * 4 * (1 + NBLK));
 
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
@@ -232,7 +266,7 @@ __global__ void __launch_bounds__(192, 1) gl_gemm_tc_kernel(const __grid_constan
       bool ok = true;
       for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
         const int m0 = (tile % tiles_m) * 128, n0 = (tile / tiles_m) * BN;
-        const int valid_nb = min(BN / 128, (p.N - n0 + 127) / 128);   // 128-column blocks of this tile that exist
+        const int valid_nb = min(NBLK, (p.N - n0 + 127) / 128);   // 128-column blocks of this tile that exist
         for (int kt = 0; kt < p.nkt; ++kt, ++it) {
           const int s = it % STAGES;
           if (!mbar_wait(empty + s, ((it / STAGES) & 1u) ^ 1u, &s_abort, p.status, 2)) { ok = false; break; }
@@ -265,7 +299,7 @@ __global__ void __launch_bounds__(192, 1) gl_gemm_tc_kernel(const __grid_constan
         // the epilogue must have drained this accumulator (first use of each passes at once)
         if (!mbar_wait(tmem_empty + ab, ((local / ACC_BUFS) & 1u) ^ 1u, &s_abort, p.status, 6)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + ab * BN;
+        const uint32_t d_tmem = tmem_base + ab * ACC_STRIDE;
         for (int kt = 0; kt < p.nkt; ++kt, ++it) {
           const int s = it % STAGES;
           if (!mbar_wait(full + s, (it / STAGES) & 1u, &s_abort, p.status, 3)) { ok = false; break; }
@@ -276,8 +310,8 @@ __global__ void __launch_bounds__(192, 1) gl_gemm_tc_kernel(const __grid_constan
             for (int a = 0; a < KT::SF_ATOMS; ++a) {
               tmem_cp_sf(tmem_base + SFA_COL + a * 4, smem_desc_sf(sb + B_BYTES + a * 512));
 #pragma unroll
-              for (int nb = 0; nb < BN / 128; ++nb)
-                tmem_cp_sf(tmem_base + SFB_COL + a * 4 * (BN / 128) + nb * 4, smem_desc_sf(sb + B_BYTES + SFA_BYTES + (nb * KT::SF_ATOMS + a) * 512));
+              for (int nb = 0; nb < NBLK; ++nb)
+                tmem_cp_sf(tmem_base + SFB_COL + a * 4 * NBLK + nb * 4, smem_desc_sf(sb + B_BYTES + SFA_BYTES + (nb * KT::SF_ATOMS + a) * 512));
             }
           }
           const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sb);
@@ -287,10 +321,10 @@ __global__ void __launch_bounds__(192, 1) gl_gemm_tc_kernel(const __grid_constan
             if constexpr (KIND == KIND_MXF4) {
               const uint32_t sfid = (uint32_t)(2 * (j & 1));
               mma_ss_block_scaled<KIND>(d_tmem, da + 2 * j, db + 2 * j, p.idesc | (sfid << 29) | (sfid << 4),
-                                        tmem_base + SFA_COL + (j >> 1) * 4, tmem_base + SFB_COL + (j >> 1) * 4 * (BN / 128), accum);
+                                        tmem_base + SFA_COL + (j >> 1) * 4, tmem_base + SFB_COL + (j >> 1) * 4 * NBLK, accum);
             } else if constexpr (KIND == KIND_NVF4) {
               mma_ss_block_scaled<KIND>(d_tmem, da + 2 * j, db + 2 * j, p.idesc,
-                                        tmem_base + SFA_COL + j * 4, tmem_base + SFB_COL + j * 4 * (BN / 128), accum);
+                                        tmem_base + SFA_COL + j * 4, tmem_base + SFB_COL + j * 4 * NBLK, accum);
             } else {
               mma_ss<KIND>(d_tmem, da + 2 * j, db + 2 * j, p.idesc, accum);
             }
@@ -307,15 +341,18 @@ __global__ void __launch_bounds__(192, 1) gl_gemm_tc_kernel(const __grid_constan
     for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
       const int m0 = (tile % tiles_m) * 128, n0 = (tile / tiles_m) * BN;
       const uint32_t ab = local % ACC_BUFS;
-      for (int c = lane; c < BN; c += 32) {
-        const int n = n0 + c;
-        sw_s[c] = (p.scales_w != nullptr && n < p.N) ? gl_load_as_float(p.scales_w, n, p.scales_w_dtype) : 1.f;
-        b_s[c] = (p.bias != nullptr && n < p.N) ? gl_load_as_float(p.bias, n, p.out_dtype) : 0.f;
+      if (!p.swap) {
+        for (int c = lane; c < BN; c += 32) {
+          const int n = n0 + c;
+          sw_s[c] = (p.scales_w != nullptr && n < p.N) ? gl_load_as_float(p.scales_w, n, p.scales_w_dtype) : 1.f;
+          b_s[c] = (p.bias != nullptr && n < p.N) ? gl_load_as_float(p.bias, n, p.out_dtype) : 0.f;
+        }
+        __syncwarp();
       }
-      __syncwarp();
       if (!mbar_wait(tmem_full + ab, (local / ACC_BUFS) & 1u, &s_abort, p.status, 4)) break;
       tc_fence_after();
-      epilogue_tile<KIND == KIND_I8>(p, tmem_base + ab * BN, m0, n0, BN, warp, lane, sw_s, b_s);
+      if (p.swap) epilogue_tile_swapped<KIND == KIND_I8>(p, tmem_base + ab * ACC_STRIDE, m0, n0, BN, warp, lane);
+      else epilogue_tile<KIND == KIND_I8>(p, tmem_base + ab * ACC_STRIDE, m0, n0, BN, warp, lane, sw_s, b_s);
       tc_fence_before();                                  // this warp's TMEM reads are complete (tcgen05.wait::ld inside)
       __syncwarp();
       if (lane == 0) mbar_arrive(tmem_empty + ab);
@@ -544,7 +581,7 @@ static int set_smem(K kern, size_t smem) {
 template <int KIND, int BN, int STAGES>
 static int launch_tma_kernel(const CUtensorMap& tmA, const CUtensorMap& tmB, const TcParams& p, cudaStream_t st) {
   using KT = KindTraits<KIND>;
-  constexpr size_t stage = 128 * 128 + BN * 128 + KT::SF_ATOMS * 512 * (1 + BN / 128);
+  constexpr size_t stage = 128 * 128 + BN * 128 + KT::SF_ATOMS * 512 * (1 + (BN + 127) / 128);
   const size_t smem = 1024 + STAGES * stage + (2 * STAGES + 4) * 8 + 32 + 4 * 2 * BN * 4 + 16;
   auto kern = gl_gemm_tc_kernel<KIND, BN, STAGES>;
   if (int rc = set_smem(kern, smem)) return rc;
@@ -657,6 +694,8 @@ int gl_gemm_tc_launch(const gl_matmul_args* a, cudaStream_t st) {
   p.status = reinterpret_cast<int*>(reinterpret_cast<char*>(a->workspace) + gl_matmul_counter_bytes() - 256);
   p.meta_scale = nullptr;
   const int BN = tc_tile_n(a);
+  // decode sizes of the TMA formats swap the operands (16 or 32 token columns)
+  const int swap_bn = (path != TC_A16WN && a->M <= 32 && a->N >= 128) ? (a->M <= 16 ? 16 : 32) : 0;
   CUtensorMap tmA, tmB;
   if (path == TC_A16WN) {
     p.nkt = (a->K + 63) / 64;
@@ -686,6 +725,14 @@ int gl_gemm_tc_launch(const gl_matmul_args* a, cudaStream_t st) {
     p.idesc = (path == TC_FP8) ? gl_idesc(1, 0, 0, 128, BN) : gl_idesc(2, 1, 1, 128, BN);
     if (a->channel_scale_mode == 2 || a->channel_scale_mode == 3) p.scales_x = reinterpret_cast<const float*>(a->scales_x);
     if (a->channel_scale_mode == 1 || a->channel_scale_mode == 3) { p.scales_w = a->scales; p.scales_w_dtype = a->meta_dtype; }
+    if (swap_bn) {   // decode sizes: weights on the 128-row side, tokens on the narrow side
+      p.M = a->N; p.N = a->M; p.swap = 1;
+      p.idesc = (path == TC_FP8) ? gl_idesc(1, 0, 0, 128, swap_bn) : gl_idesc(2, 1, 1, 128, swap_bn);
+      if (int rc = gl_make_tmap_2d(&tmA, a->w, 0, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)a->K, 128, 128, true)) return rc;
+      if (int rc = gl_make_tmap_2d(&tmB, a->x, 0, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->K, 128, (uint32_t)swap_bn, true)) return rc;
+      if (path == TC_FP8) return swap_bn == 16 ? launch_tma_kernel<KIND_F8F6F4, 16, 8>(tmA, tmB, p, st) : launch_tma_kernel<KIND_F8F6F4, 32, 8>(tmA, tmB, p, st);
+      return swap_bn == 16 ? launch_tma_kernel<KIND_I8, 16, 8>(tmA, tmB, p, st) : launch_tma_kernel<KIND_I8, 32, 8>(tmA, tmB, p, st);
+    }
     if (int rc = gl_make_tmap_2d(&tmA, a->x, 0, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->K, 128, 128, true)) return rc;
     if (int rc = gl_make_tmap_2d(&tmB, a->w, 0, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)a->K, 128, (uint32_t)BN, true)) return rc;
     if (path == TC_FP8) return BN == 256 ? launch_tma_kernel<KIND_F8F6F4, 256, 4>(tmA, tmB, p, st) : launch_tma_kernel<KIND_F8F6F4, 128, 6>(tmA, tmB, p, st);
@@ -699,6 +746,16 @@ int gl_gemm_tc_launch(const gl_matmul_args* a, cudaStream_t st) {
   p.sfb = reinterpret_cast<const uint8_t*>(a->w_scales_atoms);
   p.sf_kblocks = a->K / gs / 4;
   p.meta_scale = (path == TC_NVFP4) ? a->meta_scale : nullptr;
+  if (swap_bn) {
+    p.M = a->N; p.N = a->M; p.swap = 1;
+    p.idesc = gl_idesc_block_scaled(1, path == TC_MXFP4 ? 1 : 0, 128, swap_bn);
+    p.sfa = reinterpret_cast<const uint8_t*>(a->w_scales_atoms);
+    p.sfb = reinterpret_cast<const uint8_t*>(a->scales_x);
+    if (int rc = gl_make_tmap_2d(&tmA, a->w, 0, (uint64_t)a->K / 2, (uint64_t)a->N, (uint64_t)a->K / 2, 128, 128, true)) return rc;
+    if (int rc = gl_make_tmap_2d(&tmB, a->x, 0, (uint64_t)a->K / 2, (uint64_t)a->M, (uint64_t)a->K / 2, 128, (uint32_t)swap_bn, true)) return rc;
+    if (path == TC_MXFP4) return swap_bn == 16 ? launch_tma_kernel<KIND_MXF4, 16, 8>(tmA, tmB, p, st) : launch_tma_kernel<KIND_MXF4, 32, 8>(tmA, tmB, p, st);
+    return swap_bn == 16 ? launch_tma_kernel<KIND_NVF4, 16, 8>(tmA, tmB, p, st) : launch_tma_kernel<KIND_NVF4, 32, 8>(tmA, tmB, p, st);
+  }
   if (int rc = gl_make_tmap_2d(&tmA, a->x, 0, (uint64_t)a->K / 2, (uint64_t)a->M, (uint64_t)a->K / 2, 128, 128, true)) return rc;
   if (int rc = gl_make_tmap_2d(&tmB, a->w, 0, (uint64_t)a->K / 2, (uint64_t)a->N, (uint64_t)a->K / 2, 128, (uint32_t)BN, true)) return rc;
   if (path == TC_MXFP4) return BN == 256 ? launch_tma_kernel<KIND_MXF4, 256, 4>(tmA, tmB, p, st) : launch_tma_kernel<KIND_MXF4, 128, 6>(tmA, tmB, p, st);
