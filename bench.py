@@ -184,10 +184,15 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--case", default=None, help="run one format:M case of the sweep a few times and print its time (for profiling), e.g. MXFP4:4096")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         return run_reference_arm(args)
+    if args.case:
+        fmt, M = args.case.split(":")
+        print(json.dumps(sweep_gemm(torch.device("cuda", 0), only=(fmt, int(M)))))
+        return
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -436,7 +441,7 @@ def sweep(device, layers, stream, hbm_peak, bf16_peak):
     return res
 
 
-def sweep_gemm(device):
+def sweep_gemm(device, only=None):
     """The other benchmark configurations through the public API (GemLiteLinear.forward incl. the fused
     activation quantiser): FP8 4096->14336, MXFP4 / NVFP4 16384x16384, A16W4 8192x8192 at prefill size.
     L2 is flushed between timed calls; min of 10 calls; TFLOP/s = 2 M N K / time.  `ref_triton_ms` is the
@@ -481,8 +486,11 @@ def sweep_gemm(device):
 
     res = []
     stream = torch.cuda.Stream(device)
-    for fmt, Ms in (("A16W4", (64, 256, 1024, 4096, 8192)), ("A16W2", (1, 16, 64, 256, 1024, 4096, 8192)), ("FP8", (1, 16, 128, 1024, 4096)),
-                    ("MXFP4", (1, 64, 512, 4096, 16384)), ("NVFP4", (1, 64, 512, 4096, 16384))):
+    cases = (("A16W4", (64, 256, 1024, 4096, 8192)), ("A16W2", (1, 16, 64, 256, 1024, 4096, 8192)), ("FP8", (1, 16, 128, 1024, 4096)),
+             ("MXFP4", (1, 64, 512, 4096, 16384)), ("NVFP4", (1, 64, 512, 4096, 16384)))
+    if only is not None:
+        cases = ((only[0], (only[1],)),)
+    for fmt, Ms in cases:
         try:
             layer, K, N = make(fmt)
             wbytes = N * K // {"FP8": 1, "A16W2": 4}.get(fmt, 2)
