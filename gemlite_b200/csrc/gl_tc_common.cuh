@@ -60,6 +60,12 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* tm, ui
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(dst)), "l"(tm), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
 }
+// 4-D tiled TMA load (no multicast)
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* tm, uint64_t* bar, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(tm), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
 // 1-D bulk copy global -> smem (16-byte aligned addresses and size), completes on `bar`.
 __device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
   asm volatile(
@@ -110,6 +116,12 @@ __device__ __forceinline__ uint64_t smem_desc_sf(uint32_t saddr) {
   return (uint64_t)((saddr >> 4) & 0x3FFFu) | (1ull << 16) | (8ull << 32) | (1ull << 46);
 }
 
+// Descriptor of two 128-row x 16-byte blocks (each stored as sixteen contiguous 8-row core matrices, 2 KB) that are
+// `chunk_stride` bytes apart: the source of tcgen05.cp 128x256b.
+__device__ __forceinline__ uint64_t smem_desc_sf2(uint32_t saddr, uint32_t chunk_stride) {
+  return (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)((chunk_stride >> 4) & 0x3FFFu) << 16) | (8ull << 32) | (1ull << 46);
+}
+
 enum MmaKind { KIND_F16 = 0, KIND_F8F6F4 = 1, KIND_I8 = 2, KIND_MXF4 = 3, KIND_NVF4 = 4 };
 
 template <int KIND>
@@ -141,6 +153,11 @@ __device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t sdesc) {
   asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
 }
 
+// smem (128 rows x 32 B) -> TMEM (128 lanes x 8 columns): two scale-factor atoms at once
+__device__ __forceinline__ void tmem_cp_sf_pair2(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.128x256b [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+
 }  // namespace gltc
 
 // ---- host side: tensor maps -----------------------------------------------------------------------
@@ -148,6 +165,10 @@ __device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t sdesc) {
 // point is looked up at run time so that the library does not link against libcuda.
 int gl_make_tmap_2d(CUtensorMap* out, const void* base, int elem_kind /*0 u8, 1 bf16, 2 f16, 3 i32*/, uint64_t inner_elems,
                     uint64_t rows, uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_rows, bool swizzle128);
+
+// Scale-factor atoms [blocks][k_atoms][512 B] as a 4-D tensor [block][k atom][4 replicas, stride 0][128 words]: a box
+// (128, 4, box_atoms, 1) lands every atom four times in a row, out-of-range atoms as zeros.
+int gl_make_tmap_sf_replicated(CUtensorMap* out, const void* base, uint64_t k_atoms, uint64_t blocks, uint32_t box_atoms);
 
 // instruction descriptors (bit layout of the tcgen05 instruction descriptor)
 static inline uint32_t gl_idesc(int c_format, int a_format, int b_format, int M, int N) {

@@ -43,3 +43,18 @@ int gl_make_tmap_2d(CUtensorMap* out, const void* base, int elem_kind, uint64_t 
                                  (unsigned long long)inner_elems, (unsigned long long)rows, (unsigned long long)row_stride_bytes, box_inner, box_rows);
   return GL_OK;
 }
+
+int gl_make_tmap_sf_replicated(CUtensorMap* out, const void* base, uint64_t k_atoms, uint64_t blocks, uint32_t box_atoms) {
+  PFN_encodeTiled enc = get_encode();
+  if (!enc) GL_FAIL(GL_E_CUDA, "cuTensorMapEncodeTiled is not available from the CUDA driver");
+  if ((uintptr_t)base & 15) GL_FAIL(GL_E_INVALID, "TMA operand must be 16-byte aligned");
+  cuuint64_t dims[4] = {128, 4, k_atoms, blocks};
+  cuuint64_t strides[3] = {0, 512, 512 * k_atoms};      // the replica dimension re-reads the same 512 bytes
+  cuuint32_t box[4] = {128, 4, box_atoms, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) GL_FAIL(GL_E_CUDA, "cuTensorMapEncodeTiled (scale atoms) failed with code %d (k atoms %llu blocks %llu)", (int)r,
+                                 (unsigned long long)k_atoms, (unsigned long long)blocks);
+  return GL_OK;
+}

@@ -186,3 +186,38 @@ def test_a16wn_split_k_is_deterministic_and_sized(lib):
     a.workspace, a.workspace_bytes = core._workspace(torch.device("cuda", 0), int(need)).data_ptr(), int(need) - 16
     from gemlite_b200 import _lib
     assert lib.gl_matmul(ctypes.byref(a), torch.cuda.current_stream().cuda_stream) == _lib.GL_E_WORKSPACE   # too small: an error, no fallback
+
+
+@pytest.mark.parametrize("fmt", ["mxfp4", "nvfp4"])
+def test_a4w4_256_column_tiles_with_replicated_scale_atoms(lib, fmt):
+    """Enough tiles for the 256-column configuration: scale atoms arrive through the stride-0 tensor maps and are copied
+    to TMEM two at a time; K ends in the middle of a K tile (missing atoms read as zero).  Compared with the general
+    kernel (itself pinned to the oracle above) and, on sampled rows, with the oracle."""
+    from gemlite_b200 import core, helper
+    M, N, K = 1024, 3072, 1408
+    g = torch.Generator().manual_seed(911)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    lin = torch.nn.Linear(K, N, bias=False, dtype=torch.bfloat16)
+    lin.weight.data = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16)
+    proc = (helper.A4W4_MXFP_dynamic if fmt == "mxfp4" else helper.A4W4_NVFP_dynamic)(device="cuda:0", dtype=torch.bfloat16)
+    layer = proc.from_linear(lin.cuda())
+    y = layer(x.cuda()).float()
+    assert _status_word() == 0
+    core.set_kernel_override(1)
+    try:
+        y_gen = layer(x.cuda()).float()
+    finally:
+        core.set_kernel_override(0)
+    assert rel_fro(y.cpu().numpy(), y_gen.cpu().numpy()) < 2e-3
+    rows = [0, 127, 128, 517, 1023]
+    gs = 32 if fmt == "mxfp4" else 16
+    wq = layer.W_q.t().contiguous().cpu().numpy()
+    sw = layer.scales.contiguous().view(torch.uint8).cpu().numpy()
+    if fmt == "mxfp4":
+        xq, sx = oracle.scale_activations_mxfp4(x.float().numpy())
+        meta = None
+    else:
+        xq, sx, mx = oracle.scale_activations_nvfp4(x.float().numpy())
+        meta = 1.0 / (float(layer.meta_scale.item()) * float(mx))
+    want = oracle.matmul_mx(xq[rows], sx[rows], wq, sw, gs, meta_scale=meta)
+    assert rel_fro(y.cpu().numpy()[rows], want) < 5e-3
