@@ -465,7 +465,7 @@ __device__ __forceinline__ uint32_t and_or(uint32_t v, uint32_t mask, uint32_t m
 
 // GI: iterations per quantisation group when it divides 8 (1, 2, 4); 0 = a multiple of 8 (p.gi), flushed at run time
 template <int NB, typename XT, int MT, int GI>
-__global__ void __launch_bounds__(MT == 1 ? 512 : 256, 1) gl_gemv_warp_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(MT == 1 ? 512 : 256, MT == 1 ? 1 : 2) gl_gemv_warp_kernel(const GemvParams p) {
   constexpr int E = 32 / NB, H = E / 8, HALF = E / 2, U = 8;
   constexpr uint32_t FMASK = ((1u << NB) - 1u) * 0x00010001u;
   constexpr uint32_t ONES = OnesPair<XT>::V;
@@ -749,7 +749,7 @@ static bool plan_warp(const gl_matmul_args* a, GemvPlan* pl, const char* js) {
   if (c_in < 1 || c_in > 16 || colgroups % c_in != 0) return false;
   if (s_in <= 0 || cluster <= 0) {
     // slices: fewest "waves x (iterations per warp + fixed per-warp cost)" over the power-of-two splits that fit
-    const int64_t warp_slots = (int64_t)gl_num_sms() * (a->M <= 8 ? 16 : 8);
+    const int64_t warp_slots = (int64_t)gl_num_sms() * 16;
     int S = 0;
     int64_t best_cost = 0;
     for (int cand = 1; cand <= 64; cand <<= 1) {
