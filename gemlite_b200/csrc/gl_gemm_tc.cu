@@ -224,12 +224,14 @@ __global__ void __launch_bounds__(192, 1) gl_gemm_tc_kernel(const __grid_constan
   // in shared memory, so the atoms arrive through 4-D tensor maps whose replica dimension has stride 0.
   // (measured at M = 4096, 16384²: NVFP4, 12 copies per K tile, 0.79 -> 0.75 ms; MXFP4, 6 copies, is better off with a
   // fourth pipeline stage than with the 9 KB of replicated atoms per stage: 0.59 ms against 0.62 ms)
-  constexpr bool WIDE = KIND == KIND_NVF4 && BN == 256;
-  constexpr int SF_REP = WIDE ? 4 : 1;
+  // MXFP4 copies only the A-side atoms this way: 5 copies per K tile instead of 6 with a fourth stage still fitting.
+  constexpr bool WIDE_A = MX && BN == 256;
+  constexpr bool WIDE_B = KIND == KIND_NVF4 && BN == 256;
+  constexpr int REP_A = WIDE_A ? 4 : 1, REP_B = WIDE_B ? 4 : 1;
   constexpr int A_BYTES = 128 * 128, B_BYTES = BN * 128;
   constexpr int NBLK = (BN + 127) / 128;               // 128-row scale-factor blocks of the B tile
   constexpr int ACC_STRIDE = BN < 32 ? 32 : BN;        // TMEM columns per accumulator (tcgen05.ld reads 32 at a time)
-  constexpr int SFA_BYTES = KT::SF_ATOMS * 512 * SF_REP, SFB_BYTES = KT::SF_ATOMS * 512 * SF_REP * NBLK;
+  constexpr int SFA_BYTES = KT::SF_ATOMS * 512 * REP_A, SFB_BYTES = KT::SF_ATOMS * 512 * REP_B * NBLK;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
   constexpr int ACC_BUFS = MX ? 1 : 2;
   constexpr uint32_t SFA_COL = ACC_BUFS * ACC_STRIDE, SFB_COL = SFA_COL + KT::SF_ATOMS * 4;
@@ -257,7 +259,7 @@ __global__ void __launch_bounds__(192, 1) gl_gemm_tc_kernel(const __grid_constan
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
   }
-  if (MX && !WIDE) {   // scale-factor atoms that a short last K tile does not overwrite must hold finite numbers
+  if (MX && !(WIDE_A && WIDE_B)) {   // scale-factor atoms that a short last K tile does not overwrite must hold finite numbers
     for (int s = 0; s < STAGES; ++s)
       for (int i = threadIdx.x; i < (SFA_BYTES + SFB_BYTES) / 4; i += blockDim.x)
         reinterpret_cast<uint32_t*>(smem + s * STAGE_BYTES + A_BYTES + B_BYTES)[i] = 0u;
@@ -282,25 +284,27 @@ __global__ void __launch_bounds__(192, 1) gl_gemm_tc_kernel(const __grid_constan
           unsigned char* st = smem + s * STAGE_BYTES;
           uint32_t bytes = A_BYTES + B_BYTES;
           int atoms = 0;
-          if (WIDE) bytes += SFA_BYTES + SFB_BYTES;        // whole boxes, out-of-range atoms read as zero
-          else if (MX) {
+          if (MX) {
             atoms = min(KT::SF_ATOMS, p.sf_kblocks - kt * KT::SF_ATOMS);
-            bytes += (uint32_t)atoms * 512u * (1 + valid_nb);
+            bytes += WIDE_A ? (uint32_t)SFA_BYTES : (uint32_t)atoms * 512u;            // wide boxes are always whole
+            bytes += WIDE_B ? (uint32_t)SFB_BYTES : (uint32_t)atoms * 512u * valid_nb;
           }
           mbar_expect_tx(full + s, bytes);
           tma_load_2d(st, &tmA, full + s, kt * 128, m0);
           tma_load_2d(st + A_BYTES, &tmB, full + s, kt * 128, n0);
-          if (WIDE) {
-            tma_load_4d(st + A_BYTES + B_BYTES, &tmSFA, full + s, 0, 0, kt * KT::SF_ATOMS, m0 / 128);
-#pragma unroll
-            for (int nb = 0; nb < NBLK; ++nb)
-              tma_load_4d(st + A_BYTES + B_BYTES + SFA_BYTES + nb * (SFB_BYTES / NBLK), &tmSFB, full + s, 0, 0, kt * KT::SF_ATOMS, n0 / 128 + nb);
-          } else if (MX) {
+          if (MX) {
             const size_t koff = (size_t)kt * KT::SF_ATOMS;
-            bulk_load_1d(st + A_BYTES + B_BYTES, p.sfa + ((size_t)(m0 / 128) * p.sf_kblocks + koff) * 512, (uint32_t)atoms * 512u, full + s);
-            for (int nb = 0; nb < valid_nb; ++nb)
-              bulk_load_1d(st + A_BYTES + B_BYTES + SFA_BYTES + nb * KT::SF_ATOMS * 512,
-                           p.sfb + ((size_t)(n0 / 128 + nb) * p.sf_kblocks + koff) * 512, (uint32_t)atoms * 512u, full + s);
+            if (WIDE_A) tma_load_4d(st + A_BYTES + B_BYTES, &tmSFA, full + s, 0, 0, kt * KT::SF_ATOMS, m0 / 128);
+            else bulk_load_1d(st + A_BYTES + B_BYTES, p.sfa + ((size_t)(m0 / 128) * p.sf_kblocks + koff) * 512, (uint32_t)atoms * 512u, full + s);
+            if (WIDE_B) {
+#pragma unroll
+              for (int nb = 0; nb < NBLK; ++nb)
+                tma_load_4d(st + A_BYTES + B_BYTES + SFA_BYTES + nb * (SFB_BYTES / NBLK), &tmSFB, full + s, 0, 0, kt * KT::SF_ATOMS, n0 / 128 + nb);
+            } else {
+              for (int nb = 0; nb < valid_nb; ++nb)
+                bulk_load_1d(st + A_BYTES + B_BYTES + SFA_BYTES + nb * KT::SF_ATOMS * 512,
+                             p.sfb + ((size_t)(n0 / 128 + nb) * p.sf_kblocks + koff) * 512, (uint32_t)atoms * 512u, full + s);
+            }
           }
         }
       }
@@ -320,21 +324,26 @@ __global__ void __launch_bounds__(192, 1) gl_gemm_tc_kernel(const __grid_constan
           if (!mbar_wait(full + s, (it / STAGES) & 1u, &s_abort, p.status, 3)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + s * STAGE_BYTES), sb = sa + A_BYTES;
-          if (WIDE) {
+          if (MX) {
             const uint32_t sfa_s = sb + B_BYTES, sfb_s = sfa_s + SFA_BYTES;
+            if (WIDE_A) {
 #pragma unroll
-            for (int a = 0; a < KT::SF_ATOMS; a += 2)        // atoms a, a + 1 of the A rows: adjacent in shared memory and TMEM
-              tmem_cp_sf_pair2(tmem_base + SFA_COL + a * 4, smem_desc_sf2(sfa_s + a * 2048, 2048));
+              for (int a = 0; a < KT::SF_ATOMS; a += 2)      // atoms a, a + 1 of the A rows: adjacent in shared memory and TMEM
+                tmem_cp_sf_pair2(tmem_base + SFA_COL + a * 4, smem_desc_sf2(sfa_s + a * 2048, 2048));
+            } else {
 #pragma unroll
-            for (int a = 0; a < KT::SF_ATOMS; ++a)           // atom a of both 128-column blocks of B
-              tmem_cp_sf_pair2(tmem_base + SFB_COL + a * 8, smem_desc_sf2(sfb_s + a * 2048, SFB_BYTES / NBLK));
-          } else if (MX) {
+              for (int a = 0; a < KT::SF_ATOMS; ++a) tmem_cp_sf(tmem_base + SFA_COL + a * 4, smem_desc_sf(sfa_s + a * 512));
+            }
+            if (WIDE_B) {
 #pragma unroll
-            for (int a = 0; a < KT::SF_ATOMS; ++a) {
-              tmem_cp_sf(tmem_base + SFA_COL + a * 4, smem_desc_sf(sb + B_BYTES + a * 512));
+              for (int a = 0; a < KT::SF_ATOMS; ++a)         // atom a of both 128-column blocks of B
+                tmem_cp_sf_pair2(tmem_base + SFB_COL + a * 8, smem_desc_sf2(sfb_s + a * 2048, SFB_BYTES / NBLK));
+            } else {
 #pragma unroll
-              for (int nb = 0; nb < NBLK; ++nb)
-                tmem_cp_sf(tmem_base + SFB_COL + a * 4 * NBLK + nb * 4, smem_desc_sf(sb + B_BYTES + SFA_BYTES + (nb * KT::SF_ATOMS + a) * 512));
+              for (int a = 0; a < KT::SF_ATOMS; ++a)
+#pragma unroll
+                for (int nb = 0; nb < NBLK; ++nb)
+                  tmem_cp_sf(tmem_base + SFB_COL + a * 4 * NBLK + nb * 4, smem_desc_sf(sfb_s + (nb * KT::SF_ATOMS + a) * 512));
             }
           }
           const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sb);
@@ -605,8 +614,8 @@ template <int KIND, int BN, int STAGES>
 static int launch_tma_kernel(const CUtensorMap& tmA, const CUtensorMap& tmB, const TcParams& p, cudaStream_t st,
                              const CUtensorMap* tmSFA = nullptr, const CUtensorMap* tmSFB = nullptr) {
   using KT = KindTraits<KIND>;
-  constexpr int rep = (KIND == KIND_NVF4 && BN == 256) ? 4 : 1;
-  constexpr size_t stage = 128 * 128 + BN * 128 + KT::SF_ATOMS * 512 * rep * (1 + (BN + 127) / 128);
+  constexpr int rep_a = (KT::SF_ATOMS > 0 && BN == 256) ? 4 : 1, rep_b = (KIND == KIND_NVF4 && BN == 256) ? 4 : 1;
+  constexpr size_t stage = 128 * 128 + BN * 128 + KT::SF_ATOMS * 512 * (rep_a + rep_b * ((BN + 127) / 128));
   const size_t smem = 1024 + STAGES * stage + (2 * STAGES + 4) * 8 + 32 + 4 * 2 * BN * 4 + 16;
   auto kern = gl_gemm_tc_kernel<KIND, BN, STAGES>;
   if (int rc = set_smem(kern, smem)) return rc;
@@ -783,14 +792,15 @@ int gl_gemm_tc_launch(const gl_matmul_args* a, cudaStream_t st) {
   }
   if (int rc = gl_make_tmap_2d(&tmA, a->x, 0, (uint64_t)a->K / 2, (uint64_t)a->M, (uint64_t)a->K / 2, 128, 128, true)) return rc;
   if (int rc = gl_make_tmap_2d(&tmB, a->w, 0, (uint64_t)a->K / 2, (uint64_t)a->N, (uint64_t)a->K / 2, 128, (uint32_t)BN, true)) return rc;
-  if (BN == 256 && path == TC_NVFP4) {
+  if (BN == 256) {
     // scale-factor atoms [128-row block][K atom][512 B] seen as [block][K atom][4 replicas, stride 0][128 words]
     CUtensorMap tmSFA, tmSFB;
-    if (int rc = gl_make_tmap_sf_replicated(&tmSFA, a->scales_x, (uint64_t)p.sf_kblocks, (uint64_t)((a->M + 127) / 128), 4)) return rc;
-    if (int rc = gl_make_tmap_sf_replicated(&tmSFB, a->w_scales_atoms, (uint64_t)p.sf_kblocks, (uint64_t)((a->N + 127) / 128), 4)) return rc;
-    return launch_tma_kernel<KIND_NVF4, 256, 3>(tmA, tmB, p, st, &tmSFA, &tmSFB);
+    const uint32_t atoms = path == TC_MXFP4 ? 2 : 4;
+    if (int rc = gl_make_tmap_sf_replicated(&tmSFA, a->scales_x, (uint64_t)p.sf_kblocks, (uint64_t)((a->M + 127) / 128), atoms)) return rc;
+    if (int rc = gl_make_tmap_sf_replicated(&tmSFB, a->w_scales_atoms, (uint64_t)p.sf_kblocks, (uint64_t)((a->N + 127) / 128), atoms)) return rc;
+    return path == TC_MXFP4 ? launch_tma_kernel<KIND_MXF4, 256, 4>(tmA, tmB, p, st, &tmSFA, &tmSFB)
+                            : launch_tma_kernel<KIND_NVF4, 256, 3>(tmA, tmB, p, st, &tmSFA, &tmSFB);
   }
-  if (BN == 256) return launch_tma_kernel<KIND_MXF4, 256, 4>(tmA, tmB, p, st);
   if (path == TC_MXFP4) return launch_tma_kernel<KIND_MXF4, 128, 6>(tmA, tmB, p, st);
   return launch_tma_kernel<KIND_NVF4, 128, 6>(tmA, tmB, p, st);
 }
