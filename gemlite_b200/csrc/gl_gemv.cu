@@ -708,7 +708,7 @@ __global__ void __launch_bounds__(MT == 1 ? 512 : 256, MT == 1 ? 1 : 2) gl_gemv_
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-struct GemvPlan { int warps_n, splitK, cluster, MT, slice_iters, max_seg, tiles, fast, gi, s_in, c_in; size_t smem; };
+struct GemvPlan { int warps_n, splitK, cluster, MT, slice_iters, max_seg, tiles, warp_kernel, gi, s_in, c_in; size_t smem; };
 
 // Tile parameters: built-in heuristic, overridden by a config-cache entry for the GEMV_REVSPLITK /
 // GEMV_SPLITK / GEMV family under the reference's signature "(Mb, N, K, group_size, e, type_id)" with
@@ -770,7 +770,7 @@ static bool plan_warp(const gl_matmul_args* a, GemvPlan* pl, const char* js) {
   const size_t smem = (size_t)s_in * nit * H * a->M * 64 + (size_t)s_in * c_in * (nseg * 32 * 12 + 16) +
                       (size_t)s_in * a->M * c_in * 32 * 4 + 16;
   if (smem > 200 * 1024) return false;
-  pl->fast = 1; pl->gi = gi; pl->s_in = s_in; pl->c_in = c_in; pl->cluster = cluster; pl->splitK = cluster;
+  pl->warp_kernel = 1; pl->gi = gi; pl->s_in = s_in; pl->c_in = c_in; pl->cluster = cluster; pl->splitK = cluster;
   pl->MT = a->M <= 8 ? 1 : 2;
   pl->warps_n = s_in * c_in; pl->tiles = colgroups / c_in; pl->smem = smem;
   pl->slice_iters = nit; pl->max_seg = nseg;
@@ -801,7 +801,7 @@ static void plan_for(const gl_matmul_args* a, GemvPlan* pl, bool force_workspace
       }
     }
   }
-  pl->fast = 0; pl->s_in = pl->c_in = 1;
+  pl->warp_kernel = 0; pl->s_in = pl->c_in = 1;
   // "kernel": 1 in a cache entry pins the general kernel; entries that carry split_k / warps_n tune that kernel
   const bool general_req = cfg_js && (json_int(cfg_js, "kernel", 0) == 1 || split_req > 0);
   if (!force_workspace && !general_req && plan_warp(a, pl, cfg_js)) return;
@@ -834,7 +834,7 @@ static void plan_for(const gl_matmul_args* a, GemvPlan* pl, bool force_workspace
   const size_t part_bytes = ((size_t)a->M * 32 * warps_n * 4 + 15) / 16 * 16;
   pl->smem = (xs_bytes > part_bytes ? xs_bytes : part_bytes) + (size_t)pl->max_seg * (8 * pl->MT * 4 + 2 * warps_n * 32 * 2) + 32;
   pl->gi = gi;
-  pl->fast = 0;
+  pl->warp_kernel = 0;
 }
 
 template <int NB, typename XT, int MT>
@@ -875,7 +875,7 @@ static int launch_kernel(K kern, const GemvParams& p, dim3 grid, dim3 block, siz
   return GL_OK;
 }
 template <int NB, typename XT, int MT>
-static int launch_fast_gi(int gi, const GemvParams& p, dim3 grid, dim3 block, size_t smem, cudaStream_t st) {
+static int launch_warp_gi(int gi, const GemvParams& p, dim3 grid, dim3 block, size_t smem, cudaStream_t st) {
   if (gi == 1) return launch_kernel(gl_gemv_warp_kernel<NB, XT, MT, 1>, p, grid, block, smem, st);
   if (gi == 2) return launch_kernel(gl_gemv_warp_kernel<NB, XT, MT, 2>, p, grid, block, smem, st);
   if (gi == 4) return launch_kernel(gl_gemv_warp_kernel<NB, XT, MT, 4>, p, grid, block, smem, st);
@@ -883,8 +883,8 @@ static int launch_fast_gi(int gi, const GemvParams& p, dim3 grid, dim3 block, si
 }
 template <typename XT>
 static int launch_fast(int NB, int MT, int gi, const GemvParams& p, dim3 grid, dim3 block, size_t smem, cudaStream_t st) {
-  if (NB == 4) return MT == 1 ? launch_fast_gi<4, XT, 1>(gi, p, grid, block, smem, st) : launch_fast_gi<4, XT, 2>(gi, p, grid, block, smem, st);
-  return MT == 1 ? launch_fast_gi<2, XT, 1>(gi, p, grid, block, smem, st) : launch_fast_gi<2, XT, 2>(gi, p, grid, block, smem, st);
+  if (NB == 4) return MT == 1 ? launch_warp_gi<4, XT, 1>(gi, p, grid, block, smem, st) : launch_warp_gi<4, XT, 2>(gi, p, grid, block, smem, st);
+  return MT == 1 ? launch_warp_gi<2, XT, 1>(gi, p, grid, block, smem, st) : launch_warp_gi<2, XT, 2>(gi, p, grid, block, smem, st);
 }
 
 template <int NB, typename XT>
@@ -973,9 +973,9 @@ static int gemv_launch_impl(const gl_matmul_args* a, cudaStream_t st, const Gemv
   p.max_seg = pl.max_seg;
   p.s_in = pl.s_in; p.c_in = pl.c_in;
   dim3 grid(pl.tiles, pl.splitK), block(32 * pl.warps_n);
-  if (pl.fast) {
-    if (a->x_dtype == GL_BF16) return launch_fast<__nv_bfloat16>(a->W_nbits, pl.MT, pl.gi, p, grid, block, pl.smem, st);
-    return launch_fast<__half>(a->W_nbits, pl.MT, pl.gi, p, grid, block, pl.smem, st);
+  if (pl.warp_kernel) {
+    if (a->x_dtype == GL_BF16) return launch_warp<__nv_bfloat16>(a->W_nbits, pl.MT, pl.gi, p, grid, block, pl.smem, st);
+    return launch_warp<__half>(a->W_nbits, pl.MT, pl.gi, p, grid, block, pl.smem, st);
   }
   if (a->x_dtype == GL_BF16) return launch_nb<__nv_bfloat16>(a->W_nbits, pl.MT, p, grid, block, pl.smem, st);
   return launch_nb<__half>(a->W_nbits, pl.MT, p, grid, block, pl.smem, st);
@@ -984,7 +984,7 @@ static int gemv_launch_impl(const gl_matmul_args* a, cudaStream_t st, const Gemv
 const char* gl_gemv_stream_kernel_name(const gl_matmul_args* a) {
   GemvPlan pl;
   plan_for(a, &pl);
-  return pl.fast ? "gl_gemv_warp_kernel" : "gl_gemv_stream_kernel";
+  return pl.warp_kernel ? "gl_gemv_warp_kernel" : "gl_gemv_stream_kernel";
 }
 
 int gl_gemv_stream_launch(const gl_matmul_args* a, cudaStream_t st) {
