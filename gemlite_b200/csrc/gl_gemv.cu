@@ -882,7 +882,7 @@ static int launch_warp_gi(int gi, const GemvParams& p, dim3 grid, dim3 block, si
   return launch_kernel(gl_gemv_warp_kernel<NB, XT, MT, 0>, p, grid, block, smem, st);
 }
 template <typename XT>
-static int launch_fast(int NB, int MT, int gi, const GemvParams& p, dim3 grid, dim3 block, size_t smem, cudaStream_t st) {
+static int launch_warp(int NB, int MT, int gi, const GemvParams& p, dim3 grid, dim3 block, size_t smem, cudaStream_t st) {
   if (NB == 4) return MT == 1 ? launch_warp_gi<4, XT, 1>(gi, p, grid, block, smem, st) : launch_warp_gi<4, XT, 2>(gi, p, grid, block, smem, st);
   return MT == 1 ? launch_warp_gi<2, XT, 1>(gi, p, grid, block, smem, st) : launch_warp_gi<2, XT, 2>(gi, p, grid, block, smem, st);
 }
