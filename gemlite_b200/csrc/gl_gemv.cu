@@ -724,8 +724,9 @@ static int json_int(const char* js, const char* key, int dflt) {
   return atoi(p + 1);
 }
 
-// Plan for the warp-independent kernel; returns false when its preconditions do not hold.
-static bool plan_warp(const gl_matmul_args* a, GemvPlan* pl, const char* js) {
+// One attempt at a plan for the warp-independent kernel with `c_in0` column groups per CTA and a shared-memory budget;
+// returns false when the kernel's preconditions do not hold or the budget is exceeded.
+static bool plan_warp_with(const gl_matmul_args* a, GemvPlan* pl, const char* js, int c_in0, size_t smem_limit) {
   const int e = a->elements_per_sample;
   if (!(a->W_nbits == 4 || a->W_nbits == 2) || a->M > 16 || a->N % 32 != 0 || a->K % (4 * e) != 0) return false;
   if (a->group_size % (4 * e) != 0) return false;
@@ -738,7 +739,7 @@ static bool plan_warp(const gl_matmul_args* a, GemvPlan* pl, const char* js) {
     if (nit < 8 || nit % 8 != 0) return false;
     return gi <= 4 ? (nit % gi == 0) : (nit % gi == 0 || gi % nit == 0);
   };
-  int c_in = a->M <= 4 ? 1 : (a->M <= 8 ? 4 : 8);   // measured on 8192x8192: M = 4 runs 12.6 us as 8x1 CTAs, 13.4 us as 2x4 with a cluster of 4
+  int c_in = c_in0;
   int s_in = 0, cluster = 0;
   if (js) {
     c_in = json_int(js, "c_in", c_in);
@@ -762,6 +763,7 @@ static bool plan_warp(const gl_matmul_args* a, GemvPlan* pl, const char* js) {
     s_in = 8 / c_in; if (s_in < 1) s_in = 1; if (s_in > S) s_in = S;
     cluster = S / s_in;
     while (cluster > 8 && s_in * c_in < (a->M <= 8 ? 16 : 8)) { s_in <<= 1; cluster >>= 1; }
+    while (cluster > 8) cluster >>= 1;                              // fewer, longer slices when a cluster cannot hold them all
   }
   if (cluster < 1 || cluster > 8 || (cluster & (cluster - 1)) != 0 || s_in < 1 || s_in * c_in > (a->M <= 8 ? 16 : 8)) return false;
   if (c_in > 1 && s_in > 15) return false;                          // one named barrier per slice
@@ -769,12 +771,26 @@ static bool plan_warp(const gl_matmul_args* a, GemvPlan* pl, const char* js) {
   const int nit = T / (s_in * cluster), nseg = (nit + gi - 1) / gi;
   const size_t smem = (size_t)s_in * nit * H * a->M * 64 + (size_t)s_in * c_in * (nseg * 32 * 12 + 16) +
                       (size_t)s_in * a->M * c_in * 32 * 4 + 16;
-  if (smem > 200 * 1024) return false;
+  if (smem > smem_limit) return false;
   pl->warp_kernel = 1; pl->gi = gi; pl->s_in = s_in; pl->c_in = c_in; pl->cluster = cluster; pl->splitK = cluster;
   pl->MT = a->M <= 8 ? 1 : 2;
   pl->warps_n = s_in * c_in; pl->tiles = colgroups / c_in; pl->smem = smem;
   pl->slice_iters = nit; pl->max_seg = nseg;
   return true;
+}
+
+// Plan for the warp-independent kernel.  Without a cache entry the CTA shape starts from what was measured best on
+// 8192 x 8192 (8 slices x 1 column group up to 4 batch rows: M = 4 runs 12.6 us that way against 13.4 us as 2 x 4 with a
+// cluster of 4; 2 x 4 up to 8 rows; 1 x 8 above) and widens the column groups (which shrinks the staged activations per
+// CTA) until two CTAs fit an SM's shared memory, then until one does.
+static bool plan_warp(const gl_matmul_args* a, GemvPlan* pl, const char* js) {
+  if (js && json_int(js, "s_in", 0) > 0) return plan_warp_with(a, pl, js, json_int(js, "c_in", 1), 200 * 1024);
+  const int first = a->M <= 4 ? 1 : (a->M <= 8 ? 4 : 8);
+  const size_t budgets[2] = {110 * 1024, 200 * 1024};
+  for (int b = 0; b < 2; ++b)
+    for (int c = first; c <= 8; c <<= 1)
+      if (plan_warp_with(a, pl, js, c, budgets[b])) return true;
+  return false;
 }
 
 static void plan_for(const gl_matmul_args* a, GemvPlan* pl, bool force_workspace = false) {

@@ -165,3 +165,23 @@ def test_input_validation(lib):
     y = layer(x.cuda().view(1, 1, 128))                                           # N-D input keeps its leading dims
     assert y.shape == (1, 1, 64)
     assert layer(torch.empty(0, 128, dtype=torch.float16, device="cuda")).shape == (0, 64)
+
+
+@pytest.mark.parametrize("M", [1, 4, 8, 16])
+def test_decode_kernel_covers_long_k(lib, M):
+    """K = 28672 (a Llama-70B down projection): the staged activations of a whole K range no longer fit one CTA for
+    M >= 4, so the planner has to widen the CTA's column groups / add cluster slices instead of leaving the
+    warp-independent kernel."""
+    import ctypes
+    from gemlite_b200 import core
+    N, K = 1024, 28672
+    x, W_q, s, z, b = make_a16wn(N, K, 4, 128, torch.bfloat16, seed=300 + M, M=M)
+    layer = build_layer(W_q, s, z, b, 4, 128, torch.bfloat16)
+    xs = x.cuda()
+    y = layer(xs).float().cpu().numpy()
+    assert rel_fro(y, exact_a16wn(x, W_q, s, z, b, 128)) < TOL
+    out = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    a = core._fill_args(xs, layer.bias, layer.W_q, layer.scales, layer.zeros, None, None, out, layer.get_meta_args(), -1)
+    # at M = 16 the 16 x 3584 activations of a cluster slice plus the per-group constants exceed one CTA: general kernel
+    want_name = (b"gl_gemv_warp_kernel",) if M <= 8 else (b"gl_gemv_warp_kernel", b"gl_gemv_stream_kernel")
+    assert lib.gl_matmul_kernel_name(ctypes.byref(a)) in want_name
