@@ -749,21 +749,30 @@ static bool plan_warp_with(const gl_matmul_args* a, GemvPlan* pl, const char* js
   while (c_in > 1 && colgroups % c_in != 0) c_in >>= 1;
   if (c_in < 1 || c_in > 16 || colgroups % c_in != 0) return false;
   if (s_in <= 0 || cluster <= 0) {
-    // slices: fewest "waves x (iterations per warp + fixed per-warp cost)" over the power-of-two splits that fit
+    // slices: fewest "waves x (iterations per warp + fixed per-warp cost)" over every split into equal slices that fit
+    // (K = 3584 has 112 iterations: 7 slices of 16 fill the machine where the power-of-two choice, 2 of 56, cannot)
     const int64_t warp_slots = (int64_t)gl_num_sms() * 16;
+    const int max_warps = a->M <= 8 ? 16 : 8;
     int S = 0;
     int64_t best_cost = 0;
-    for (int cand = 1; cand <= 64; cand <<= 1) {
+    for (int cand = 1; cand <= 64; ++cand) {
       if (!slice_ok(cand)) continue;
+      // cand = s_in x cluster with a power-of-two cluster of at most 8 and a CTA of at most max_warps warps
+      bool fits = false;
+      for (int cl = 1; cl <= 8; cl <<= 1)
+        if (cand % cl == 0 && (cand / cl) * c_in <= max_warps && (32 * c_in) % cl == 0) { fits = true; break; }
+      if (!fits) continue;
       const int64_t waves = ((int64_t)colgroups * cand + warp_slots - 1) / warp_slots;
       const int64_t cost = waves * (T / cand + 12);
       if (S == 0 || cost < best_cost) { S = cand; best_cost = cost; }
     }
     if (S == 0) return false;
-    s_in = 8 / c_in; if (s_in < 1) s_in = 1; if (s_in > S) s_in = S;
-    cluster = S / s_in;
-    while (cluster > 8 && s_in * c_in < (a->M <= 8 ? 16 : 8)) { s_in <<= 1; cluster >>= 1; }
-    while (cluster > 8) cluster >>= 1;                              // fewer, longer slices when a cluster cannot hold them all
+    // prefer CTAs of at most 8 warps (two per SM), then up to max_warps
+    s_in = 0;
+    for (int lim = 8; lim <= max_warps && s_in == 0; lim <<= 1)
+      for (int cl = 1; cl <= 8; cl <<= 1)
+        if (S % cl == 0 && (S / cl) * c_in <= lim && (32 * c_in) % cl == 0) { cluster = cl; s_in = S / cl; break; }
+    if (s_in == 0) return false;
   }
   if (cluster < 1 || cluster > 8 || (cluster & (cluster - 1)) != 0 || s_in < 1 || s_in * c_in > (a->M <= 8 ? 16 : 8)) return false;
   if (c_in > 1 && s_in > 15) return false;                          // one named barrier per slice

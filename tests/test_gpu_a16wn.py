@@ -167,14 +167,14 @@ def test_input_validation(lib):
     assert layer(torch.empty(0, 128, dtype=torch.float16, device="cuda")).shape == (0, 64)
 
 
+@pytest.mark.parametrize("N,K", [(1024, 28672), (8192, 3584), (1280, 8192), (8192, 1024)])
 @pytest.mark.parametrize("M", [1, 4, 8, 16])
-def test_decode_kernel_covers_long_k(lib, M):
-    """K = 28672 (a Llama-70B down projection): the staged activations of a whole K range no longer fit one CTA for
-    M >= 4, so the planner has to widen the CTA's column groups / add cluster slices instead of leaving the
-    warp-independent kernel."""
+def test_decode_kernel_covers_llama_shard_shapes(lib, M, N, K):
+    """Per-GPU shapes of Llama-70B linears under tensor parallelism.  K = 28672: the staged activations of a whole K
+    range no longer fit one CTA for M >= 4, so the planner widens the CTA's column groups / adds cluster slices.
+    K = 3584 = 112 iterations: 7 slices of 16 iterations (no power-of-two split fills the machine).  K = 1024: 4 slices."""
     import ctypes
     from gemlite_b200 import core
-    N, K = 1024, 28672
     x, W_q, s, z, b = make_a16wn(N, K, 4, 128, torch.bfloat16, seed=300 + M, M=M)
     layer = build_layer(W_q, s, z, b, 4, 128, torch.bfloat16)
     xs = x.cuda()
@@ -182,6 +182,6 @@ def test_decode_kernel_covers_long_k(lib, M):
     assert rel_fro(y, exact_a16wn(x, W_q, s, z, b, 128)) < TOL
     out = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
     a = core._fill_args(xs, layer.bias, layer.W_q, layer.scales, layer.zeros, None, None, out, layer.get_meta_args(), -1)
-    # at M = 16 the 16 x 3584 activations of a cluster slice plus the per-group constants exceed one CTA: general kernel
-    want_name = (b"gl_gemv_warp_kernel",) if M <= 8 else (b"gl_gemv_warp_kernel", b"gl_gemv_stream_kernel")
+    # at M = 16, K = 28672 the 16 x 3584 activations of a cluster slice plus the per-group constants exceed one CTA: general kernel
+    want_name = (b"gl_gemv_warp_kernel",) if (M <= 8 or K < 28672) else (b"gl_gemv_warp_kernel", b"gl_gemv_stream_kernel")
     assert lib.gl_matmul_kernel_name(ctypes.byref(a)) in want_name
