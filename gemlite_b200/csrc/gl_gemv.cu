@@ -521,19 +521,32 @@ __global__ void __launch_bounds__(MT == 1 ? 512 : 256, MT == 1 ? 1 : 2) gl_gemv_
   asm volatile("cp.async.wait_all;" ::: "memory");
   __syncwarp();
   {                                                   // per-group fp32 constants: out += alpha * acc + beta * xsum
+    // a lane converts 8 consecutive columns of one group at a time (two 16-byte loads, four 16-byte stores)
     const float zs = p.zero_is_scalar ? (float)(*reinterpret_cast<const int32_t*>(p.zeros)) : 0.f;
-    for (int i = lane; i < nseg * 32; i += 32) {
-      float al = 1.f, z = zs;
-      if (p.W_group_mode >= 2) al = XTr::to_float(ms[i]);
-      if ((p.W_group_mode == 1 || p.W_group_mode >= 3) && !p.zero_is_scalar) z = XTr::to_float(mz[i]);
-      float be;
-      if (p.W_group_mode == 4)      be = z - XTr::BIAS * al;
-      else if (p.W_group_mode == 3) be = -(XTr::BIAS + z) * al;
-      else if (p.W_group_mode == 1) be = -(XTr::BIAS + z);
-      else                          be = -XTr::BIAS * al;
-      alpha[i] = al;
-      beta[i] = be;
+    const bool has_s = p.W_group_mode >= 2, has_z = (p.W_group_mode == 1 || p.W_group_mode >= 3) && !p.zero_is_scalar;
+    for (int i = lane * 8; i < nseg * 32; i += 256) {
+      uint4 sv = make_uint4(0u, 0u, 0u, 0u), zv = make_uint4(0u, 0u, 0u, 0u);
+      if (has_s) sv = *reinterpret_cast<const uint4*>(ms + i);
+      if (has_z) zv = *reinterpret_cast<const uint4*>(mz + i);
+      const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w}, zw[4] = {zv.x, zv.y, zv.z, zv.w};
+      float al[8], be[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float a1 = has_s ? XTr::to_float((uint16_t)((sw[j >> 1] >> (16 * (j & 1))) & 0xffffu)) : 1.f;
+        const float z1 = has_z ? XTr::to_float((uint16_t)((zw[j >> 1] >> (16 * (j & 1))) & 0xffffu)) : zs;
+        float b1;
+        if (p.W_group_mode == 4)      b1 = z1 - XTr::BIAS * a1;
+        else if (p.W_group_mode == 3) b1 = -(XTr::BIAS + z1) * a1;
+        else if (p.W_group_mode == 1) b1 = -(XTr::BIAS + z1);
+        else                          b1 = -XTr::BIAS * a1;
+        al[j] = a1; be[j] = b1;
+      }
+      *reinterpret_cast<float4*>(alpha + i) = make_float4(al[0], al[1], al[2], al[3]);
+      *reinterpret_cast<float4*>(alpha + i + 4) = make_float4(al[4], al[5], al[6], al[7]);
+      *reinterpret_cast<float4*>(beta + i) = make_float4(be[0], be[1], be[2], be[3]);
+      *reinterpret_cast<float4*>(beta + i + 4) = make_float4(be[4], be[5], be[6], be[7]);
     }
+    __syncwarp();
   }
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
