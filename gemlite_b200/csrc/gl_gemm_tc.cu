@@ -554,6 +554,7 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
         const h2 zs2 = (p.W_group_mode == 1 || p.W_group_mode == 3) ? z2 : H2<XT>::from_float(0.f);
         const h2 ss2 = (p.W_group_mode >= 2) ? s2 : H2<XT>::from_float(1.f);
         uint32_t wv[RPW];                                    // all packed words first: the stores below may alias them for the compiler
+        uint32_t keep_lo = 0u, keep_hi = 0u;
 #pragma unroll
         for (int cc = 0; cc < RPW; ++cc) wv[cc] = wst[(c_begin + cc) * BN + nl];
 #pragma unroll
@@ -564,8 +565,16 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
           uint32_t P[HALF];
 #pragma unroll
           for (int a = 0; a < HALF; ++a) {
-            uint32_t bits = ((w >> (NB * a)) & FMASK) | kMagic;
-            h2 q = __hsub2(*reinterpret_cast<h2*>(&bits), magic);            // exact integer code
+            h2 q;                                                            // exact integer code
+            if constexpr (NB == 8 && sizeof(XT) == 2 && H2<XT>::MAGIC == 0x43004300u) {
+              // bf16 has 7 mantissa bits: the byte goes in as its low 7 bits (128 + q7) and its top bit (128 or 256)
+              const uint32_t v = w >> (8 * a);
+              uint32_t lo7 = (v & 0x007F007Fu) | kMagic, top = (v & 0x00800080u) | kMagic;
+              q = __hadd2(__hsub2(*reinterpret_cast<h2*>(&lo7), magic), __hsub2(*reinterpret_cast<h2*>(&top), magic));
+            } else {
+              uint32_t bits = ((w >> (NB * a)) & FMASK) | kMagic;
+              q = __hsub2(*reinterpret_cast<h2*>(&bits), magic);
+            }
             // mode 4: q*s + z' in one rounding; the other modes as (q - z) * s with z = 0 / s = 1 where absent:
             // the same roundings as the reference's dequantize() (triton_kernels/utils.py:73-105)
             if (FMA) q = __hfma2(q, s2, z2);
@@ -580,7 +589,10 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
             Hh[j] = __byte_perm(P[2 * j], P[2 * j + 1], 0x7632);
           }
           const int chunk0 = c * (E / 8);
-          if constexpr (NB == 4) {
+          if constexpr (NB == 8) {                         // a word holds 4 k: two consecutive packed rows make one 16-byte chunk
+            if ((cc & 1) == 0) { keep_lo = L[0]; keep_hi = Hh[0]; }
+            else *reinterpret_cast<uint4*>(brow + (((c >> 1) ^ (nl & 7)) << 4)) = make_uint4(keep_lo, keep_hi, L[0], Hh[0]);
+          } else if constexpr (NB == 4) {
             *reinterpret_cast<uint4*>(brow + (((chunk0) ^ (nl & 7)) << 4)) = make_uint4(L[0], L[1], Hh[0], Hh[1]);
           } else {
             constexpr int CH = HALF / 8;                     // chunks per half (1 for 2-bit, 2 for 1-bit)
@@ -649,7 +661,7 @@ static TcPath classify(const gl_matmul_args* a) {
   const int e = a->elements_per_sample;
   // A16Wn: fp16 / bf16 activations, 4- or 2-bit codes packed in int32 along K, group-wise meta data
   if ((a->x_dtype == GL_BF16 || a->x_dtype == GL_FP16) && a->input_dtype == a->x_dtype && a->w_dtype == GL_INT32 &&
-      (a->W_nbits == 4 || a->W_nbits == 2 || a->W_nbits == 1) && e == 32 / a->W_nbits) {
+      (a->W_nbits == 8 || a->W_nbits == 4 || a->W_nbits == 2 || a->W_nbits == 1) && e == 32 / a->W_nbits) {
     if (a->w_stride_n != 1 || a->w_stride_k != a->N || a->N % 4 != 0) return TC_NONE;
     if (a->group_size % 64 != 0) return TC_NONE;
     if (!(a->channel_scale_mode == 0 || a->channel_scale_mode == 1)) return TC_NONE;
@@ -745,10 +757,12 @@ int gl_gemm_tc_launch(const gl_matmul_args* a, cudaStream_t st) {
 #define GL_A16(XT, NB)                                                                              \
     (BN == 256 ? launch_a16_kernel<XT, NB, 256, 3>(tmA, tmB, p, st) : launch_a16_kernel<XT, NB, 128, 4>(tmA, tmB, p, st))
     if (a->x_dtype == GL_BF16) {
+      if (a->W_nbits == 8) return GL_A16(__nv_bfloat16, 8);
       if (a->W_nbits == 4) return GL_A16(__nv_bfloat16, 4);
       if (a->W_nbits == 2) return GL_A16(__nv_bfloat16, 2);
       return GL_A16(__nv_bfloat16, 1);
     }
+    if (a->W_nbits == 8) return GL_A16(__half, 8);
     if (a->W_nbits == 4) return GL_A16(__half, 4);
     if (a->W_nbits == 2) return GL_A16(__half, 2);
     return GL_A16(__half, 1);

@@ -31,7 +31,7 @@ def _status_word():
     return int(ws[off:off + 4].view(torch.int32).item())
 
 
-@pytest.mark.parametrize("nbits,gs", [(4, 128), (2, 64), (1, 128), (4, 64)])
+@pytest.mark.parametrize("nbits,gs", [(4, 128), (2, 64), (1, 128), (4, 64), (8, 128)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_a16wn_prefill_ragged(lib, nbits, gs, dtype):
     from gemlite_b200 import helper
