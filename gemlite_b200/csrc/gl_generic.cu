@@ -4,7 +4,7 @@
 // :509-737 for MX / NV block-scaled weights), computed the way those kernels define it:
 // unpack -> dequantise in the scale dtype (triton_kernels/utils.py:73-105) -> multiply with
 // the activations -> fp32 (int32 for INT8 x INT8) accumulation -> channel scales -> bias.
-// One thread owns one output column for up to MBG batch rows and walks K; it is the
+// Eight threads share one output column (one K slice each, added in slice order) for up to MBG batch rows; it is the
 // correctness-complete path for shapes and modes that the streaming and tensor-core kernels
 // do not specialise, not a fast path.
 #include "gl_common.cuh"
@@ -30,11 +30,15 @@ __device__ __forceinline__ uint64_t load_word(const void* w, int64_t idx, int dt
   }
 }
 
-__global__ void __launch_bounds__(128) gl_generic_kernel(const GenParams p) {
+// A CTA is 32 columns x KS slices of K: thread (x, y) walks the packed words of slice y of column x, the slices are
+// added in slice order through shared memory (deterministic), slice 0 finishes the column.
+constexpr int KS = 8;
+
+__global__ void __launch_bounds__(32 * KS) gl_generic_kernel(const GenParams p) {
   const gl_matmul_args& a = p.a;
-  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  const int n = blockIdx.x * 32 + threadIdx.x;
   const int m0 = blockIdx.y * MBG;
-  if (n >= a.N) return;
+  const bool valid = n < a.N;
   const int e = a.elements_per_sample;
   const uint64_t mask = (a.W_nbits >= 64) ? ~0ull : ((1ull << a.W_nbits) - 1ull);
   const int gs = a.group_size;
@@ -48,7 +52,9 @@ __global__ void __launch_bounds__(128) gl_generic_kernel(const GenParams p) {
   if (a.zero_is_scalar && a.zeros) zscalar = gl_load_as_float(a.zeros, 0, a.zeros_dtype);
   const bool x_fp4 = p.is_mx && a.x_dtype == GL_UINT8;   // activations packed e2m1, two per byte
 
-  for (int kw = 0; kw < a.K / e; ++kw) {
+  const int kwords = a.K / e, per = (kwords + KS - 1) / KS;
+  const int kw_begin = min(kwords, (int)threadIdx.y * per), kw_end = valid ? min(kwords, kw_begin + per) : kw_begin;
+  for (int kw = kw_begin; kw < kw_end; ++kw) {
     const uint64_t word = load_word(a.w, (int64_t)kw * a.w_stride_k + (int64_t)n * a.w_stride_n, a.w_dtype);
     for (int j = 0; j < e; ++j) {
       const int k = kw * e + j;
@@ -114,6 +120,16 @@ __global__ void __launch_bounds__(128) gl_generic_kernel(const GenParams p) {
     }
   }
 
+  __shared__ float s_acc[KS][MBG][32];
+  __shared__ int s_iacc[KS][MBG][32];
+#pragma unroll
+  for (int i = 0; i < MBG; ++i) { s_acc[threadIdx.y][i][threadIdx.x] = acc[i]; s_iacc[threadIdx.y][i][threadIdx.x] = iacc[i]; }
+  __syncthreads();
+  if (threadIdx.y != 0 || !valid) return;
+#pragma unroll
+  for (int i = 0; i < MBG; ++i)
+    for (int y = 1; y < KS; ++y) { acc[i] += s_acc[y][i][threadIdx.x]; iacc[i] += s_iacc[y][i][threadIdx.x]; }
+
   const int md = (a.meta_dtype == GL_FP16 || a.meta_dtype == GL_BF16 || a.meta_dtype == GL_FP32) ? a.meta_dtype : GL_FP32;
 #pragma unroll
   for (int i = 0; i < MBG; ++i) {
@@ -154,7 +170,7 @@ int gl_generic_launch(const gl_matmul_args* a, cudaStream_t st) {
   }
   if ((a->channel_scale_mode == 2 || a->channel_scale_mode == 3) && a->scales_x == nullptr)
     GL_FAIL(GL_E_INVALID, "gl_matmul: channel_scale_mode %d needs activation scales", a->channel_scale_mode);
-  dim3 block(128), grid((unsigned)gl_cdiv(a->N, 128), (unsigned)gl_cdiv(a->M, MBG));
+  dim3 block(32, KS), grid((unsigned)gl_cdiv(a->N, 32), (unsigned)gl_cdiv(a->M, MBG));
   gl_generic_kernel<<<grid, block, 0, st>>>(p);
   GL_LAUNCH_CHECK("gl_generic_kernel");
   return GL_OK;
