@@ -466,8 +466,13 @@ __device__ __forceinline__ uint32_t and_or(uint32_t v, uint32_t mask, uint32_t m
 // GI: iterations per quantisation group when it divides 8 (1, 2, 4); 0 = a multiple of 8 (p.gi), flushed at run time
 template <int NB, typename XT, int MT, int GI>
 __global__ void __launch_bounds__(MT == 1 ? 512 : 256, MT == 1 ? 1 : 2) gl_gemv_warp_kernel(const GemvParams p) {
-  constexpr int E = 32 / NB, H = E / 8, HALF = E / 2, U = 8;
-  constexpr uint32_t FMASK = ((1u << NB) - 1u) * 0x00010001u;
+  // 8-bit words hold 4 k: two iterations share one 16-byte unit of staged activations (W8 below)
+  constexpr bool W8 = NB == 8;
+  constexpr int E = 32 / NB, H = W8 ? 1 : E / 8, HALF = E / 2, U = 8;
+  // bf16 has 7 mantissa bits: a byte enters as (128 + low 7 bits) and (128 + 128 * top bit) in two MMAs, bias 256 in all
+  constexpr bool SPLIT8 = W8 && XTraits<XT>::MAGIC == 0x43004300u;
+  constexpr float BIASV = SPLIT8 ? 256.f : XTraits<XT>::BIAS;
+  constexpr uint32_t FMASK = SPLIT8 ? 0x007F007Fu : ((1u << NB) - 1u) * 0x00010001u;
   constexpr uint32_t ONES = OnesPair<XT>::V;
   using XTr = XTraits<XT>;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -482,7 +487,7 @@ __global__ void __launch_bounds__(MT == 1 ? 512 : 256, MT == 1 ? 1 : 2) gl_gemv_
   const int ccols = c_in * 32;
 
   // shared: x fragments [slice] | per-warp {alpha, beta, raw scales, raw zeros, zero unit} | partial tiles [slice]
-  const int xs_slice_units = nit * H * p.M * 4;
+  const int xs_slice_units = (W8 ? nit / 2 : nit * H) * p.M * 4;
   uint4* xs = reinterpret_cast<uint4*>(smem_raw) + (size_t)sl * xs_slice_units;
   unsigned char* wbase = smem_raw + (size_t)s_in * xs_slice_units * 16 + (size_t)warp * (nseg * 32 * 12 + 16);
   float* alpha = reinterpret_cast<float*>(wbase);
@@ -535,10 +540,10 @@ __global__ void __launch_bounds__(MT == 1 ? 512 : 256, MT == 1 ? 1 : 2) gl_gemv_
         const float a1 = has_s ? XTr::to_float((uint16_t)((sw[j >> 1] >> (16 * (j & 1))) & 0xffffu)) : 1.f;
         const float z1 = has_z ? XTr::to_float((uint16_t)((zw[j >> 1] >> (16 * (j & 1))) & 0xffffu)) : zs;
         float b1;
-        if (p.W_group_mode == 4)      b1 = z1 - XTr::BIAS * a1;
-        else if (p.W_group_mode == 3) b1 = -(XTr::BIAS + z1) * a1;
-        else if (p.W_group_mode == 1) b1 = -(XTr::BIAS + z1);
-        else                          b1 = -XTr::BIAS * a1;
+        if (p.W_group_mode == 4)      b1 = z1 - BIASV * a1;
+        else if (p.W_group_mode == 3) b1 = -(BIASV + z1) * a1;
+        else if (p.W_group_mode == 1) b1 = -(BIASV + z1);
+        else                          b1 = -BIASV * a1;
         al[j] = a1; be[j] = b1;
       }
       *reinterpret_cast<float4*>(alpha + i) = make_float4(al[0], al[1], al[2], al[3]);
@@ -553,10 +558,24 @@ __global__ void __launch_bounds__(MT == 1 ? 512 : 256, MT == 1 ? 1 : 2) gl_gemv_
   // ---- stage this slice of x in B-fragment order (shared by the c_in warps of the slice) -------------------
   {
     const uint16_t* xg = reinterpret_cast<const uint16_t*>(p.x) + (size_t)it0 * 4 * E;
-    const int row_units = nit * 4 * H;                             // 16-byte units per batch row
+    const int row_units = W8 ? nit * 2 : nit * 4 * H;              // 16-byte units per batch row
     const int tg = wc * 32 + lane, tgn = ccols;
     for (int m = 0; m < p.M; ++m) {
       const uint16_t* xr = xg + (size_t)m * p.K;
+      if (W8) {
+        // unit (iteration pair j, packed row t): {b0, b1} of iteration 2j then of 2j + 1, where b0 = (x0, x2) and
+        // b1 = (x1, x3) of the row's four k (bytes 0 / 2 and 1 / 3 of the packed word share an extraction)
+        for (int u = tg; u < row_units; u += tgn) {
+          const int j = u >> 2, tt = u & 3;
+          const uint2 ev = *reinterpret_cast<const uint2*>(xr + ((2 * j) * 4 + tt) * 4);
+          const uint2 od = *reinterpret_cast<const uint2*>(xr + ((2 * j + 1) * 4 + tt) * 4);
+          uint4 o;
+          o.x = __byte_perm(ev.x, ev.y, 0x5410); o.y = __byte_perm(ev.x, ev.y, 0x7632);
+          o.z = __byte_perm(od.x, od.y, 0x5410); o.w = __byte_perm(od.x, od.y, 0x7632);
+          xs[((j * p.M + m) << 2) + tt] = o;
+        }
+        continue;
+      }
       for (int u = tg; u < row_units; u += tgn) {
         const int row = u / H, hh = u - row * H;                   // packed row inside the slice, piece of the row
         const uint2 lo = *reinterpret_cast<const uint2*>(xr + row * E + 4 * hh);
@@ -619,8 +638,28 @@ __global__ void __launch_bounds__(MT == 1 ? 512 : 256, MT == 1 ? 1 : 2) gl_gemv_
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const uint32_t w[4] = {(uint32_t)buf[u].x, (uint32_t)buf[u].y, (uint32_t)buf[u].z, (uint32_t)buf[u].w};
+      if constexpr (W8) {
+        // one MMA K extent per iteration: bytes 0 / 2 of a word are k slots (2t, 2t+1), bytes 1 / 3 slots (2t+8, 2t+9)
 #pragma unroll
-      for (int hh = 0; hh < H; ++hh) {
+        for (int mt = 0; mt < MT; ++mt) {
+          const uint4 xv = xcur[mt][0];
+          const uint32_t b0 = (u & 1) ? xv.z : xv.x, b1 = (u & 1) ? xv.w : xv.y;
+          uint32_t lo[4], hi[4];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) { lo[c] = and_or(w[c], fmask, magic); hi[c] = and_or(w[c] >> 8, fmask, magic); }
+          mma16816<XT>(acc[0][mt], lo[0], lo[1], hi[0], hi[1], b0, b1);
+          mma16816<XT>(acc[1][mt], lo[2], lo[3], hi[2], hi[3], b0, b1);
+          if constexpr (SPLIT8) {                        // the top bit of every byte: 128 + 128 * bit
+#pragma unroll
+            for (int c = 0; c < 4; ++c) { lo[c] = and_or(w[c], 0x00800080u, magic); hi[c] = and_or(w[c] >> 8, 0x00800080u, magic); }
+            mma16816<XT>(acc[0][mt], lo[0], lo[1], hi[0], hi[1], b0, b1);
+            mma16816<XT>(acc[1][mt], lo[2], lo[3], hi[2], hi[3], b0, b1);
+          }
+          mma16816<XT>(accS[mt], ones0, ones1, ones2, ones3, b0, b1);
+        }
+      }
+#pragma unroll
+      for (int hh = 0; hh < (W8 ? 0 : H); ++hh) {
         uint4 xb[MT];
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) xb[mt] = xcur[mt][hh * pstride[mt]];
@@ -650,8 +689,10 @@ __global__ void __launch_bounds__(MT == 1 ? 512 : 256, MT == 1 ? 1 : 2) gl_gemv_
         }
       }
       if (reload) { buf[u] = ldg_stream(wnext); wnext += wstep; }
+      if (!W8 || (u & 1)) {                            // two 8-bit iterations share a unit
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt) xcur[mt] += xstride[mt];
+        for (int mt = 0; mt < MT; ++mt) xcur[mt] += xstride[mt];
+      }
       if (GI > 0) {
         if ((u % (GI > 0 ? GI : 1)) == (GI > 0 ? GI : 1) - 1) { flush(seg, false); ++seg; }
       }
@@ -741,11 +782,12 @@ static int json_int(const char* js, const char* key, int dflt) {
 // returns false when the kernel's preconditions do not hold or the budget is exceeded.
 static bool plan_warp_with(const gl_matmul_args* a, GemvPlan* pl, const char* js, int c_in0, size_t smem_limit) {
   const int e = a->elements_per_sample;
-  if (!(a->W_nbits == 4 || a->W_nbits == 2) || a->M > 16 || a->N % 32 != 0 || a->K % (4 * e) != 0) return false;
+  if (!(a->W_nbits == 8 || a->W_nbits == 4 || a->W_nbits == 2) || a->M > 16 || a->N % 32 != 0 || a->K % (4 * e) != 0) return false;
   if (a->group_size % (4 * e) != 0) return false;
   const int T = a->K / (4 * e), H = e / 8, gi = a->group_size / (4 * e);
   const int colgroups = a->N / 32;
   if (!(gi == 1 || gi == 2 || gi == 4 || gi % 8 == 0)) return false;
+  if (a->W_nbits == 8 && gi % 8 != 0) return false;               // 8-bit: only the run-time flush variant is built
   auto slice_ok = [&](int S) {
     if (S < 1 || T % S != 0) return false;
     const int nit = T / S;
@@ -791,7 +833,8 @@ static bool plan_warp_with(const gl_matmul_args* a, GemvPlan* pl, const char* js
   if (c_in > 1 && s_in > 15) return false;                          // one named barrier per slice
   if (!slice_ok(s_in * cluster) || (32 * c_in) % cluster != 0) return false;
   const int nit = T / (s_in * cluster), nseg = (nit + gi - 1) / gi;
-  const size_t smem = (size_t)s_in * nit * H * a->M * 64 + (size_t)s_in * c_in * (nseg * 32 * 12 + 16) +
+  const size_t x_bytes = a->W_nbits == 8 ? (size_t)nit * a->M * 32 : (size_t)nit * H * a->M * 64;   // staged activations per slice
+  const size_t smem = (size_t)s_in * x_bytes + (size_t)s_in * c_in * (nseg * 32 * 12 + 16) +
                       (size_t)s_in * a->M * c_in * 32 * 4 + 16;
   if (smem > smem_limit) return false;
   pl->warp_kernel = 1; pl->gi = gi; pl->s_in = s_in; pl->c_in = c_in; pl->cluster = cluster; pl->splitK = cluster;
@@ -819,7 +862,7 @@ static void plan_for(const gl_matmul_args* a, GemvPlan* pl, bool force_workspace
   const int e = a->elements_per_sample;
   const int T = a->K / (4 * e);
   pl->MT = a->M <= 8 ? 1 : (a->M <= 16 ? 2 : 4);
-  const int H = e / 8;
+  const int H = e >= 8 ? e / 8 : 1;   // (packed bytes, e = 4, never reach the general kernel; this keeps the sizes below defined)
   int warps_n = a->N <= 32 ? 1 : 2;
   int split_req = 0, cluster_req = -1;
   const char* cfg_js = nullptr;
@@ -921,6 +964,8 @@ static int launch_warp_gi(int gi, const GemvParams& p, dim3 grid, dim3 block, si
 }
 template <typename XT>
 static int launch_warp(int NB, int MT, int gi, const GemvParams& p, dim3 grid, dim3 block, size_t smem, cudaStream_t st) {
+  if (NB == 8) return MT == 1 ? launch_kernel(gl_gemv_warp_kernel<8, XT, 1, 0>, p, grid, block, smem, st)
+                              : launch_kernel(gl_gemv_warp_kernel<8, XT, 2, 0>, p, grid, block, smem, st);
   if (NB == 4) return MT == 1 ? launch_warp_gi<4, XT, 1>(gi, p, grid, block, smem, st) : launch_warp_gi<4, XT, 2>(gi, p, grid, block, smem, st);
   return MT == 1 ? launch_warp_gi<2, XT, 1>(gi, p, grid, block, smem, st) : launch_warp_gi<2, XT, 2>(gi, p, grid, block, smem, st);
 }
@@ -942,7 +987,7 @@ static int launch_nb(int NB, int MT, const GemvParams& p, dim3 grid, dim3 block,
 int gl_gemv_stream_supported(const gl_matmul_args* a) {
   const int e = a->elements_per_sample;
   if (a->M < 1 || a->M > 32) return 0;
-  if (!(a->W_nbits == 4 || a->W_nbits == 2 || a->W_nbits == 1)) return 0;
+  if (!(a->W_nbits == 8 || a->W_nbits == 4 || a->W_nbits == 2 || a->W_nbits == 1)) return 0;
   if (a->w_dtype != GL_INT32 || e != 32 / a->W_nbits) return 0;
   if (!(a->x_dtype == GL_BF16 || a->x_dtype == GL_FP16) || a->input_dtype != a->x_dtype) return 0;
   if (a->w_stride_n != 1 || a->w_stride_k != a->N) return 0;
@@ -967,6 +1012,7 @@ int gl_gemv_stream_supported(const gl_matmul_args* a) {
   if (a->bias && ((uintptr_t)a->bias & 15)) return 0;
   GemvPlan pl;
   plan_for(a, &pl);
+  if (a->W_nbits == 8 && !pl.warp_kernel) return 0;               // packed bytes: only the warp-independent kernel
   if (pl.tiles > kMaxTiles) return 0;
   if (pl.smem > 200 * 1024) return 0;
   return 1;
@@ -1015,6 +1061,7 @@ static int gemv_launch_impl(const gl_matmul_args* a, cudaStream_t st, const Gemv
     if (a->x_dtype == GL_BF16) return launch_warp<__nv_bfloat16>(a->W_nbits, pl.MT, pl.gi, p, grid, block, pl.smem, st);
     return launch_warp<__half>(a->W_nbits, pl.MT, pl.gi, p, grid, block, pl.smem, st);
   }
+  if (a->W_nbits == 8) GL_FAIL(GL_E_UNSUPPORTED, "gl_matmul: packed 8-bit weights have no general streaming kernel for this shape");
   if (a->x_dtype == GL_BF16) return launch_nb<__nv_bfloat16>(a->W_nbits, pl.MT, p, grid, block, pl.smem, st);
   return launch_nb<__half>(a->W_nbits, pl.MT, p, grid, block, pl.smem, st);
 }

@@ -185,3 +185,21 @@ def test_decode_kernel_covers_llama_shard_shapes(lib, M, N, K):
     # at M = 16, K = 28672 the 16 x 3584 activations of a cluster slice plus the per-group constants exceed one CTA: general kernel
     want_name = (b"gl_gemv_warp_kernel",) if (M <= 8 or K < 28672) else (b"gl_gemv_warp_kernel", b"gl_gemv_stream_kernel")
     assert lib.gl_matmul_kernel_name(ctypes.byref(a)) in want_name
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M", [1, 3, 8, 16])
+def test_decode_kernel_packed_8bit(lib, M, dtype):
+    """Packed 8-bit group-wise weights (A16W8 HQQ) at decode sizes on the warp-independent kernel: a word holds 4 k, and
+    for bf16 (7 mantissa bits) every byte enters the MMA as its low 7 bits and its top bit separately."""
+    import ctypes
+    from gemlite_b200 import core
+    N, K = 2048, 4096
+    x, W_q, s, z, b = make_a16wn(N, K, 8, 128, dtype, seed=800 + M, M=M)
+    layer = build_layer(W_q, s, z, b, 8, 128, dtype)
+    xs = x.cuda()
+    y = layer(xs).float().cpu().numpy()
+    assert rel_fro(y, exact_a16wn(x, W_q, s, z, b, 128)) < TOL
+    out = torch.empty((M, N), dtype=dtype, device="cuda")
+    a = core._fill_args(xs, layer.bias, layer.W_q, layer.scales, layer.zeros, None, None, out, layer.get_meta_args(), -1)
+    assert lib.gl_matmul_kernel_name(ctypes.byref(a)) == b"gl_gemv_warp_kernel"
