@@ -453,7 +453,7 @@ def sweep_gemm(device, only=None):
     except Exception:
         pass
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.int8, device=device)
-    dense_peak = {"A16W4": 2250.0, "A16W2": 2250.0, "FP8": 4500.0, "MXFP4": 9000.0, "NVFP4": 9000.0}     # nominal dense TFLOP/s
+    dense_peak = {"A16W4": 2250.0, "A16W2": 2250.0, "A16W8": 2250.0, "FP8": 4500.0, "MXFP4": 9000.0, "NVFP4": 9000.0}     # nominal dense TFLOP/s
 
     def timed(fn, reps=10):
         for _ in range(3):
@@ -470,9 +470,9 @@ def sweep_gemm(device, only=None):
 
     def make(fmt):
         g = torch.Generator(device=device).manual_seed(7)
-        if fmt in ("A16W4", "A16W2"):
+        if fmt in ("A16W4", "A16W2", "A16W8"):
             N = K = 8192
-            nbits, gs = (4, 128) if fmt == "A16W4" else (2, 64)
+            nbits, gs = {"A16W4": (4, 128), "A16W2": (2, 64), "A16W8": (8, 128)}[fmt]
             W_q = torch.randint(0, 2 ** nbits, (N, K), generator=g, device=device, dtype=torch.int32).to(torch.uint8)
             sc = (torch.randn(N * K // gs, 1, generator=g, device=device).abs() * 0.02).to(torch.bfloat16)
             z = (torch.rand(N * K // gs, 1, generator=g, device=device) * (2 ** nbits - 1)).to(torch.bfloat16)
@@ -486,14 +486,14 @@ def sweep_gemm(device, only=None):
 
     res = []
     stream = torch.cuda.Stream(device)
-    cases = (("A16W4", (64, 256, 1024, 4096, 8192)), ("A16W2", (1, 16, 64, 256, 1024, 4096, 8192)), ("FP8", (1, 16, 128, 1024, 4096)),
+    cases = (("A16W4", (64, 256, 1024, 4096, 8192)), ("A16W2", (1, 16, 64, 256, 1024, 4096, 8192)), ("A16W8", (1, 16, 1024)), ("FP8", (1, 16, 128, 1024, 4096)),
              ("MXFP4", (1, 64, 512, 4096, 16384)), ("NVFP4", (1, 64, 512, 4096, 16384)))
     if only is not None:
         cases = ((only[0], (only[1],)),)
     for fmt, Ms in cases:
         try:
             layer, K, N = make(fmt)
-            wbytes = N * K // {"FP8": 1, "A16W2": 4}.get(fmt, 2)
+            wbytes = N * K // {"FP8": 1, "A16W8": 1, "A16W2": 4}.get(fmt, 2)
             for M in Ms:
                 x = torch.randn(M, K, dtype=torch.bfloat16, device=device)
                 row = {"format": fmt, "M": M, "N": N, "K": K}
