@@ -1,0 +1,62 @@
+"""CPU: kernel selection and workspace sizing are host-only code in the library (no device call, pointers are never
+dereferenced), so the planner can be swept over shapes without a GPU: it must not fail on any of them, and the shapes
+of the benchmark configurations must land on the kernels built for them."""
+import ctypes
+import itertools
+
+from gemlite_b200 import _lib
+from gemlite_b200.dtypes import DType
+
+FAKE = 0x7F0000000000        # 16-byte aligned, never dereferenced
+
+
+def _args(M, N, K, nbits, gs, dtype=DType.BF16):
+    a = _lib.GLMatmulArgs()
+    for f in ("x", "w", "scales", "zeros", "out", "workspace"):
+        setattr(a, f, FAKE)
+    a.workspace_bytes = 1 << 30
+    a.M, a.N, a.K, a.W_nbits, a.group_size, a.elements_per_sample = M, N, K, nbits, gs, 32 // nbits
+    a.input_dtype = a.x_dtype = a.out_dtype = a.meta_dtype = a.zeros_dtype = dtype.value
+    a.w_dtype = DType.INT32.value
+    a.W_group_mode, a.channel_scale_mode, a.matmul_type = 4, 0, -1
+    a.w_stride_k, a.w_stride_n, a.s_stride_g, a.s_stride_n = N, 1, N, 1
+    return a
+
+
+def _plan(*shape):
+    L = _lib.lib()
+    a = _args(*shape)
+    return L.gl_matmul_kernel_name(ctypes.byref(a)).decode(), int(L.gl_matmul_workspace_bytes(ctypes.byref(a)))
+
+
+def test_planner_survives_a_sweep_of_shapes():
+    L = _lib.lib()
+    counter = int(L.gl_matmul_counter_bytes())
+    names = set()
+    for M, (N, K), (nbits, gs) in itertools.product(
+            (1, 2, 3, 4, 8, 9, 16, 17, 32, 33, 64, 200, 4096),
+            ((8192, 8192), (2032, 3968), (1024, 28672), (8192, 3584), (1280, 8192), (8192, 1024), (32, 256), (4096, 128)),
+            ((8, 128), (4, 128), (4, 64), (4, 32), (2, 64), (1, 128))):
+        if K % gs:
+            continue
+        name, ws = _plan(M, N, K, nbits, gs)
+        assert name.startswith("gl_"), (M, N, K, nbits, gs, name)
+        assert ws >= counter or name == "gl_generic_kernel"      # the general kernel needs no workspace
+        names.add(name)
+    assert {"gl_gemv_warp_kernel", "gl_gemv_stream_kernel", "gl_gemm_tc_kernel"} <= names
+
+
+def test_benchmark_shapes_land_on_their_kernels():
+    for M in (1, 2, 4, 8, 16):
+        assert _plan(M, 8192, 8192, 4, 128)[0] == "gl_gemv_warp_kernel"
+        assert _plan(M, 8192, 8192, 2, 64)[0] == "gl_gemv_warp_kernel"
+        assert _plan(M, 8192, 8192, 8, 128)[0] == "gl_gemv_warp_kernel"
+    for M in (17, 64, 256, 1024, 4096, 8192):
+        assert _plan(M, 8192, 8192, 4, 128)[0] == "gl_gemm_tc_kernel"
+    # Llama-70B shard shapes at decode size
+    for N, K in ((8192, 3584), (1280, 8192), (8192, 1024), (7168, 8192)):
+        assert _plan(1, N, K, 4, 128)[0] == "gl_gemv_warp_kernel"
+    # few-tile tensor-core problems ask for room for their split-K partial tiles
+    counter = int(_lib.lib().gl_matmul_counter_bytes())
+    assert _plan(64, 8192, 8192, 4, 128)[1] >= counter + 2 * 64 * 8192 * 4
+    assert _plan(4096, 8192, 8192, 4, 128)[1] == counter
