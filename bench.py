@@ -30,11 +30,17 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 N_FEAT = K_FEAT = 8192
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the headline kernel, from the ncu capture summarised in
-# profiles/gemv_a16w4_m1_8192x8192.md (algorithmic bytes: 35,700,736)
-NCU_DRAM_BYTES_PER_LAUNCH = 35725824
 GROUP = 128
 LAYERS = 32
+
+
+def bench_reference():
+    """Figures measured outside this script and kept beside it in bench_reference.json: the DRAM bytes of one launch
+    of the headline kernel from an ncu capture, and the reference's own Triton kernels timed on a B200."""
+    try:
+        return json.load(open(os.path.join(ROOT, "bench_reference.json")))
+    except Exception:
+        return {}
 
 
 def algorithmic_bytes(M, N, K, nbits, group, itemsize=2, bias=True):
@@ -184,6 +190,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel decoder-layer step")
     ap.add_argument("--case", default=None, help="run one format:M case of the sweep a few times and print its time (for profiling), e.g. MXFP4:4096")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -311,7 +318,7 @@ def main():
                 "eager_ms_per_step": ms_eager, "eager_value": total_bytes / (ms_eager * 1e-3) / 1e9, "finite": finite},
         "gpu_launches": args.steps * LAYERS,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH, "peak_kind": peak_kind, "frac_of_nominal_8000": achieved / 8000.0,
+                     "traffic": bench_reference().get("ncu_dram_bytes_per_launch", {}).get(kernel_name), "peak_kind": peak_kind, "frac_of_nominal_8000": achieved / 8000.0,
                      "bytes_per_launch": bytes_per_launch},
         "clocks": clocks,
     }
@@ -329,75 +336,150 @@ def main():
             result["cpu_baseline"] = cpu_path_sample(seconds=12.0)
         except Exception as e:  # the CPU sample must not lose the GPU numbers
             result["cpu_baseline"] = {"value": None, "unit": "GB/s", "cores": os.cpu_count(), "kind": "port", "sample": "failed: %s" % e}
-    if dist is not None:
+    if not args.no_tp:
         try:
+            torch.cuda.empty_cache()
             tp = tensor_parallel_step(device, rank, world, dist)
             if rank == 0:
                 result["tensor_parallel"] = tp
         except Exception as e:  # the weak-scaling line above stands on its own
             if rank == 0:
-                result["tensor_parallel"] = {"error": str(e)[:200]}
+                result["tensor_parallel"] = {"error": str(e)[:300]}
+    if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
     if rank == 0:
         print(json.dumps(result))
 
 
-def tensor_parallel_step(device, rank, world, dist, steps=30):
-    """Decode step (M = 1) through the seven A16W4 linears of one Llama-70B decoder layer, tensor-parallel over
-    all ranks: column-parallel qkv and gate/up, row-parallel o_proj and down_proj with one NCCL all-reduce each.
-    Device time per step, max over ranks."""
+def tensor_parallel_step(device, rank, world, dist, Ms=(1, 8, 32, 64, 2048), steps=30):
+    """The seven A16W4 linears of one Llama-70B decoder layer (hidden 8192, intermediate 28672, 64 q / 8 kv heads of
+    128), tensor-parallel over all ranks: column-parallel fused qkv and gate/up, row-parallel o_proj and down_proj
+    with an all-reduce each -- the one-shot peer-memory kernel while the result fits its receive slots (decode
+    sizes), NCCL above.  For every M: device time per step as a CUDA-graph replay (max over ranks) and the relative
+    Frobenius error of the sharded result against the same layers unsharded on one GPU (rank 0 holds both)."""
     from gemlite_b200 import tp
     hidden, inter, heads, kv_heads, head_dim = 8192, 28672, 64, 8, 128
-    blk = tp.LlamaLinears(hidden, inter, heads, kv_heads, head_dim, world, rank, device, seed=11)
-    x = torch.randn(1, hidden, device=device, dtype=torch.bfloat16) * 0.1
-    for _ in range(5):
-        y = blk(x)
-    dist.barrier()
-    torch.cuda.synchronize(device)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        y = blk(x)
-    e1.record()
-    torch.cuda.synchronize(device)
-    ms_eager = e0.elapsed_time(e1) / steps
-    # the same step captured once in a CUDA graph (NCCL all-reduces included) and replayed: device-bound time
-    ms_graph, graph = None, None
-    side = torch.cuda.Stream(device)
-    try:
-        side.wait_stream(torch.cuda.current_stream(device))
-        with torch.cuda.stream(side):
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=side):
-                y = blk(x)
-        side.synchronize()
-    except Exception:
-        graph = None
-    # replay only if every rank captured: a rank replaying all-reduces alone would wait for ever
-    ok = torch.tensor([0.0 if graph is None else 1.0], device=device, dtype=torch.float64)
-    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-    if ok.item() == 1.0:
-        with torch.cuda.stream(side):
-            for _ in range(3):
-                graph.replay()
-            side.synchronize()
-            dist.barrier()
-            e0.record(side)
-            for _ in range(steps):
-                graph.replay()
-            e1.record(side)
-            side.synchronize()
-        ms_graph = e0.elapsed_time(e1) / steps
-    t = torch.tensor([ms_eager, ms_graph if ms_graph is not None else 0.0], device=device, dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_eager = t[0].item()
-    ms_graph = t[1].item() if ms_graph is not None else None
+    comm = tp.PeerComm(device, slot_bytes=2 << 20) if world > 1 else None
+    blk = tp.LlamaLinears(hidden, inter, heads, kv_heads, head_dim, world, rank, device, seed=11, comm=comm)
+    full = tp.LlamaLinears(hidden, inter, heads, kv_heads, head_dim, 1, 0, device, seed=11) if (world > 1 and rank == 0) else None
     weights = (heads + 2 * kv_heads) * head_dim * hidden + hidden * heads * head_dim + 3 * inter * hidden   # elements
-    return {"workload": "Llama-70B decoder-layer linears, A16W4 gs128, M=1, tp%d" % world,
-            "ms_per_step": ms_graph if ms_graph is not None else ms_eager, "ms_per_step_eager": ms_eager,
-            "timing": "CUDA graph replay" if ms_graph is not None else "eager", "all_reduces_per_step": 2, "finite": bool(torch.isfinite(y.float()).all()),
-            "packed_weight_GB_per_step_all_ranks": weights / 2 / 1e9}
+    rows = []
+    side = torch.cuda.Stream(device)
+    for M in Ms:
+        gx = torch.Generator(device=device).manual_seed(500 + M)             # the same activations on every rank
+        x = (torch.randn(M, hidden, generator=gx, device=device) * 0.1).to(torch.bfloat16)
+        n_steps = steps if M <= 64 else 5
+        for _ in range(3):
+            y = blk(x)
+        rel = None
+        if full is not None:
+            y1 = full(x).float()
+            rel = float((y.float() - y1).norm() / y1.norm())
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n_steps):
+            y = blk(x)
+        e1.record()
+        torch.cuda.synchronize(device)
+        ms_eager = e0.elapsed_time(e1) / n_steps
+        # the same step captured once in a CUDA graph (all-reduces included) and replayed: device-bound time
+        ms_graph, graph = None, None
+        try:
+            side.wait_stream(torch.cuda.current_stream(device))
+            with torch.cuda.stream(side):
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    y = blk(x)
+            side.synchronize()
+        except Exception:
+            graph = None
+        ok = torch.tensor([0.0 if graph is None else 1.0], device=device, dtype=torch.float64)
+        if dist is not None:   # replay only if every rank captured: a rank replaying all-reduces alone would wait
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if ok.item() == 1.0:
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    graph.replay()
+                side.synchronize()
+                if dist is not None:
+                    dist.barrier()
+                e0.record(side)
+                for _ in range(n_steps):
+                    graph.replay()
+                e1.record(side)
+                side.synchronize()
+            ms_graph = e0.elapsed_time(e1) / n_steps
+        t = torch.tensor([ms_eager, ms_graph if ms_graph is not None else 0.0], device=device, dtype=torch.float64)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        one_shot = comm is not None and M * hidden * 2 <= comm.slot_bytes
+        rows.append({"M": M, "ms_per_step": t[1].item() if ms_graph is not None else t[0].item(), "ms_per_step_eager": t[0].item(),
+                     "timing": "CUDA graph replay" if ms_graph is not None else "eager",
+                     "all_reduce": "none (one GPU)" if world == 1 else ("one-shot peer-memory kernel" if one_shot else "NCCL"),
+                     "rel_fro_vs_unsharded": rel, "finite": bool(torch.isfinite(y.float()).all())})
+        del graph
+    status = comm.status()[0] if comm is not None else 0
+    if comm is not None:
+        comm.close()
+    return {"workload": "Llama-70B decoder-layer linears, A16W4 gs128, tp%d" % world, "all_reduces_per_step": 0 if world == 1 else 2,
+            "packed_weight_GB_per_step_all_ranks": weights / 2 / 1e9, "parity_tolerance": 1e-2, "wait_status": status, "per_M": rows,
+            "ms_per_step": rows[0]["ms_per_step"]}
+
+
+# -------------------------------------------------------------------------------------------------
+# Output checks of the sweeps (outside every timed region): a plain torch fp32 product of the same quantised
+# operands, decoded with torch ops, on up to 256 sampled rows.  No library matmul kernel is involved.
+_E2M1 = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0)
+
+
+def _decode_fp4(q_bytes, scale_bytes, group, e8m0):
+    R, K2 = q_bytes.shape
+    lut = torch.tensor(_E2M1, dtype=torch.float32, device=q_bytes.device)
+    vals = torch.stack((lut[(q_bytes & 0xF).long()], lut[(q_bytes >> 4).long()]), dim=-1).view(R, K2 * 2)
+    sb = scale_bytes.view(torch.uint8)[:R]
+    sc = torch.pow(2.0, sb.float() - 127.0) if e8m0 else sb.view(torch.float8_e4m3fn).float()
+    return (vals.view(R, -1, group) * sc.view(R, -1, 1)).view(R, K2 * 2)
+
+
+def _dequant_packed_int(layer):
+    """fp32 [K, N] weights of a packed A16Wn layer from its stored tensors: codes * s + z' (fma mode) or (codes - z) * s."""
+    nbits, e, gs = layer.W_nbits, layer.elements_per_sample, layer.group_size
+    Wp = layer.W_q                                         # int32 [K/e, N]
+    shifts = (torch.arange(e, device=Wp.device, dtype=torch.int32) * nbits).view(1, e, 1)
+    codes = ((Wp.unsqueeze(1) >> shifts) & (2 ** nbits - 1)).reshape(-1, Wp.shape[1]).float()      # [K, N]
+    sc = layer.scales.float().repeat_interleave(gs, 0)
+    z = layer.zeros.float().repeat_interleave(gs, 0)
+    return codes * sc + z if layer.W_group_mode == 4 else (codes - z) * sc
+
+
+def check_output(layer, fmt, x, y, W_ref=None):
+    """Relative Frobenius error of y = layer(x) against the torch product of the identical quantised operands."""
+    from gemlite_b200 import quant_utils as qu
+    M = x.shape[0]
+    idx = torch.arange(0, M, max(1, M // 256), device=x.device)[:256]
+    if fmt.startswith("A16"):
+        W = W_ref if W_ref is not None else _dequant_packed_int(layer)
+        ref = x[idx].float() @ W + (layer.bias.float() if layer.bias is not None else 0.0)
+    elif fmt == "FP8":
+        xq, sx = qu.scale_activations_per_token(x, torch.float8_e4m3fn)
+        ref = (xq[idx].float() @ layer.W_q.float()) * sx[idx].view(-1, 1) * layer.scales.float().view(1, -1)
+    else:
+        gs, e8 = (32, True) if fmt == "MXFP4" else (16, False)
+        wq, sw = layer.W_q.t().contiguous(), layer.scales.contiguous().view(torch.uint8)
+        if fmt == "MXFP4":
+            xq, sx = qu.scale_activations_mxfp4(x, scale_layout=0)
+            meta = 1.0
+        else:
+            xq, sx, mx = qu.scale_activations_nvfp4(x, scale_layout=0)
+            meta = 1.0 / (float(layer.meta_scale.item()) * float(mx.item()))
+        Wd = W_ref if W_ref is not None else _decode_fp4(wq, sw, gs, e8)
+        ref = (_decode_fp4(xq[idx], sx[idx], gs, e8) @ Wd.T) * meta
+    got = y[idx].float()
+    return float((got - ref).norm() / ref.norm())
 
 
 def sweep(device, layers, stream, hbm_peak, bf16_peak):
@@ -405,6 +487,7 @@ def sweep(device, layers, stream, hbm_peak, bf16_peak):
     from gemlite_b200 import _lib, core
     L = _lib.lib()
     res = []
+    W_last = _dequant_packed_int(layers[-1])               # reference weights of the layer whose output is checked
     for M in (1, 2, 4, 8, 16):
         x = torch.randn(M, K_FEAT, device=device, dtype=torch.bfloat16)
         outs = [torch.empty(M, N_FEAT, device=device, dtype=torch.bfloat16) for _ in layers]
@@ -434,8 +517,11 @@ def sweep(device, layers, stream, hbm_peak, bf16_peak):
             us = e0.elapsed_time(e1) / 10 / len(layers) * 1e3
             b = algorithmic_bytes(M, N_FEAT, K_FEAT, 4, GROUP)
             flops = 2.0 * M * N_FEAT * K_FEAT
+            torch.cuda.synchronize(device)
+            rel = check_output(layers[-1], "A16W4", x, outs[-1], W_ref=W_last)
             res.append({"format": "A16W4", "M": M, "us_per_launch": us, "GBps": b / us / 1e3, "frac_hbm": b / us / 1e3 / hbm_peak,
-                        "TFLOPs": flops / us / 1e6, "kernel": L.gl_matmul_kernel_name(ctypes.byref(structs[0])).decode()})
+                        "TFLOPs": flops / us / 1e6, "kernel": L.gl_matmul_kernel_name(ctypes.byref(structs[0])).decode(),
+                        "checked": rel < 1e-2, "rel_fro": rel})
         except Exception as e:
             res.append({"format": "A16W4", "M": M, "error": str(e)[:200]})
     return res
@@ -447,11 +533,7 @@ def sweep_gemm(device, only=None):
     L2 is flushed between timed calls; min of 10 calls; TFLOP/s = 2 M N K / time.  `ref_triton_ms` is the
     reference's own Triton kernel timed on a B200 when the golden fixtures were captured."""
     from gemlite_b200 import helper
-    ref = {}
-    try:
-        ref = json.load(open(os.path.join(ROOT, "tests", "golden", "triton_timings.json")))["timings"]
-    except Exception:
-        pass
+    ref = bench_reference().get("reference_triton_timings", {}).get("timings", {})
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.int8, device=device)
     dense_peak = {"A16W4": 2250.0, "A16W2": 2250.0, "A16W8": 2250.0, "FP8": 4500.0, "MXFP4": 9000.0, "NVFP4": 9000.0}     # nominal dense TFLOP/s
 
@@ -494,9 +576,16 @@ def sweep_gemm(device, only=None):
         try:
             layer, K, N = make(fmt)
             wbytes = N * K // {"FP8": 1, "A16W8": 1, "A16W2": 4}.get(fmt, 2)
+            W_ref = _dequant_packed_int(layer) if fmt.startswith("A16") else (
+                None if fmt == "FP8" else _decode_fp4(layer.W_q.t().contiguous(), layer.scales.contiguous().view(torch.uint8),
+                                                      32 if fmt == "MXFP4" else 16, fmt == "MXFP4"))
             for M in Ms:
                 x = torch.randn(M, K, dtype=torch.bfloat16, device=device)
                 row = {"format": fmt, "M": M, "N": N, "K": K}
+                rel = check_output(layer, fmt, x, layer(x), W_ref=W_ref)      # once, outside the timed region
+                row.update({"checked": rel < (1e-2 if fmt.startswith("A16") else 5e-3), "rel_fro": rel})
+                if fmt == "NVFP4":
+                    row["reference_parity"] = "oracle only: the reference's NVFP4 Triton kernels do not compile on sm_100 with Triton 3.6"
                 if M <= 512:
                     # small batch: host launch overhead would hide the kernels, so the forwards of several distinct
                     # layers (together larger than L2) are captured in one CUDA graph and replayed
@@ -521,8 +610,9 @@ def sweep_gemm(device, only=None):
                 r = ref.get("%s_%dx%d_M%d" % (fmt, K if fmt == "FP8" else N, N if fmt == "FP8" else K, M))
                 if r:
                     row["ref_triton_ms"] = r["min_ms"]
+                    row["ref_triton_protocol"] = "eager call, L2 flushed (separate capture)"
                 res.append(row)
-            del layer
+            del layer, W_ref
             torch.cuda.empty_cache()
         except Exception as e:
             res.append({"format": fmt, "error": str(e)[:200]})

@@ -36,6 +36,12 @@ class GLMatmulArgs(ctypes.Structure):
     ]
 
 
+class GLTpComm(ctypes.Structure):
+    """Mirror of ``struct gl_tp_comm``."""
+    _fields_ = [("rank", c_int32), ("world", c_int32), ("slot_bytes", c_uint64), ("wait_cycles", c_uint64),
+                ("buffers", c_void_p * 8)]
+
+
 # name -> (restype, argtypes); every symbol include/gemlite_b200.h declares
 SIGNATURES = {
     "gl_abi_version": (c_int32, []),
@@ -62,6 +68,14 @@ SIGNATURES = {
     "gl_cfg_get": (c_char_p, [c_char_p, c_char_p]),
     "gl_cfg_size": (c_int64, [c_char_p]),
     "gl_get_closest_m": (c_int32, [c_int32]),
+    "gl_tp_buffer_bytes": (c_uint64, [c_int32, c_uint64]),
+    "gl_tp_buffer_create": (c_int32, [c_uint64, ctypes.POINTER(c_void_p), c_void_p]),
+    "gl_tp_buffer_open": (c_int32, [c_void_p, ctypes.POINTER(c_void_p)]),
+    "gl_tp_buffer_close": (c_int32, [c_void_p]),
+    "gl_tp_buffer_destroy": (c_int32, [c_void_p]),
+    "gl_tp_allreduce": (c_int32, [ctypes.POINTER(GLTpComm), c_void_p, c_void_p, c_int64, c_int32, c_int32, c_void_p]),
+    "gl_tp_status": (c_int32, [ctypes.POINTER(GLTpComm), ctypes.POINTER(c_int32), ctypes.POINTER(ctypes.c_uint32)]),
+    "gl_silu_mul": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p]),
 }
 
 _lib = None

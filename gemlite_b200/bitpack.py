@@ -56,9 +56,8 @@ def _packing_bitwidth_of(t):
     return t.element_size() * 8
 
 
-@torch.library.custom_op("gemlite::unpack_over_cols_cuda", mutates_args=())
-def unpack_over_cols(W_q_packed: torch.Tensor, W_nbits: int, num_output_cols: int,
-                     dtype: torch.dtype = torch.uint8) -> torch.Tensor:
+def _unpack_over_cols_impl(W_q_packed: torch.Tensor, W_nbits: int, num_output_cols: int,
+                           dtype: torch.dtype = torch.uint8) -> torch.Tensor:
     """Inverse of :func:`pack_weights_over_cols`: [rows, cols_packed] -> [rows, num_output_cols].
 
     ``num_output_cols // cols_packed`` fields are taken from every word (bitpack.py:154-155)."""
@@ -74,14 +73,12 @@ def unpack_over_cols(W_q_packed: torch.Tensor, W_nbits: int, num_output_cols: in
     return out.view(rows, num_output_cols)
 
 
-@torch.library.register_fake("gemlite::unpack_over_cols_cuda")
-def _unpack_over_cols_fake(W_q_packed, W_nbits, num_output_cols, dtype):
+def _unpack_over_cols_fake(W_q_packed, W_nbits, num_output_cols, dtype=torch.uint8):
     return torch.empty((W_q_packed.shape[0], num_output_cols), dtype=dtype, device=W_q_packed.device)
 
 
-@torch.library.custom_op("gemlite::unpack_over_rows_cuda", mutates_args=())
-def unpack_over_rows(W_q_packed: torch.Tensor, W_nbits: int, num_output_rows: int,
-                     dtype: torch.dtype = torch.uint8) -> torch.Tensor:
+def _unpack_over_rows_impl(W_q_packed: torch.Tensor, W_nbits: int, num_output_rows: int,
+                           dtype: torch.dtype = torch.uint8) -> torch.Tensor:
     """Inverse of :func:`pack_weights_over_rows`: [rows_packed, cols] -> [num_output_rows, cols]."""
     _lib.require_cuda(W_q_packed, "W_q_packed")
     src = W_q_packed.contiguous()
@@ -95,17 +92,27 @@ def unpack_over_rows(W_q_packed: torch.Tensor, W_nbits: int, num_output_rows: in
     return out.view(num_output_rows, cols)
 
 
-@torch.library.register_fake("gemlite::unpack_over_rows_cuda")
-def _unpack_over_rows_fake(W_q_packed, W_nbits, num_output_rows, dtype):
+def _unpack_over_rows_fake(W_q_packed, W_nbits, num_output_rows, dtype=torch.uint8):
     return torch.empty((num_output_rows, W_q_packed.shape[1]), dtype=dtype, device=W_q_packed.device)
 
+
+def _register_op(name, impl, fake):
+    op = torch.library.custom_op("gemlite::" + name, mutates_args=())(impl)
+    torch.library.register_fake("gemlite::" + name)(fake)
+    return op
+
+
+# Operator names: the reference registers gemlite::unpack_over_{cols,rows}_{torch,triton} (gemlite/bitpack.py:146, 207,
+# 320, 383) and graphs traced against it carry those names; all of them are the one CUDA kernel here.
+unpack_over_cols_torch = _register_op("unpack_over_cols_torch", _unpack_over_cols_impl, _unpack_over_cols_fake)
+unpack_over_cols_triton = _register_op("unpack_over_cols_triton", _unpack_over_cols_impl, _unpack_over_cols_fake)
+unpack_over_rows_torch = _register_op("unpack_over_rows_torch", _unpack_over_rows_impl, _unpack_over_rows_fake)
+unpack_over_rows_triton = _register_op("unpack_over_rows_triton", _unpack_over_rows_impl, _unpack_over_rows_fake)
+unpack_over_cols = unpack_over_cols_triton
+unpack_over_rows = unpack_over_rows_triton
 
 # Names the reference exports (gemlite/bitpack.py:430-433 and the *_torch / *_triton pairs).
 pack_weights_over_cols_torch = pack_weights_over_cols
 pack_weights_over_cols_triton = pack_weights_over_cols
 pack_weights_over_rows_torch = pack_weights_over_rows
 pack_weights_over_rows_triton = pack_weights_over_rows
-unpack_over_cols_torch = unpack_over_cols
-unpack_over_cols_triton = unpack_over_cols
-unpack_over_rows_torch = unpack_over_rows
-unpack_over_rows_triton = unpack_over_rows

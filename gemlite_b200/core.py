@@ -179,6 +179,23 @@ def _make_scale_atoms(scales):
     return s2d.contiguous().view(N // 128, 4, 32, G // 4, 4).permute(0, 3, 2, 1, 4).contiguous()
 
 
+def _scale_atoms_of(scales):
+    """The 128x4-atom copy of MX / NV weight scales, kept as an attribute of the scales tensor itself (so that it lives
+    and dies with it and `get_tensor_args()` stays the reference's four tensors); rebuilt when the tensor was
+    modified in place or the attribute is missing (a tensor that did not come from `get_tensor_args()`)."""
+    if scales is None or scales.dim() != 2:
+        return None
+    key = (scales.data_ptr(), scales._version, tuple(scales.shape), tuple(scales.stride()))
+    cached = getattr(scales, "_gl_scale_atoms", None)
+    if cached is None or cached[0] != key:
+        cached = (key, _make_scale_atoms(scales))
+        try:
+            scales._gl_scale_atoms = cached
+        except Exception:       # a tensor subclass that refuses attributes: recomputed per call
+            pass
+    return cached[1]
+
+
 def _fill_args(x2d, bias, W_q, scales, zeros, scales_x, meta_scale, out, meta_args, matmul_type, w_atoms=None, sx_layout=0):
     (_, W_nbits, group_size, _, eps, input_dtype, output_dtype, _, meta_dtype, channel_scale_mode,
      W_group_mode, _) = meta_args
@@ -244,11 +261,10 @@ def forward_functional(
     channel_scale_mode = meta_args[9]
 
     scales_x, meta_scale = None, None
-    # tensor_args[4], when present, is the layer's derived copy of the weight scales as 128x4 scale atoms
+    # block-scaled fp4 layers: the derived copy of the weight scales as 128x4 scale atoms rides on the scales tensor
     w_atoms = None
-    if (len(tensor_args) > 4 and _KERNEL_OVERRIDE != 1 and channel_scale_mode == 4
-            and input_dtype in (DType.MXFP4, DType.NVFP4) and tensor_args[4].numel() > 0):
-        w_atoms = tensor_args[4]
+    if _KERNEL_OVERRIDE != 1 and channel_scale_mode == 4 and input_dtype in (DType.MXFP4, DType.NVFP4):
+        w_atoms = _scale_atoms_of(scales)
     sx_layout = 0 if w_atoms is None else 1
     if bool(meta_args[0]) and enable_activation_scaling(x.numel() // x.shape[-1]):
         if input_dtype in FP8_INT8_DTYPES and channel_scale_mode == 5:
@@ -548,23 +564,14 @@ class GemLiteLinear(torch.nn.Module):
         meta_scale = self.meta_scale
         if not isinstance(meta_scale, torch.Tensor):
             meta_scale = torch.tensor(meta_scale, dtype=torch.float32, device=self.W_q.device)
-        args = [self.W_q, self.scales, self.zeros, meta_scale]
         if self.channel_scale_mode == 4 and self.input_dtype in (DType.MXFP4, DType.NVFP4):
-            atoms = self._scale_atoms()
-            if atoms is not None:
-                args.append(atoms)
-        return args
+            _scale_atoms_of(self.scales)      # derived layout for the block-scaled tensor-core kernel, built once
+        return [self.W_q, self.scales, self.zeros, meta_scale]
 
     def _scale_atoms(self):
         """Derived, non-serialised copy of the MX / NV weight scales in the layout the block-scaled tensor-core
         kernel reads; rebuilt when the stored scales change."""
-        sc = self.scales
-        key = (sc.data_ptr(), sc._version, tuple(sc.shape), tuple(sc.stride()))
-        cached = self.__dict__.get("_atoms_cache")
-        if cached is None or cached[0] != key:
-            cached = (key, _make_scale_atoms(sc))
-            self.__dict__["_atoms_cache"] = cached
-        return cached[1]
+        return _scale_atoms_of(self.scales)
 
     def get_meta_args(self):
         return [int(self.scaled_activations), self.W_nbits, self.group_size, self.unpack_mask, self.elements_per_sample,

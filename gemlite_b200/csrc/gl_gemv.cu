@@ -1112,11 +1112,16 @@ static int noalloc_scratch_ptr(void** out) {
 extern "C" int gl_matmul_noalloc(const gl_matmul_args* a, void* stream) {
   if (int rc = gl_validate_matmul_args(a)) return rc;
   if (a->M == 0) return GL_OK;
-  if (gl_is_mx(a->input_dtype) || !gl_gemv_stream_supported(a))
+  // packed 8-bit words only run on the warp-independent kernel, which has no split-K-through-scratch form
+  if (gl_is_mx(a->input_dtype) || a->W_nbits == 8 || !gl_gemv_stream_supported(a))
     GL_FAIL(GL_E_UNSUPPORTED, "gl_matmul_noalloc: only the streaming decode kernel (packed 4/2/1-bit weights, fp16/bf16 "
                               "activations, M <= 32) has a built-in-scratch variant");
   GemvPlan pl;
   plan_for(a, &pl, /*force_workspace=*/true);
+  // the limits are checked on the plan that is launched, before anything is enqueued
+  if (pl.tiles > kMaxTiles || pl.smem > 200 * 1024)
+    GL_FAIL(GL_E_UNSUPPORTED, "gl_matmul_noalloc: this shape (M=%d N=%d K=%d) exceeds the streaming kernel's tile or shared-memory limits",
+            a->M, a->N, a->K);
   const uint64_t need = workspace_for_plan(a, pl);
   if (need > (uint64_t)GL_NOALLOC_SCRATCH_BYTES)
     GL_FAIL(GL_E_WORKSPACE, "gl_matmul_noalloc: this problem (M=%d N=%d, %d K slices) needs %llu bytes of scratch, the built-in "

@@ -146,6 +146,20 @@ def scale_activations_per_token(tensor: Tensor, w_dtype: torch.dtype, fp32_scale
     return q.view(shape), scales
 
 
+def scale_activations_per_token_torch(tensor: Tensor, w_dtype: torch.dtype, fp32_scale: bool = True) -> Tuple[Tensor, Tensor]:
+    """The same quantiser in plain torch ops (gemlite/quant_utils.py:261-283): callers and tests of the reference use
+    it as the comparison point for the kernel.  Rows are scaled by amax / qmax (at least 1e-6), clamped, and rounded
+    for integer targets."""
+    lo, hi = get_dtype_range(w_dtype)
+    t = tensor.to(torch.float32) if fp32_scale else tensor
+    rows = t.reshape(-1, t.shape[-1])
+    scales = rows.abs().amax(dim=1, keepdim=True).div(hi).clamp(min=1e-6)
+    q = (rows / scales).clamp(lo, hi)
+    if not w_dtype.is_floating_point:
+        q = q.round()
+    return q.to(w_dtype).view(tensor.shape), scales
+
+
 def _scale_buffer(M, G, pad, scale_layout, dtype, device):
     """Row layout [ceil_pad(M), G] (what the reference returns) or, for scale_layout=1, the 128x4 scale
     atoms the block-scaled tensor-core kernel reads: [ceil128(M)/128, G/4, 512] bytes."""

@@ -243,6 +243,43 @@ GL_API int64_t     gl_cfg_size(const char* family);                       /* ent
 /* M bucket used in signatures.  Replaces get_closest_m(), triton_kernels/utils.py:182-220. */
 GL_API int32_t     gl_get_closest_m(int32_t M);
 
+/* ---- tensor parallelism: one-shot all-reduce over peer memory ---------------------------------- */
+/* The reference has no multi-GPU code: under vLLM the host shards the layers and calls
+ * tensor_model_parallel_all_reduce after every row-parallel one (gemlite/vllm/onthefly.py:83-99).  These entry
+ * points are that host role for decode-size results ([M, N] of a few KB to a few MB), where an NCCL ring is bound by
+ * launch and hop latency: one kernel pushes the local partial result to every rank's receive area with plain stores
+ * to peer memory (NVLink / NVSwitch), publishes a per-chunk flag, waits (bounded) for the other ranks' flags and adds
+ * the received chunks in rank order, so every rank ends with bit-identical sums.
+ *
+ * Unlike the rest of the library, gl_tp_buffer_create / _destroy allocate and free device memory (cudaMalloc), once,
+ * at set-up: the receive areas must be exportable to the other processes.  Every rank creates one buffer of
+ * gl_tp_buffer_bytes(world, slot_bytes), sends its 64-byte handle to the other ranks by any host channel, opens
+ * theirs, and fills a gl_tp_comm.  One process per GPU; at most GL_TP_MAX_RANKS ranks. */
+#define GL_TP_MAX_RANKS 8
+#define GL_TP_MAX_CTAS 512
+#define GL_TP_HANDLE_BYTES 64
+typedef struct gl_tp_comm {
+  int32_t  rank, world;
+  uint64_t slot_bytes;                 /* largest all-reduce input in bytes (what the buffers were sized for) */
+  uint64_t wait_cycles;                /* SM cycles a flag wait may take before it gives up; 0 = about two seconds */
+  void*    buffers[GL_TP_MAX_RANKS];   /* buffers[r] = rank r's buffer as mapped in this process (own: the created pointer) */
+} gl_tp_comm;
+GL_API uint64_t gl_tp_buffer_bytes(int32_t world, uint64_t slot_bytes);
+GL_API int gl_tp_buffer_create(uint64_t bytes, void** ptr, uint8_t* handle /* GL_TP_HANDLE_BYTES */);  /* zero-filled, on the current device */
+GL_API int gl_tp_buffer_open(const uint8_t* handle, void** ptr);     /* map another rank's buffer (enables peer access) */
+GL_API int gl_tp_buffer_close(void* ptr);
+GL_API int gl_tp_buffer_destroy(void* ptr);
+/* out[i] = sum over ranks of in[i], i < count; `in` 16-byte aligned, count * sizeof(dtype) a multiple of 16 and
+ * <= slot_bytes; every rank must call it with the same count and dtype, in the same order.  A wait that runs out sets
+ * the communicator's status word (gl_tp_status) and leaves `out` of the affected chunks unwritten; nothing hangs. */
+GL_API int gl_tp_allreduce(const gl_tp_comm* c, const void* in, void* out, int64_t count, int32_t in_dtype,
+                           int32_t out_dtype, void* stream);
+/* Reads the status word (0 = no wait ever gave up) and the number of completed all-reduces.  Synchronous copy. */
+GL_API int gl_tp_status(const gl_tp_comm* c, int32_t* status, uint32_t* epoch);
+/* act[m, j] = silu(gate_up[m, j]) * gate_up[m, inter + j]: the element-wise step between a fused gate/up projection
+ * and the down projection of a decoder MLP (two torch ops in a host that runs the reference). fp16 / bf16. */
+GL_API int gl_silu_mul(const void* gate_up, void* out, int32_t M, int32_t inter, int32_t dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
