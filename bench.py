@@ -328,7 +328,11 @@ def main():
         del layers, arg_structs, outs
         torch.cuda.empty_cache()
         try:
-            result["sweep_gemm"] = sweep_gemm(device)
+            result["measured_mma_peak_tflops"] = measure_mma_peaks(device)
+        except Exception as e:
+            result["measured_mma_peak_tflops"] = {"error": str(e)[:200]}
+        try:
+            result["sweep_gemm"] = sweep_gemm(device, mma_peaks=result.get("measured_mma_peak_tflops"))
         except Exception as e:  # the extra formats must not lose the headline numbers
             result["sweep_gemm"] = [{"error": str(e)[:200]}]
     if rank == 0 and not args.no_cpu and world >= 1:
@@ -527,7 +531,33 @@ def sweep(device, layers, stream, hbm_peak, bf16_peak):
     return res
 
 
-def sweep_gemm(device, only=None):
+def measure_mma_peaks(device, iters=4000, reps=6):
+    """Tensor-pipe ceiling of this GPU per MMA kind: `reps` back-to-back launches of the library's resident-tile
+    tcgen05.mma kernel (no loads, no epilogue), TFLOP/s over the whole set, i.e. under the power cap the GEMMs see."""
+    from gemlite_b200 import _lib
+    from gemlite_b200.dtypes import DType
+    L = _lib.lib()
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    out = {}
+    for name, kind in (("bf16", DType.BF16), ("fp8", DType.FP8), ("int8", DType.INT8), ("mxfp4", DType.MXFP4), ("nvfp4", DType.NVFP4)):
+        flops = ctypes.c_double(0.0)
+        sp = torch.cuda.current_stream(device).cuda_stream
+        for _ in range(2):
+            if L.gl_mma_peak(kind.value, iters, status.data_ptr(), ctypes.byref(flops), sp) != 0:
+                raise RuntimeError(L.gl_last_error().decode())
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            L.gl_mma_peak(kind.value, iters, status.data_ptr(), ctypes.byref(flops), sp)
+        e1.record()
+        torch.cuda.synchronize(device)
+        out[name] = flops.value * reps / (e0.elapsed_time(e1) * 1e-3) / 1e12
+    out["wait_status"] = int(status.item())
+    return out
+
+
+def sweep_gemm(device, only=None, mma_peaks=None):
     """The other benchmark configurations through the public API (GemLiteLinear.forward incl. the fused
     activation quantiser): FP8 4096->14336, MXFP4 / NVFP4 16384x16384, A16W4 8192x8192 at prefill size.
     L2 is flushed between timed calls; min of 10 calls; TFLOP/s = 2 M N K / time.  `ref_triton_ms` is the
@@ -568,7 +598,7 @@ def sweep_gemm(device, only=None):
 
     res = []
     stream = torch.cuda.Stream(device)
-    cases = (("A16W4", (64, 256, 1024, 4096, 8192)), ("A16W2", (1, 16, 64, 256, 1024, 4096, 8192)), ("A16W8", (1, 16, 1024)), ("FP8", (1, 16, 128, 1024, 4096)),
+    cases = (("A16W4", (32, 64, 256, 1024, 4096, 8192)), ("A16W2", (1, 16, 64, 256, 1024, 4096, 8192)), ("A16W8", (1, 16, 1024)), ("FP8", (1, 16, 128, 1024, 4096)),
              ("MXFP4", (1, 64, 512, 4096, 16384)), ("NVFP4", (1, 64, 512, 4096, 16384)))
     if only is not None:
         cases = ((only[0], (only[1],)),)
@@ -607,6 +637,9 @@ def sweep_gemm(device, only=None):
                     row["ms"] = ms
                 tf = 2.0 * M * N * K / ms / 1e9
                 row.update({"TFLOPs": tf, "frac_dense_nominal": tf / dense_peak[fmt]})
+                pk = (mma_peaks or {}).get({"FP8": "fp8", "MXFP4": "mxfp4", "NVFP4": "nvfp4"}.get(fmt, "bf16"))
+                if pk:
+                    row["frac_measured_mma_peak"] = tf / pk
                 r = ref.get("%s_%dx%d_M%d" % (fmt, K if fmt == "FP8" else N, N if fmt == "FP8" else K, M))
                 if r:
                     row["ref_triton_ms"] = r["min_ms"]

@@ -76,6 +76,7 @@ SIGNATURES = {
     "gl_tp_allreduce": (c_int32, [ctypes.POINTER(GLTpComm), c_void_p, c_void_p, c_int64, c_int32, c_int32, c_void_p]),
     "gl_tp_status": (c_int32, [ctypes.POINTER(GLTpComm), ctypes.POINTER(c_int32), ctypes.POINTER(ctypes.c_uint32)]),
     "gl_silu_mul": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_void_p]),
+    "gl_mma_peak": (c_int32, [c_int32, c_int32, c_void_p, ctypes.POINTER(ctypes.c_double), c_void_p]),
 }
 
 _lib = None
@@ -103,7 +104,27 @@ def lib():
             fn.restype = restype
             fn.argtypes = argtypes
         _lib = handle
+        _load_shipped_config(handle)
     return _lib
+
+
+def _load_shipped_config(handle):
+    """Tile-config table shipped for this GPU (configs/<tag>.json, the tag contained in the device name, longest tag
+    first), loaded once when the library is first used: what the reference does at import (gemlite/core.py:913-933).
+    GEMLITE_B200_NO_SHIPPED_CONFIG=1 skips it."""
+    if os.environ.get("GEMLITE_B200_NO_SHIPPED_CONFIG") or not torch.cuda.is_available():
+        return
+    root = os.path.join(_HERE, "configs")
+    if not os.path.isdir(root):
+        return
+    try:
+        name = torch.cuda.get_device_properties(torch.cuda.current_device()).name.lower().replace(" ", "_")
+    except Exception:
+        return
+    for tag in sorted((f[:-5] for f in os.listdir(root) if f.endswith(".json")), key=len, reverse=True):
+        if tag in name:
+            handle.gl_cfg_load(os.fsencode(os.path.join(root, tag + ".json")), 0)
+            return
 
 
 def check(status):

@@ -243,8 +243,7 @@ def _fill_args(x2d, bias, W_q, scales, zeros, scales_x, meta_scale, out, meta_ar
 # ---------------------------------------------------------------------------------------------
 # Functional forward (custom op so that torch.compile / CUDA-graph capture see one opaque node)
 # ---------------------------------------------------------------------------------------------
-@torch.library.custom_op("gemlite::forward_functional", mutates_args=())
-def forward_functional(
+def _forward_impl(
     x: Tensor,
     bias: Union[None, Tensor],
     tensor_args: List[Tensor],
@@ -305,6 +304,10 @@ def forward_functional(
             raise Exception(msg)
         _lib.check(status)
     return out.view(out_shape)
+
+
+# the operator the reference registers (gemlite/core.py:193); eager module calls go to _forward_impl directly
+forward_functional = torch.library.custom_op("gemlite::forward_functional", mutates_args=())(_forward_impl)
 
 
 @torch.library.register_fake("gemlite::forward_functional")
@@ -372,6 +375,7 @@ class GemLiteLinear(torch.nn.Module):
 
     def _clear_pack_slots(self):
         self.__dict__.pop("_atoms_cache", None)
+        self.__dict__.pop("_arg_cache", None)
         for name in self._PACK_MUTATED_NAMES:
             self._clear_slot(name)
 
@@ -579,11 +583,57 @@ class GemLiteLinear(torch.nn.Module):
                 self.channel_scale_mode, self.W_group_mode, int(self.data_contiguous)]
 
     def forward_manual(self, x: Tensor, matmul_type: str = "GEMM") -> Tensor:
-        return forward_functional(x, self.bias, self.get_tensor_args(), self.get_meta_args(),
-                                  GEMLITE_MATMUL_TYPES_MAPPING[matmul_type])
+        return self._forward(x, GEMLITE_MATMUL_TYPES_MAPPING[matmul_type])
 
     def forward_auto_no_warmup(self, x: Tensor) -> Tensor:
-        return forward_functional(x, self.bias, self.get_tensor_args(), self.get_meta_args())
+        return self._forward(x, -1)
+
+    def _forward(self, x: Tensor, matmul_type: int) -> Tensor:
+        """Module call.  Under torch.compile the registered operator is used (one opaque node); in eager mode the
+        dispatcher is skipped, and layers without activation quantisation re-use a filled argument struct per
+        (batch rows, dtype, family): only the x / out / workspace pointers change between calls."""
+        if torch.compiler.is_compiling():
+            return forward_functional(x, self.bias, self.get_tensor_args(), self.get_meta_args(), matmul_type)
+        if self.scaled_activations or is_mx_dtype(self.input_dtype) or _KERNEL_OVERRIDE != 0 or x.device.type != "cuda":
+            return _forward_impl(x, self.bias, self.get_tensor_args(), self.get_meta_args(), matmul_type)
+        if not x.is_contiguous():
+            x = x.contiguous()
+        x2d = x.view(-1, x.shape[-1])
+        M = x2d.shape[0]
+        W_q, scales, zeros, bias = self.W_q, self.scales, self.zeros, self.bias
+        out_dtype = DTYPE_TO_TORCH[self.output_dtype.value]
+        if bias is not None and bias.dtype != out_dtype:
+            return _forward_impl(x, bias, self.get_tensor_args(), self.get_meta_args(), matmul_type)
+        out = torch.empty((M, W_q.shape[1]), dtype=out_dtype, device=x.device)
+        if M == 0:
+            return out.view(x.shape[:-1] + (W_q.shape[1],))
+        sig = (W_q.data_ptr(), scales.data_ptr(), zeros.data_ptr(), 0 if bias is None else bias.data_ptr(),
+               self.W_group_mode, self.channel_scale_mode, self.output_dtype)
+        cache = self.__dict__.setdefault("_arg_cache", {})
+        key = (M, x2d.dtype, matmul_type, x.device.index)
+        ent = cache.get(key)
+        L = _lib.lib()
+        if ent is None or ent[0] != sig:
+            a = _fill_args(x2d, bias, W_q, scales, zeros, None, None, out, self.get_meta_args(), matmul_type)
+            with torch.cuda.device(x.device):
+                need = int(L.gl_matmul_workspace_bytes(ctypes.byref(a)))
+            if len(cache) > 64:
+                cache.clear()
+            ent = (sig, a, need)
+            cache[key] = ent
+        a, need = ent[1], ent[2]
+        a.x, a.out = x2d.data_ptr(), out.data_ptr()
+        with torch.cuda.device(x.device):
+            ws = _workspace(x.device, need)
+            if ws is not None:
+                a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+            status = L.gl_matmul(ctypes.byref(a), _lib.current_stream_ptr(x.device))
+        if status != 0:
+            msg = L.gl_last_error().decode("utf-8", "replace")
+            if status == _lib.GL_E_UNSUPPORTED:
+                raise Exception(msg)
+            _lib.check(status)
+        return out.view(x.shape[:-1] + (W_q.shape[1],))
 
     # -- tile-config cache (core.py:838-906), kept in the C library --------------------------
     @staticmethod

@@ -82,6 +82,9 @@ KernelId select(const gl_matmul_args* a, int* family_out) {
   // 128-row tcgen05 tile takes 77 us), and the streaming kernel only covers what that kernel cannot take
   const bool stream_ok = !mx && gl_gemv_stream_supported(a);
   if (stream_ok && a->M <= 16) return K_STREAM;
+  // 17..32 rows: two launches of the warp-independent streaming kernel (16 rows each; the second reads the weights from
+  // L2) take about half the time of the 128-row tensor-core tile at these sizes
+  if (stream_ok && a->M <= 32 && gl_gemv_split_rows_ok(a)) return K_STREAM;
   if (gl_gemm_tc_supported(a)) return K_TC;
   if (stream_ok) return K_STREAM;
   return K_GENERIC;

@@ -14,6 +14,7 @@
 #include <map>
 #include <mutex>
 #include <string>
+#include <stdlib.h>
 #include <vector>
 #include "../../include/gemlite_b200.h"
 
@@ -228,6 +229,23 @@ extern "C" const char* gl_cfg_get(const char* family, const char* signature) {
   if (e == f->second.end()) return nullptr;
   g_tmp = e->second;
   return g_tmp.c_str();
+}
+
+// integer field `key` of the JSON object stored for (family, signature), or `dflt`; a cheap early-out when the cache is
+// empty keeps the per-launch cost of planners that consult it at one lock
+int gl_cfg_int(const char* family, const char* signature, const char* key, int dflt) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (g_cache.empty()) return dflt;
+  auto f = g_cache.find(family);
+  if (f == g_cache.end()) return dflt;
+  auto e = f->second.find(signature);
+  if (e == f->second.end()) return dflt;
+  const std::string pat = std::string("\"") + key + "\"";
+  size_t pos = e->second.find(pat);
+  if (pos == std::string::npos) return dflt;
+  pos = e->second.find(':', pos + pat.size());
+  if (pos == std::string::npos) return dflt;
+  return atoi(e->second.c_str() + pos + 1);
 }
 
 extern "C" int64_t gl_cfg_size(const char* family) {

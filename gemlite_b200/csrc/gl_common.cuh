@@ -35,12 +35,15 @@ static inline int64_t gl_cdiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
 // number of SMs of the current device (cached per device id)
 int gl_num_sms();
+// integer field of a tile-config cache entry, or dflt (gl_cfg.cpp)
+int gl_cfg_int(const char* family, const char* signature, const char* key, int dflt);
 
 // ---- family launchers (each returns GL_OK / GL_E_*; GL_E_UNSUPPORTED = "not my case") -----
 int gl_gemv_stream_supported(const gl_matmul_args* a);
 uint64_t gl_gemv_stream_workspace(const gl_matmul_args* a);
 const char* gl_gemv_stream_kernel_name(const gl_matmul_args* a);
 int gl_gemv_stream_launch(const gl_matmul_args* a, cudaStream_t st);
+int gl_gemv_split_rows_ok(const gl_matmul_args* a);   // 17..32 rows served by two launches of the warp-independent kernel
 int gl_generic_launch(const gl_matmul_args* a, cudaStream_t st);
 int gl_validate_matmul_args(const gl_matmul_args* a);
 int gl_gemm_tc_supported(const gl_matmul_args* a);

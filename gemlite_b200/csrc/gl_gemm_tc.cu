@@ -698,8 +698,20 @@ static TcPath classify(const gl_matmul_args* a) {
 
 int gl_gemm_tc_supported(const gl_matmul_args* a) { return classify(a) != TC_NONE; }
 
+// Tile-config cache entry of this problem: family GEMM (M >= 64) / GEMM_SPLITK under the reference's signature
+// "(Mb, N, K, group_size, e, type_id)"; the fields "tile_n" (128 / 256) and "splits" (A16Wn K splits) override the
+// built-in choices below.
+static int tc_cfg_int(const gl_matmul_args* a, const char* key, int dflt) {
+  const int idt = (a->input_dtype == GL_BF16) ? GL_FP16 : a->input_dtype;
+  char sig[128];
+  snprintf(sig, sizeof(sig), "(%d, %d, %d, %d, %d, %d)", gl_get_closest_m(a->M), a->N, a->K, a->group_size, a->elements_per_sample, idt * 100 + a->W_nbits);
+  return gl_cfg_int(a->M >= 64 ? "GEMM" : "GEMM_SPLITK", sig, key, dflt);
+}
+
 static int tc_tile_n(const gl_matmul_args* a) {
-  return (a->N >= 256 && ((int64_t)((a->M + 127) / 128) * ((a->N + 255) / 256) >= 96)) ? 256 : 128;
+  const int dflt = (a->N >= 256 && ((int64_t)((a->M + 127) / 128) * ((a->N + 255) / 256) >= 96)) ? 256 : 128;
+  const int req = tc_cfg_int(a, "tile_n", 0);
+  return ((req == 128 || req == 256) && a->N >= req) ? req : dflt;
 }
 
 // K splits of the A16Wn kernel: when the tiles alone leave more than half of the SMs idle, the K range is divided
@@ -708,7 +720,10 @@ static int a16_splits(const gl_matmul_args* a) {
   const int BN = tc_tile_n(a);
   const int64_t tiles = (int64_t)((a->M + 127) / 128) * ((a->N + BN - 1) / BN);
   const int nkt = (a->K + 63) / 64, sms = gl_num_sms();
-  if (tiles * 2 > sms || tiles > 16384 || nkt < 16) return 1;
+  if (tiles > 16384 || nkt < 16) return 1;
+  const int req = tc_cfg_int(a, "splits", 0);
+  if (req >= 1 && req <= 8 && req <= nkt / 8) { int s = req; while (s > 1 && (s - 1) * ((nkt + s - 1) / s) >= nkt) --s; return s; }
+  if (tiles * 2 > sms) return 1;
   int s = (int)(sms / tiles);
   if (s > 8) s = 8;
   if (s > nkt / 8) s = nkt / 8;

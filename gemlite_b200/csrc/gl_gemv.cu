@@ -48,7 +48,18 @@ struct GemvParams {
   int out_dtype;
   int max_slice_iters, max_seg;
   int s_in, c_in;   // warp-independent kernel: K slices and 32-column groups inside a CTA
+#ifdef GL_GEMV_TRACE
+  unsigned long long* trace;   // profiling build: per-warp globaltimer stamps [cta][warp][8]
+#endif
 };
+// Profiling build (-DGL_GEMV_TRACE): every warp of the warp-independent kernel records globaltimer stamps at its phase
+// boundaries (start, constants ready, dependency resolved, activations staged, main loop done, end).
+#ifdef GL_GEMV_TRACE
+#define GL_STAMP(i) do { if (p.trace != nullptr && (threadIdx.x & 31) == 0) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); \
+  p.trace[(((size_t)blockIdx.y * gridDim.x + blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5)) * 8 + (i)] = t_; } } while (0)
+#else
+#define GL_STAMP(i) do { } while (0)
+#endif
 
 template <typename XT> struct XTraits;
 template <> struct XTraits<__nv_bfloat16> {
@@ -498,6 +509,7 @@ __global__ void __launch_bounds__(MT == 1 ? 512 : 256, MT == 1 ? 1 : 2) gl_gemv_
   float* part = reinterpret_cast<float*>(smem_raw + (size_t)s_in * xs_slice_units * 16 +
                                          (size_t)s_in * c_in * (nseg * 32 * 12 + 16));     // [slice][M][ccols]
 
+  GL_STAMP(0);
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the next layer may start its own weight loads
   // ---- before the dependency wait: first batch of weights, raw scales / zeros of this warp's groups -------
   const int n0 = blockIdx.x * ccols + wc * 32 + 4 * r;
@@ -553,7 +565,9 @@ __global__ void __launch_bounds__(MT == 1 ? 512 : 256, MT == 1 ? 1 : 2) gl_gemv_
     }
     __syncwarp();
   }
+  GL_STAMP(1);
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  GL_STAMP(2);
 
   // ---- stage this slice of x in B-fragment order (shared by the c_in warps of the slice) -------------------
   {
@@ -589,6 +603,7 @@ __global__ void __launch_bounds__(MT == 1 ? 512 : 256, MT == 1 ? 1 : 2) gl_gemv_
   }
   if (c_in > 1) asm volatile("bar.sync %0, %1;" ::"r"(1 + sl), "r"(ccols) : "memory");
   else __syncwarp();
+  GL_STAMP(3);
 
   // ---- main loop ----------------------------------------------------------------------------------------------
   const uint4* xcur[MT];
@@ -707,6 +722,7 @@ __global__ void __launch_bounds__(MT == 1 ? 512 : 256, MT == 1 ? 1 : 2) gl_gemv_
   for (int b = 0; b + 1 < nb; ++b) process(b * U, true);
   process((nb - 1) * U, false);
 
+  GL_STAMP(4);
   // ---- reduction over the CTA's slices, then over the cluster ---------------------------------------------------
   {
     float* mine = part + (size_t)sl * p.M * ccols + wc * 32 + 4 * r;
@@ -730,6 +746,7 @@ __global__ void __launch_bounds__(MT == 1 ? 512 : 256, MT == 1 ? 1 : 2) gl_gemv_
       if (p.bias != nullptr) v += gl_load_as_float(p.bias, n, p.out_dtype);
       gl_store_out(p.out, (int64_t)m * p.N + n, v, p.out_dtype);
     }
+    GL_STAMP(5);
     return;
   }
   for (int i = threadIdx.x; i < tile_elems; i += blockDim.x) {      // fold the CTA's slices into slice 0
@@ -937,9 +954,29 @@ static int launch_t(const GemvParams& p, dim3 grid, dim3 block, size_t smem, cud
   GL_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, p));
   return GL_OK;
 }
+// cudaFuncSetAttribute costs about a microsecond of host time: the limit is raised once per (kernel, device) to the
+// largest size any plan can ask for, not on every launch.  (All kernels here share one function-pointer type, so the
+// record is keyed by the pointer value.)
+static int raise_smem_limit(const void* kern) {
+  static const void* seen[64][96];
+  static int nseen[64];
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); dev = -1; }
+  if (dev >= 0) {
+    std::lock_guard<std::mutex> lk(mu);
+    for (int i = 0; i < nseen[dev]; ++i) if (seen[dev][i] == kern) return GL_OK;
+  }
+  GL_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+  if (dev >= 0) {
+    std::lock_guard<std::mutex> lk(mu);
+    if (nseen[dev] < 96) seen[dev][nseen[dev]++] = kern;
+  }
+  return GL_OK;
+}
 template <typename K>
 static int launch_kernel(K kern, const GemvParams& p, dim3 grid, dim3 block, size_t smem, cudaStream_t st) {
-  if (smem > 48 * 1024) GL_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  if (smem > 48 * 1024) { if (int rc = raise_smem_limit(reinterpret_cast<const void*>(kern))) return rc; }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
   cudaLaunchAttribute attr[2];
@@ -1020,8 +1057,33 @@ int gl_gemv_stream_supported(const gl_matmul_args* a) {
 
 uint64_t gl_matmul_counter_bytes(void) { return (uint64_t)kMaxTiles * sizeof(unsigned int) + kStatusBytes; }
 
+// 17 to 32 batch rows: two launches of the warp-independent kernel (rows 0..15, then the rest).  The packed weights of
+// one layer are a fraction of the 126 MB L2, so the second launch reads them from there; together they take about half
+// the time of the 128-row tensor-core tile (which pads the batch and dequantises through shared memory) at these sizes.
+static bool split_rows_plans(const gl_matmul_args* a, gl_matmul_args* lo, gl_matmul_args* hi, GemvPlan* pl_lo, GemvPlan* pl_hi) {
+  if (a->M <= 16 || a->M > 32) return false;
+  *lo = *a; *hi = *a;
+  lo->M = 16; hi->M = a->M - 16;
+  hi->x = reinterpret_cast<const char*>(a->x) + (size_t)16 * a->K * gl_dtype_size(a->x_dtype);
+  hi->out = reinterpret_cast<char*>(a->out) + (size_t)16 * a->N * gl_dtype_size(a->out_dtype);
+  plan_for(lo, pl_lo);
+  plan_for(hi, pl_hi);
+  return pl_lo->warp_kernel && pl_hi->warp_kernel;
+}
+
+int gl_gemv_split_rows_ok(const gl_matmul_args* a) {
+  gl_matmul_args lo, hi;
+  GemvPlan p1, p2;
+  return split_rows_plans(a, &lo, &hi, &p1, &p2) ? 1 : 0;
+}
+
 uint64_t gl_gemv_stream_workspace(const gl_matmul_args* a) {
   GemvPlan pl;
+  {
+    gl_matmul_args lo, hi;
+    GemvPlan pl_hi;
+    if (split_rows_plans(a, &lo, &hi, &pl, &pl_hi)) return gl_matmul_counter_bytes();   // both launches reduce inside CTAs / clusters
+  }
   plan_for(a, &pl);
   return gl_matmul_counter_bytes() + ((pl.splitK > 1 && pl.cluster == 1) ? (uint64_t)pl.splitK * a->M * a->N * sizeof(float) : 0);
 }
@@ -1030,6 +1092,13 @@ uint64_t gl_gemv_stream_workspace(const gl_matmul_args* a) {
 static uint64_t workspace_for_plan(const gl_matmul_args* a, const GemvPlan& pl) {
   return gl_matmul_counter_bytes() + ((pl.splitK > 1 && pl.cluster == 1) ? (uint64_t)pl.splitK * a->M * a->N * sizeof(float) : 0);
 }
+
+#ifdef GL_GEMV_TRACE
+// profiling build only: a device buffer of 64 x 8192 x 8 stamps that successive launches fill round-robin
+static unsigned long long* g_gemv_trace = nullptr;
+static unsigned int g_gemv_trace_launch = 0;
+extern "C" __attribute__((visibility("default"))) void gl_debug_gemv_trace(unsigned long long* buf) { g_gemv_trace = buf; g_gemv_trace_launch = 0; }
+#endif
 
 // launches the streaming kernel with `workspace` as its scratch (counters | status | partial sums)
 static int gemv_launch_impl(const gl_matmul_args* a, cudaStream_t st, const GemvPlan& pl, void* workspace, uint64_t workspace_bytes) {
@@ -1056,6 +1125,9 @@ static int gemv_launch_impl(const gl_matmul_args* a, cudaStream_t st, const Gemv
   p.max_slice_iters = pl.slice_iters;
   p.max_seg = pl.max_seg;
   p.s_in = pl.s_in; p.c_in = pl.c_in;
+#ifdef GL_GEMV_TRACE
+  p.trace = g_gemv_trace ? g_gemv_trace + (size_t)(g_gemv_trace_launch++ % 64) * 8192 * 8 : nullptr;   // one 8192-warp record per launch
+#endif
   dim3 grid(pl.tiles, pl.splitK), block(32 * pl.warps_n);
   if (pl.warp_kernel) {
     if (a->x_dtype == GL_BF16) return launch_warp<__nv_bfloat16>(a->W_nbits, pl.MT, pl.gi, p, grid, block, pl.smem, st);
@@ -1068,12 +1140,21 @@ static int gemv_launch_impl(const gl_matmul_args* a, cudaStream_t st, const Gemv
 
 const char* gl_gemv_stream_kernel_name(const gl_matmul_args* a) {
   GemvPlan pl;
+  if (gl_gemv_split_rows_ok(a)) return "gl_gemv_warp_kernel";
   plan_for(a, &pl);
   return pl.warp_kernel ? "gl_gemv_warp_kernel" : "gl_gemv_stream_kernel";
 }
 
 int gl_gemv_stream_launch(const gl_matmul_args* a, cudaStream_t st) {
   GemvPlan pl;
+  {
+    gl_matmul_args lo, hi;
+    GemvPlan pl_hi;
+    if (split_rows_plans(a, &lo, &hi, &pl, &pl_hi)) {
+      if (int rc = gemv_launch_impl(&lo, st, pl, a->workspace, a->workspace_bytes)) return rc;
+      return gemv_launch_impl(&hi, st, pl_hi, a->workspace, a->workspace_bytes);
+    }
+  }
   plan_for(a, &pl);
   return gemv_launch_impl(a, st, pl, a->workspace, a->workspace_bytes);
 }

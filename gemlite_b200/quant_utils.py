@@ -198,8 +198,9 @@ _NVFP4_SCRATCH = {}
 
 
 def _nvfp4_scratch(device):
-    """4 bytes per device for the tensor-wide amax (allocated once, outside any graph capture)."""
-    key = (device.type, device.index)
+    """4 bytes per (device, stream) for the tensor-wide amax (allocated on first use, outside any graph capture): two
+    layers quantising on different streams of one GPU must not share the cell."""
+    key = (device.type, device.index, torch.cuda.current_stream(device).cuda_stream)
     buf = _NVFP4_SCRATCH.get(key)
     if buf is None:
         buf = torch.zeros(1, dtype=torch.int32, device=device)

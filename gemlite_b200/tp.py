@@ -154,14 +154,17 @@ class TPLinear(torch.nn.Module):
     """A sharded layer plus its collective.  `layer` is any callable x -> y (a GemLiteLinear on a GPU).  With a
     `PeerComm`, results that fit its receive slots are reduced by the one-shot kernel, larger ones by NCCL."""
 
-    def __init__(self, layer, mode, group=None, comm=None):
+    def __init__(self, layer, mode, group=None, comm=None, world=None):
         super().__init__()
         assert mode in ("column", "row")
         self.layer, self.mode, self.group, self.comm = layer, mode, group, comm
+        # number of shards the layer was cut into (None: the size of the process group); an unsharded layer never reduces
+        self.world = world
 
     def forward(self, x):
         y = self.layer(x)
-        if self.mode == "row" and dist.is_initialized() and dist.get_world_size(self.group) > 1:
+        world = self.world if self.world is not None else (dist.get_world_size(self.group) if dist.is_initialized() else 1)
+        if self.mode == "row" and world > 1:
             if self.comm is not None and self.comm.fits(y):
                 return self.comm.all_reduce(y)
             dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
@@ -176,7 +179,7 @@ def build_a16w4_tp_linear(W, bias, mode, world, rank, device, dtype=torch.bfloat
     W_q, s, z, b = shard(W_q, s, z, bias, world, rank, group_size)
     proc = A16Wn_HQQ_INT(device=str(device), dtype=dtype, W_nbits=nbits)
     layer = proc.from_weights(W_q.to(device), s.to(device), z.to(device), bias=None if b is None else b.to(device))
-    return TPLinear(layer, mode, comm=comm)
+    return TPLinear(layer, mode, comm=comm, world=world)
 
 
 class LlamaLinears(torch.nn.Module):
@@ -204,7 +207,7 @@ class LlamaLinears(torch.nn.Module):
             zz = torch.cat([s[2].reshape(s[0].shape[0], -1) for s in shards], 0).reshape(-1, 1)
             from .helper import A16W4_HQQ_INT
             layer = A16W4_HQQ_INT(device=str(device), dtype=dtype).from_weights(W_q.to(device), sc.to(device), zz.to(device))
-            return TPLinear(layer, "column")
+            return TPLinear(layer, "column", world=world)
 
         self.qkv = col(w(n_heads * head_dim, hidden), w(n_kv_heads * head_dim, hidden), w(n_kv_heads * head_dim, hidden))
         self.o = build_a16w4_tp_linear(w(hidden, n_heads * head_dim), None, "row", world, rank, device, dtype, 4, group_size, comm)

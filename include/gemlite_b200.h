@@ -280,6 +280,14 @@ GL_API int gl_tp_status(const gl_tp_comm* c, int32_t* status, uint32_t* epoch);
  * and the down projection of a decoder MLP (two torch ops in a host that runs the reference). fp16 / bf16. */
 GL_API int gl_silu_mul(const void* gate_up, void* out, int32_t M, int32_t inter, int32_t dtype, void* stream);
 
+/* ---- measurement: tensor-pipe ceiling ------------------------------------------------------------ */
+/* Enqueues one kernel in which every SM issues iters x 4 tcgen05.mma of 128 x 256 x (32 bytes of K) on operand tiles
+ * resident in shared memory: the MMA-issue ceiling for `kind` (GL_BF16, GL_FP8, GL_INT8, GL_MXFP4, GL_NVFP4) on this
+ * GPU at its current clocks.  *flops_out receives the operations of the launch; the caller times it with events.
+ * `status_word`: 4 zeroed device bytes (set if the kernel's final wait runs out).  No counterpart in the reference
+ * (its benchmarks quote spec-sheet peaks); bench.py uses it as the FP8 / FP4 roofline denominator. */
+GL_API int gl_mma_peak(int32_t kind, int32_t iters, void* status_word, double* flops_out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -203,3 +203,46 @@ def test_decode_kernel_packed_8bit(lib, M, dtype):
     out = torch.empty((M, N), dtype=dtype, device="cuda")
     a = core._fill_args(xs, layer.bias, layer.W_q, layer.scales, layer.zeros, None, None, out, layer.get_meta_args(), -1)
     assert lib.gl_matmul_kernel_name(ctypes.byref(a)) == b"gl_gemv_warp_kernel"
+
+
+@pytest.mark.parametrize("nbits,gs", [(4, 128), (2, 64)])
+@pytest.mark.parametrize("M", [1, 3, 12])
+def test_decode_bf16_activations_wide_range(lib, nbits, gs, M):
+    """bf16 activations far outside the fp16 range in one batch row (up to ~1e6) next to ordinary rows and tiny values
+    (1e-30): the decode kernel multiplies in the activation dtype and accumulates in fp32, so every row still agrees
+    with fp64 at the usual tolerance (a kernel that went through fp16 would overflow here)."""
+    from gemlite_b200 import helper
+    N, K = 2048, 4096
+    x, W_q, s, z, b = make_a16wn(N, K, nbits, gs, torch.bfloat16, seed=31 + M, M=M)
+    x = x.float()
+    x[0] *= 3.0e5
+    x[0, ::7] = 1e-30
+    if M > 1:
+        x[1, 100:200] *= 1.0e4          # one K slice of another row
+    x = x.to(torch.bfloat16)
+    layer = helper.A16Wn_HQQ_INT(device="cuda:0", dtype=torch.bfloat16, W_nbits=nbits).from_weights(W_q.cuda(), s.cuda(), z.cuda(), bias=b.cuda())
+    from tests.test_gpu_tc import _kernel_name
+    assert _kernel_name(layer, x.cuda()) == "gl_gemv_warp_kernel"
+    y = layer(x.cuda()).float().cpu().numpy()
+    assert np.isfinite(y).all()
+    want = exact_a16wn(x, W_q, s, z, b, gs)
+    for m in range(M):                   # row by row: the rows differ by orders of magnitude
+        assert rel_fro(y[m], want[m]) < 1e-2, (m, rel_fro(y[m], want[m]))
+
+
+@pytest.mark.parametrize("nbits,gs", [(4, 128), (2, 64), (8, 128), (4, 64)])
+@pytest.mark.parametrize("M", [17, 25, 32])
+def test_decode_kernel_up_to_32_rows(lib, nbits, gs, M):
+    """17 to 32 batch rows run as two launches of the warp-independent streaming kernel (rows 0..15, then the rest)."""
+    from gemlite_b200 import helper
+    from tests.test_gpu_tc import _kernel_name
+    for N, K in ((2048, 4096), (8192, 1024)):
+        x, W_q, s, z, b = make_a16wn(N, K, nbits, gs, torch.bfloat16, seed=800 + M + nbits, M=M)
+        layer = helper.A16Wn_HQQ_INT(device="cuda:0", dtype=torch.bfloat16, W_nbits=nbits).from_weights(W_q.cuda(), s.cuda(), z.cuda(), bias=b.cuda())
+        if nbits != 8:      # (packed bytes with a short K have no warp-kernel plan for every row count: the tensor-core kernel takes them)
+            assert _kernel_name(layer, x.cuda()) == "gl_gemv_warp_kernel"
+        y = layer(x.cuda()).float().cpu().numpy()
+        want = exact_a16wn(x, W_q, s, z, b, gs)
+        assert rel_fro(y, want) < 1e-2, (N, K, rel_fro(y, want))
+        for m in (0, M - 1):
+            assert rel_fro(y[m], want[m]) < 1e-2

@@ -45,7 +45,7 @@ def test_silu_mul_matches_torch(lib):
 def test_allreduce_single_rank_is_a_copy(lib, dtype):
     from gemlite_b200 import _lib
     from gemlite_b200.dtypes import TORCH_TO_DTYPE
-    comm, ptrs = _local_comm(lib, 1, 1 << 20)
+    comm, ptrs = _local_comm(lib, 1, 4 << 20)
     st = torch.cuda.current_stream().cuda_stream
     try:
         for n in (8192, 64 * 8192, 16):
@@ -60,7 +60,7 @@ def test_allreduce_single_rank_is_a_copy(lib, dtype):
         assert lib.gl_tp_status(ctypes.byref(comm), ctypes.byref(status), ctypes.byref(epoch)) == 0
         assert status.value == 0 and epoch.value == 9
         # too large for the receive slots: an error, nothing is launched
-        big = torch.zeros((1 << 20) // 2 + 8, device="cuda", dtype=torch.float32)
+        big = torch.zeros((4 << 20) // 4 + 8, device="cuda", dtype=torch.float32)
         assert lib.gl_tp_allreduce(ctypes.byref(comm), big.data_ptr(), big.data_ptr(), big.numel(), 0, 0, st) == _lib.GL_E_WORKSPACE
     finally:
         torch.cuda.synchronize()
