@@ -408,14 +408,18 @@ template <> struct H2<__half> {
   __device__ static T from_float(float v) { return __float2half2_rn(v); }
 };
 
-template <typename XT, int NB, int BN, int STAGES>
+// AM: 128-row activation tiles per CTA (1 or 2).  The kernel is bound by the dequantisation of the weight tile (unpack,
+// HFMA2, swizzled stores: the same work whatever the batch), so with AM = 2 one dequantised tile feeds two 128-row
+// accumulators (2 x BN TMEM columns): half the dequantisation per flop and half the re-reads of the packed weights.
+template <typename XT, int NB, int BN, int STAGES, int AM = 1>
 __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_kernel(const __grid_constant__ CUtensorMap tmA,
                                                                   const __grid_constant__ CUtensorMap tmW, const TcParams p) {
   constexpr int E = 32 / NB;                           // k values per packed word
   constexpr int WROWS = 64 / E;                        // packed rows per 64-wide K tile (8 for 4-bit)
-  constexpr int A_BYTES = 128 * 128, B_BYTES = BN * 128, W_BYTES = WROWS * BN * 4;
+  constexpr int A_TILE = 128 * 128;
+  constexpr int A_BYTES = AM * A_TILE, B_BYTES = BN * 128, W_BYTES = WROWS * BN * 4;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES + ((W_BYTES + 1023) / 1024) * 1024;
-  constexpr uint32_t TMEM_COLS = next_pow2_cols(BN);
+  constexpr uint32_t TMEM_COLS = next_pow2_cols(AM * BN);
   constexpr int HALF = 16 / NB;                        // field a shares a 32-bit extraction with field a + HALF
   constexpr uint32_t FMASK = ((1u << NB) - 1u) * 0x00010001u;
   using h2 = typename H2<XT>::T;
@@ -433,8 +437,8 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
   __shared__ int s_abort;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_m = (p.M + 127) / 128;
-  const int m0 = (blockIdx.x % tiles_m) * 128, n0 = (blockIdx.x / tiles_m) * BN;
+  const int tiles_m = (p.M + 128 * AM - 1) / (128 * AM);
+  const int m0 = (blockIdx.x % tiles_m) * (128 * AM), n0 = (blockIdx.x / tiles_m) * BN;
   // K tiles of this CTA: blockIdx.y picks one of p.splits equal ranges (the last one may be shorter)
   const int kt_per = (p.nkt + p.splits - 1) / p.splits;
   const int kt0 = blockIdx.y * kt_per;
@@ -465,7 +469,8 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
         mbar_expect_tx(wfull + s, W_BYTES);
         tma_load_2d(st + A_BYTES + B_BYTES, &tmW, wfull + s, n0, kt * WROWS);
         mbar_expect_tx(full + s, A_BYTES);
-        tma_load_2d(st, &tmA, full + s, kt * 64, m0);
+#pragma unroll
+        for (int am = 0; am < AM; ++am) tma_load_2d(st + am * A_TILE, &tmA, full + s, kt * 64, m0 + am * 128);   // rows past M read as zeros
       }
     }
   } else if (warp == 1) {
@@ -477,9 +482,13 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
         if (!mbar_wait(full + s, ph, &s_abort, p.status, 3) || !mbar_wait(bready + s, ph, &s_abort, p.status, 5)) { ok = false; break; }
         tc_fence_after();
         const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
-        const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sa + A_BYTES);
+        const uint64_t db = smem_desc_sw128(sa + A_BYTES);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) mma_ss<KIND_F16>(tmem_base, da + 2 * j, db + 2 * j, p.idesc, (i > 0 || j > 0) ? 1u : 0u);
+        for (int am = 0; am < AM; ++am) {
+          const uint64_t da = smem_desc_sw128(sa + am * A_TILE);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) mma_ss<KIND_F16>(tmem_base + am * BN, da + 2 * j, db + 2 * j, p.idesc, (i > 0 || j > 0) ? 1u : 0u);
+        }
         tc_commit(empty + s);
       }
       if (ok) tc_commit(tmem_full);
@@ -488,9 +497,11 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
     if (mbar_wait(tmem_full, 0u, &s_abort, p.status, 4)) {
       tc_fence_after();
       if (p.splits == 1) {
-        epilogue_tile<false>(p, tmem_base, m0, n0, BN, warp, lane, sw_s, b_s);
+#pragma unroll
+        for (int am = 0; am < AM; ++am) epilogue_tile<false>(p, tmem_base + am * BN, m0 + am * 128, n0, BN, warp, lane, sw_s, b_s);
       } else {
-        epilogue_store_partial(p, tmem_base, m0, n0, BN, warp, lane, blockIdx.y);
+#pragma unroll
+        for (int am = 0; am < AM; ++am) epilogue_store_partial(p, tmem_base + am * BN, m0 + am * 128, n0, BN, warp, lane, blockIdx.y);
         __threadfence();
         asm volatile("bar.sync 1, %0;" ::"n"(kNumEpiWarps * 32) : "memory");        // the four epilogue warps
         if (warp == 2 && lane == 0) {
@@ -501,7 +512,8 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
         asm volatile("bar.sync 1, %0;" ::"n"(kNumEpiWarps * 32) : "memory");
         if (s_last) {
           __threadfence();
-          epilogue_reduce_partials(p, m0, n0, BN, warp, lane, sw_s, b_s);
+#pragma unroll
+          for (int am = 0; am < AM; ++am) epilogue_reduce_partials(p, m0 + am * 128, n0, BN, warp, lane, sw_s, b_s);
         }
       }
     }
@@ -638,14 +650,14 @@ static int launch_tma_kernel(const CUtensorMap& tmA, const CUtensorMap& tmB, con
   return GL_OK;
 }
 
-template <typename XT, int NB, int BN, int STAGES>
+template <typename XT, int NB, int BN, int STAGES, int AM = 1>
 static int launch_a16_kernel(const CUtensorMap& tmA, const CUtensorMap& tmW, const TcParams& p, cudaStream_t st) {
   constexpr int WROWS = 64 / (32 / NB);
-  constexpr size_t stage = 128 * 128 + BN * 128 + ((WROWS * BN * 4 + 1023) / 1024) * 1024;
+  constexpr size_t stage = AM * 128 * 128 + BN * 128 + ((WROWS * BN * 4 + 1023) / 1024) * 1024;
   const size_t smem = 1024 + STAGES * stage + (4 * STAGES + 1) * 8 + 32 + 2 * BN * 4 + 16;
-  auto kern = gl_gemm_tc_a16wn_kernel<XT, NB, BN, STAGES>;
+  auto kern = gl_gemm_tc_a16wn_kernel<XT, NB, BN, STAGES, AM>;
   if (int rc = set_smem(kern, smem)) return rc;
-  const int tiles = ((p.M + 127) / 128) * ((p.N + BN - 1) / BN);
+  const int tiles = ((p.M + 128 * AM - 1) / (128 * AM)) * ((p.N + BN - 1) / BN);
   kern<<<dim3(tiles, p.splits), (6 + deq_warps(BN)) * 32, smem, st>>>(tmA, tmW, p);
   GL_LAUNCH_CHECK("gl_gemm_tc_a16wn_kernel");
   return GL_OK;
@@ -771,6 +783,18 @@ int gl_gemm_tc_launch(const gl_matmul_args* a, cudaStream_t st) {
     if (int rc = gl_make_tmap_2d(&tmB, a->w, 3, (uint64_t)a->N, (uint64_t)(a->K / a->elements_per_sample), (uint64_t)a->N * 4, (uint32_t)BN, (uint32_t)wrows, false)) return rc;
 #define GL_A16(XT, NB)                                                                              \
     (BN == 256 ? launch_a16_kernel<XT, NB, 256, 3>(tmA, tmB, p, st) : launch_a16_kernel<XT, NB, 128, 4>(tmA, tmB, p, st))
+    // two activation tiles per CTA when that still leaves at least 96 CTAs (4-bit and narrower words: three stages of
+    // 72 KB still fit); "am": 1 in a cache entry keeps one
+    if (BN == 256 && a->W_nbits <= 4 && p.splits == 1 && (int64_t)((a->M + 255) / 256) * ((a->N + 255) / 256) >= 96 && tc_cfg_int(a, "am", 2) == 2) {
+      if (a->x_dtype == GL_BF16) {
+        if (a->W_nbits == 4) return launch_a16_kernel<__nv_bfloat16, 4, 256, 3, 2>(tmA, tmB, p, st);
+        if (a->W_nbits == 2) return launch_a16_kernel<__nv_bfloat16, 2, 256, 3, 2>(tmA, tmB, p, st);
+        return launch_a16_kernel<__nv_bfloat16, 1, 256, 3, 2>(tmA, tmB, p, st);
+      }
+      if (a->W_nbits == 4) return launch_a16_kernel<__half, 4, 256, 3, 2>(tmA, tmB, p, st);
+      if (a->W_nbits == 2) return launch_a16_kernel<__half, 2, 256, 3, 2>(tmA, tmB, p, st);
+      return launch_a16_kernel<__half, 1, 256, 3, 2>(tmA, tmB, p, st);
+    }
     if (a->x_dtype == GL_BF16) {
       if (a->W_nbits == 8) return GL_A16(__nv_bfloat16, 8);
       if (a->W_nbits == 4) return GL_A16(__nv_bfloat16, 4);

@@ -518,6 +518,15 @@ __global__ void __launch_bounds__(MT == 1 ? 512 : 256, MT == 1 ? 1 : 2) gl_gemv_
   int4 buf[U];
 #pragma unroll
   for (int u = 0; u < U; ++u) buf[u] = ldg_stream(wp + (size_t)u * wstep);
+  // Epilogue constants of the column this thread finishes after the last barrier (thread i finishes elements i,
+  // i + blockDim.x, ... of the [M][ccols] tile, and blockDim.x is a multiple of ccols): requested now, so that their
+  // DRAM latency is not paid by the last CTA at the very end of the kernel
+  float epi_bias = 0.f, epi_scale = 1.f;
+  {
+    const int n = blockIdx.x * ccols + (int)(threadIdx.x % ccols);
+    if (p.bias != nullptr) epi_bias = gl_load_as_float(p.bias, n, p.out_dtype);
+    if (p.channel_scale_mode == 1) epi_scale = XTr::to_float(reinterpret_cast<const uint16_t*>(p.scales)[n]);
+  }
   {
     const bool need_s = p.W_group_mode >= 2;
     const bool need_z = (p.W_group_mode == 1 || p.W_group_mode >= 3) && !p.zero_is_scalar;
@@ -742,9 +751,7 @@ __global__ void __launch_bounds__(MT == 1 ? 512 : 256, MT == 1 ? 1 : 2) gl_gemv_
       float v = part[i];
       for (int q = 1; q < s_in; ++q) v += part[q * tile_elems + i];
       const int m = i / ccols, n = blockIdx.x * ccols + (i - m * ccols);
-      if (p.channel_scale_mode == 1) v *= XTr::to_float(reinterpret_cast<const uint16_t*>(p.scales)[n]);
-      if (p.bias != nullptr) v += gl_load_as_float(p.bias, n, p.out_dtype);
-      gl_store_out(p.out, (int64_t)m * p.N + n, v, p.out_dtype);
+      gl_store_out(p.out, (int64_t)m * p.N + n, v * epi_scale + epi_bias, p.out_dtype);
     }
     GL_STAMP(5);
     return;
