@@ -728,26 +728,39 @@ static int tc_tile_n(const gl_matmul_args* a) {
 
 // K splits of the A16Wn kernel: when the tiles alone leave more than half of the SMs idle, the K range is divided
 // so that about one CTA per SM runs; every split gets at least 8 K tiles and none is empty
-static int a16_splits(const gl_matmul_args* a) {
-  const int BN = tc_tile_n(a);
-  const int64_t tiles = (int64_t)((a->M + 127) / 128) * ((a->N + BN - 1) / BN);
+// Shape of an A16Wn launch: columns per tile (BN), 128-row activation tiles per CTA (AM) and K splits.
+// More than 128 rows and words of at most 4 bits share one dequantised weight tile between two accumulators (AM = 2);
+// 256-column tiles when that still gives 96 CTAs; when the tiles alone leave more than half of the SMs idle, the K range
+// is divided so that about one CTA per SM runs (every split gets at least 8 K tiles and none is empty).
+// Cache entry fields "tile_n", "am", "splits" override the three choices.
+struct A16Plan { int BN, AM, splits; };
+static A16Plan a16_plan(const gl_matmul_args* a) {
+  A16Plan pl;
+  pl.AM = (a->M > 128 && a->W_nbits <= 4 && tc_cfg_int(a, "am", 2) == 2) ? 2 : 1;
+  const int64_t tiles_m = (a->M + 128 * pl.AM - 1) / (128 * pl.AM);
+  const int req_bn = tc_cfg_int(a, "tile_n", 0);
+  pl.BN = (a->N >= 256 && tiles_m * ((a->N + 255) / 256) >= 96) ? 256 : 128;
+  if ((req_bn == 128 || req_bn == 256) && a->N >= req_bn) pl.BN = req_bn;
+  const int64_t tiles = tiles_m * ((a->N + pl.BN - 1) / pl.BN);
   const int nkt = (a->K + 63) / 64, sms = gl_num_sms();
-  if (tiles > 16384 || nkt < 16) return 1;
+  pl.splits = 1;
+  if (tiles > 16384 || nkt < 16) return pl;
+  auto trim = [&](int s) { while (s > 1 && (s - 1) * ((nkt + s - 1) / s) >= nkt) --s; return s; };
   const int req = tc_cfg_int(a, "splits", 0);
-  if (req >= 1 && req <= 8 && req <= nkt / 8) { int s = req; while (s > 1 && (s - 1) * ((nkt + s - 1) / s) >= nkt) --s; return s; }
-  if (tiles * 2 > sms) return 1;
+  if (req >= 1 && req <= 8 && req <= nkt / 8) { pl.splits = trim(req); return pl; }
+  if (tiles * 2 > sms) return pl;
   int s = (int)(sms / tiles);
   if (s > 8) s = 8;
   if (s > nkt / 8) s = nkt / 8;
   if (s < 1) s = 1;
-  while (s > 1 && (s - 1) * ((nkt + s - 1) / s) >= nkt) --s;
-  return s;
+  pl.splits = trim(s);
+  return pl;
 }
 
 uint64_t gl_gemm_tc_workspace(const gl_matmul_args* a) {
   uint64_t need = gl_matmul_counter_bytes();
   if (classify(a) == TC_A16WN) {
-    const int s = a16_splits(a);
+    const int s = a16_plan(a).splits;
     if (s > 1) need += (uint64_t)s * a->M * a->N * sizeof(float);
   }
   return need;
@@ -766,13 +779,14 @@ int gl_gemm_tc_launch(const gl_matmul_args* a, cudaStream_t st) {
   p.out = a->out; p.out_dtype = a->out_dtype; p.bias = a->bias;
   p.status = reinterpret_cast<int*>(reinterpret_cast<char*>(a->workspace) + gl_matmul_counter_bytes() - 256);
   p.meta_scale = nullptr;
-  const int BN = tc_tile_n(a);
+  const A16Plan a16 = path == TC_A16WN ? a16_plan(a) : A16Plan{0, 1, 1};
+  const int BN = path == TC_A16WN ? a16.BN : tc_tile_n(a);
   // decode sizes of the TMA formats swap the operands (16 or 32 token columns)
   const int swap_bn = (path != TC_A16WN && a->M <= 32 && a->N >= 128) ? (a->M <= 16 ? 16 : 32) : 0;
   CUtensorMap tmA, tmB;
   if (path == TC_A16WN) {
     p.nkt = (a->K + 63) / 64;
-    p.splits = a16_splits(a);
+    p.splits = a16.splits;
     p.counters = reinterpret_cast<unsigned int*>(a->workspace);
     p.partials = reinterpret_cast<float*>(reinterpret_cast<char*>(a->workspace) + gl_matmul_counter_bytes());
     p.idesc = gl_idesc(1, a->x_dtype == GL_BF16 ? 1 : 0, a->x_dtype == GL_BF16 ? 1 : 0, 128, BN);
@@ -783,17 +797,17 @@ int gl_gemm_tc_launch(const gl_matmul_args* a, cudaStream_t st) {
     if (int rc = gl_make_tmap_2d(&tmB, a->w, 3, (uint64_t)a->N, (uint64_t)(a->K / a->elements_per_sample), (uint64_t)a->N * 4, (uint32_t)BN, (uint32_t)wrows, false)) return rc;
 #define GL_A16(XT, NB)                                                                              \
     (BN == 256 ? launch_a16_kernel<XT, NB, 256, 3>(tmA, tmB, p, st) : launch_a16_kernel<XT, NB, 128, 4>(tmA, tmB, p, st))
-    // two activation tiles per CTA when that still leaves at least 96 CTAs (4-bit and narrower words: three stages of
-    // 72 KB still fit); "am": 1 in a cache entry keeps one
-    if (BN == 256 && a->W_nbits <= 4 && p.splits == 1 && (int64_t)((a->M + 255) / 256) * ((a->N + 255) / 256) >= 96 && tc_cfg_int(a, "am", 2) == 2) {
+    if (a16.AM == 2) {      // (words of at most 4 bits: three 72 KB stages at BN = 256, four 52 KB stages at BN = 128)
+#define GL_A16_2(XT, NB) (BN == 256 ? launch_a16_kernel<XT, NB, 256, 3, 2>(tmA, tmB, p, st) : launch_a16_kernel<XT, NB, 128, 4, 2>(tmA, tmB, p, st))
       if (a->x_dtype == GL_BF16) {
-        if (a->W_nbits == 4) return launch_a16_kernel<__nv_bfloat16, 4, 256, 3, 2>(tmA, tmB, p, st);
-        if (a->W_nbits == 2) return launch_a16_kernel<__nv_bfloat16, 2, 256, 3, 2>(tmA, tmB, p, st);
-        return launch_a16_kernel<__nv_bfloat16, 1, 256, 3, 2>(tmA, tmB, p, st);
+        if (a->W_nbits == 4) return GL_A16_2(__nv_bfloat16, 4);
+        if (a->W_nbits == 2) return GL_A16_2(__nv_bfloat16, 2);
+        return GL_A16_2(__nv_bfloat16, 1);
       }
-      if (a->W_nbits == 4) return launch_a16_kernel<__half, 4, 256, 3, 2>(tmA, tmB, p, st);
-      if (a->W_nbits == 2) return launch_a16_kernel<__half, 2, 256, 3, 2>(tmA, tmB, p, st);
-      return launch_a16_kernel<__half, 1, 256, 3, 2>(tmA, tmB, p, st);
+      if (a->W_nbits == 4) return GL_A16_2(__half, 4);
+      if (a->W_nbits == 2) return GL_A16_2(__half, 2);
+      return GL_A16_2(__half, 1);
+#undef GL_A16_2
     }
     if (a->x_dtype == GL_BF16) {
       if (a->W_nbits == 8) return GL_A16(__nv_bfloat16, 8);
