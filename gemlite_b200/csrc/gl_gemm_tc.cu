@@ -44,7 +44,7 @@ struct TcParams {
   int* status;
   int swap;                                     // operands swapped: kernel rows = output channels, columns = tokens
   // split-K (A16Wn, few tiles): fp32 partial tiles [splits][M][N] and one arrival counter per tile in the workspace
-  int splits; float* partials; unsigned int* counters;
+  int splits;
   // block-scaled formats: scale-factor atoms [rows/128][kblocks][512 B]
   const uint8_t* sfa; const uint8_t* sfb; int sf_kblocks;
   // A16Wn
@@ -157,52 +157,48 @@ __device__ __forceinline__ void epilogue_tile_swapped(const TcParams& p, uint32_
   }
 }
 
-// split-K: this CTA's fp32 partial tile goes to the workspace [split][M][N] ...
-__device__ __forceinline__ void epilogue_store_partial(const TcParams& p, uint32_t tmem_d, int m0, int n0, int BN, int epi_warp, int lane, int split) {
-  const int quad = epi_warp & 3;
-  const int m = m0 + quad * 32 + lane;
-  float* part = p.partials + ((size_t)split * p.M + m) * p.N;
-  for (int c0 = 0; c0 < BN; c0 += 32) {
-    if (n0 + c0 >= p.N) break;
+// split-K of the A16Wn kernel: the CTAs that share an output tile (one per K range) form a thread-block cluster.  Each
+// leaves its fp32 partial tile in its own shared memory (the operand ring is free by then) as 4 KB blocks of
+// 32 rows x 32 columns, [float4 index][row] so that a warp moves 512 contiguous bytes per instruction ...
+__device__ __forceinline__ void epilogue_dump_partial(uint32_t tmem_d, unsigned char* dump, int block0, int BN, int epi_warp, int lane) {
+  const int quad = epi_warp & 3;                       // TMEM lane quadrant this warp may read
+  for (int c = 0; c < BN / 32; ++c) {
     uint32_t rr[32];
-    tmem_ld_32x32(tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, rr);
-    if (m >= p.M) continue;
-    const int nb = n0 + c0;
-    if (nb + 32 <= p.N && p.N % 4 == 0) {
+    tmem_ld_32x32(tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32), rr);
+    float4* dst = reinterpret_cast<float4*>(dump + (size_t)(block0 + c * 4 + quad) * 4096) + lane;
 #pragma unroll
-      for (int q = 0; q < 8; ++q)
-        __stcg(reinterpret_cast<float4*>(part + nb) + q, make_float4(__uint_as_float(rr[4 * q]), __uint_as_float(rr[4 * q + 1]), __uint_as_float(rr[4 * q + 2]), __uint_as_float(rr[4 * q + 3])));
-    } else {
-      for (int i = 0; i < 32 && nb + i < p.N; ++i) __stcg(part + nb + i, __uint_as_float(rr[i]));
-    }
+    for (int q = 0; q < 8; ++q)
+      dst[q * 32] = make_float4(__uint_as_float(rr[4 * q]), __uint_as_float(rr[4 * q + 1]), __uint_as_float(rr[4 * q + 2]), __uint_as_float(rr[4 * q + 3]));
   }
 }
-// ... and the CTA that arrives last at the tile's counter adds the partial tiles in split order and finishes the rows
-__device__ __forceinline__ void epilogue_reduce_partials(const TcParams& p, int m0, int n0, int BN, int epi_warp, int lane,
-                                                         const float* sw_s, const float* b_s) {
-  const int quad = epi_warp & 3;
-  const int m = m0 + quad * 32 + lane;
-  if (m >= p.M) return;
-  for (int c0 = 0; c0 < BN; c0 += 32) {
-    const int nb = n0 + c0;
-    if (nb >= p.N) break;
+// ... and after a cluster barrier CTA r sums, in split order, every block b with b % splits == r out of all the CTAs'
+// shared memories and finishes those rows.  Every warp of the CTA takes part.
+__device__ __forceinline__ void cluster_reduce_partials(const TcParams& p, const unsigned char* dump, int m0, int n0, int BN, int AM, int warp,
+                                                        int n_warps, int lane, const float* sw_s, const float* b_s) {
+  const int CB = BN / 32, blocks = AM * CB * 4, S = p.splits, r = blockIdx.y;
+  for (int b = r + S * warp; b < blocks; b += S * n_warps) {
+    const int am = b / (CB * 4), c = (b >> 2) % CB, quad = b & 3;
+    const int mrow = m0 + am * 128 + quad * 32, nb = n0 + c * 32;
+    if (mrow >= p.M || nb >= p.N) continue;            // warp-uniform
     float v[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = 0.f;
-    for (int sidx = 0; sidx < p.splits; ++sidx) {
-      const float* part = p.partials + ((size_t)sidx * p.M + m) * p.N + nb;
-      if (nb + 32 <= p.N && p.N % 4 == 0) {
+    const uint32_t local = smem_u32(dump + (size_t)b * 4096) + (uint32_t)lane * 16u;
+    for (int sidx = 0; sidx < S; ++sidx) {
+      uint32_t ra;
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(local), "r"(sidx));
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          const float4 t = __ldcg(reinterpret_cast<const float4*>(part) + q);
-          v[4 * q] += t.x; v[4 * q + 1] += t.y; v[4 * q + 2] += t.z; v[4 * q + 3] += t.w;
-        }
-      } else {
-        for (int i = 0; i < 32 && nb + i < p.N; ++i) v[i] += __ldcg(part + i);
+      for (int q = 0; q < 8; ++q) {
+        float4 t;
+        asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(t.x), "=f"(t.y), "=f"(t.z), "=f"(t.w) : "r"(ra + (uint32_t)q * 512u) : "memory");
+        v[4 * q] += t.x; v[4 * q + 1] += t.y; v[4 * q + 2] += t.z; v[4 * q + 3] += t.w;
       }
     }
-    finish_row_chunk(p, m, nb, v, 1.f, sw_s + c0, b_s + c0);
+    if (mrow + lane < p.M) finish_row_chunk(p, mrow + lane, nb, v, 1.f, sw_s + c * 32, b_s + c * 32);
   }
+}
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
 // ---- both operands by TMA: fp8 / int8 / mxfp4 / nvfp4 ---------------------------------------------
@@ -411,14 +407,47 @@ template <> struct H2<__half> {
 // AM: 128-row activation tiles per CTA (1 or 2).  The kernel is bound by the dequantisation of the weight tile (unpack,
 // HFMA2, swizzled stores: the same work whatever the batch), so with AM = 2 one dequantised tile feeds two 128-row
 // accumulators (2 x BN TMEM columns): half the dequantisation per flop and half the re-reads of the packed weights.
-template <typename XT, int NB, int BN, int STAGES, int AM = 1>
+// bytes of a slot of the A16Wn kernel's packed-word ring: the packed words of a 64-deep K tile, a row of scales and a row of zeros
+constexpr int a16_wslot_bytes(int NB, int BN) { return ((64 / (32 / NB) * BN * 4 + 2 * BN * 2 + 255) / 256) * 256; }
+
+// Profiling build (-DGL_TC_TRACE): the A16Wn kernel writes 16 counters per CTA (globaltimer stamps of its phases and
+// clock64 sums of what its MMA, producer and first dequant warp waited for) to a buffer set with gl_debug_tc_trace.
+#ifdef GL_TC_TRACE
+__device__ unsigned long long* g_tc_trace = nullptr;
+extern "C" __attribute__((visibility("default"))) void gl_debug_tc_trace(void* buf) {
+  unsigned long long* b = reinterpret_cast<unsigned long long*>(buf);
+  cudaMemcpyToSymbol(g_tc_trace, &b, sizeof(b));
+}
+#define TC_GT(i) do { if (g_tc_trace) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); \
+    g_tc_trace[(size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 16 + (i)] = t_; } } while (0)
+#define TC_CK(v) const long long v = clock64()
+#define TC_ACC(acc, a, b) acc += (b) - (a)
+#define TC_PUT(i, acc) do { if (g_tc_trace) g_tc_trace[(size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 16 + (i)] = (unsigned long long)(acc); } while (0)
+#else
+#define TC_GT(i) do { } while (0)
+#define TC_CK(v) do { } while (0)
+#define TC_ACC(acc, a, b) do { } while (0)
+#define TC_PUT(i, acc) do { } while (0)
+#endif
+
+// WS: slots of the packed-word ring.  The packed weights come from DRAM (every other operand of a stage is L2- or
+// SM-local), and a K tile of them is only a few KB, so they get a ring of their own that runs WS tiles ahead of the
+// STAGES-deep activation / dequantised-tile ring: with both in one ring the DRAM latency was paid once per STAGES tiles.
+// A slot of that ring also carries the tile's row of group scales and of group zeros (BN values each): a dequant warp
+// that fetched them from global memory had the load's latency in its chain at every change of group, because the
+// mbarrier arrive that publishes its tile orders all of the thread's earlier memory operations.
+template <typename XT, int NB, int BN, int STAGES, int AM = 1, int WS = STAGES>
 __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_kernel(const __grid_constant__ CUtensorMap tmA,
-                                                                  const __grid_constant__ CUtensorMap tmW, const TcParams p) {
+                                                                  const __grid_constant__ CUtensorMap tmW,
+                                                                  const __grid_constant__ CUtensorMap tmS,
+                                                                  const __grid_constant__ CUtensorMap tmZ, const TcParams p) {
   constexpr int E = 32 / NB;                           // k values per packed word
   constexpr int WROWS = 64 / E;                        // packed rows per 64-wide K tile (8 for 4-bit)
   constexpr int A_TILE = 128 * 128;
   constexpr int A_BYTES = AM * A_TILE, B_BYTES = BN * 128, W_BYTES = WROWS * BN * 4;
-  constexpr int STAGE_BYTES = A_BYTES + B_BYTES + ((W_BYTES + 1023) / 1024) * 1024;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int META_BYTES = BN * 2;                   // one row of scales or zeros
+  constexpr int WSLOT_BYTES = a16_wslot_bytes(NB, BN);
   constexpr uint32_t TMEM_COLS = next_pow2_cols(AM * BN);
   constexpr int HALF = 16 / NB;                        // field a shares a 32-bit extraction with field a + HALF
   constexpr uint32_t FMASK = ((1u << NB) - 1u) * 0x00010001u;
@@ -426,11 +455,13 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
 
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);   // A landed
-  uint64_t* wfull = full + STAGES;                                              // packed W landed
-  uint64_t* bready = wfull + STAGES;                                            // B tile written by the dequant warps
+  unsigned char* wring = smem + STAGES * STAGE_BYTES;                           // [WS] packed-word tiles
+  uint64_t* full = reinterpret_cast<uint64_t*>(wring + WS * WSLOT_BYTES);       // A landed
+  uint64_t* bready = full + STAGES;                                             // B tile written by the dequant warps
   uint64_t* empty = bready + STAGES;                                            // MMAs of the stage retired
-  uint64_t* tmem_full = empty + STAGES;
+  uint64_t* wfull = empty + STAGES;                                             // [WS] packed W landed
+  uint64_t* wempty = wfull + WS;                                                // [WS] packed W read by every dequant warp
+  uint64_t* tmem_full = wempty + WS;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
   float* sw_s = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(tmem_slot + 1) + 15) & ~(uintptr_t)15);
   float* b_s = sw_s + BN;
@@ -443,35 +474,45 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
   const int kt_per = (p.nkt + p.splits - 1) / p.splits;
   const int kt0 = blockIdx.y * kt_per;
   const int nloc = min(kt_per, p.nkt - kt0);
-  __shared__ int s_last;
+  if (threadIdx.x == 0) TC_GT(0);
   stage_epilogue_consts(p, sw_s, b_s, n0, BN);
 
   if (threadIdx.x == 0) {
     s_abort = 0;
-    for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(wfull + s, 1); mbar_init(bready + s, deq_warps(BN)); mbar_init(empty + s, 1); }
+    // a K tile is dequantised by BN / 32 warps (one per 32 columns)
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(bready + s, BN / 32); mbar_init(empty + s, 1); }
+    for (int s = 0; s < WS; ++s) { mbar_init(wfull + s, 1); mbar_init(wempty + s, BN / 32); }
     mbar_init(tmem_full, 1);
     fence_barrier_init();
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmW);
+    prefetch_tmap(&tmS);
+    prefetch_tmap(&tmZ);
   }
   if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const bool need_s = p.W_group_mode >= 2, need_z = (p.W_group_mode == 1 || p.W_group_mode >= 3) && !p.zero_is_scalar;
+  if (threadIdx.x == 0) TC_GT(1);
+#ifdef GL_TC_TRACE
+  long long acc0 = 0, acc1 = 0, acc2 = 0, acc3 = 0;
+#endif
 
   if (warp == 0) {
     if (lane == 0) {
       for (int i = 0; i < nloc; ++i) {
         const int s = i % STAGES, kt = kt0 + i;
+        TC_CK(c0);
         if (!mbar_wait(empty + s, (uint32_t)(((i / STAGES) & 1) ^ 1), &s_abort, p.status, 2)) break;
+        TC_CK(c1); TC_ACC(acc0, c0, c1);
         unsigned char* st = smem + s * STAGE_BYTES;
-        mbar_expect_tx(wfull + s, W_BYTES);
-        tma_load_2d(st + A_BYTES + B_BYTES, &tmW, wfull + s, n0, kt * WROWS);
         mbar_expect_tx(full + s, A_BYTES);
 #pragma unroll
         for (int am = 0; am < AM; ++am) tma_load_2d(st + am * A_TILE, &tmA, full + s, kt * 64, m0 + am * 128);   // rows past M read as zeros
       }
+      TC_PUT(12, acc0);
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -479,7 +520,11 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
       for (int i = 0; i < nloc && ok; ++i) {
         const int s = i % STAGES;
         const uint32_t ph = (uint32_t)((i / STAGES) & 1);
-        if (!mbar_wait(full + s, ph, &s_abort, p.status, 3) || !mbar_wait(bready + s, ph, &s_abort, p.status, 5)) { ok = false; break; }
+        TC_CK(c0);
+        if (!mbar_wait(full + s, ph, &s_abort, p.status, 3)) { ok = false; break; }
+        TC_CK(c1); TC_ACC(acc0, c0, c1);
+        if (!mbar_wait(bready + s, ph, &s_abort, p.status, 5)) { ok = false; break; }
+        TC_CK(c2); TC_ACC(acc1, c1, c2);
         tc_fence_after();
         const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
         const uint64_t db = smem_desc_sw128(sa + A_BYTES);
@@ -490,85 +535,83 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
           for (int j = 0; j < 4; ++j) mma_ss<KIND_F16>(tmem_base + am * BN, da + 2 * j, db + 2 * j, p.idesc, (i > 0 || j > 0) ? 1u : 0u);
         }
         tc_commit(empty + s);
+        TC_CK(c3); TC_ACC(acc2, c2, c3);
       }
       if (ok) tc_commit(tmem_full);
+      TC_GT(2); TC_PUT(5, acc0); TC_PUT(6, acc1); TC_PUT(7, acc2);
     }
   } else if (warp < 2 + kNumEpiWarps) {
+    if (warp == 2) {
+      // the first epilogue warp has nothing to do until the accumulator is complete: its lane 0 feeds the packed-word ring
+      if (lane == 0) {
+        for (int i = 0; i < nloc; ++i) {
+          const int ws = i % WS;
+          if (!mbar_wait(wempty + ws, (uint32_t)(((i / WS) & 1) ^ 1), &s_abort, p.status, 7)) break;
+          unsigned char* slot = wring + ws * WSLOT_BYTES;
+          const int g = ((kt0 + i) * 64) / p.group_size;
+          mbar_expect_tx(wfull + ws, W_BYTES + (need_s ? META_BYTES : 0) + (need_z ? META_BYTES : 0));
+          tma_load_2d(slot, &tmW, wfull + ws, n0, (kt0 + i) * WROWS);
+          if (need_s) tma_load_2d(slot + W_BYTES, &tmS, wfull + ws, n0, g);                  // columns past N read as zeros
+          if (need_z) tma_load_2d(slot + W_BYTES + META_BYTES, &tmZ, wfull + ws, n0, g);
+        }
+      }
+      __syncwarp();
+    }
     if (mbar_wait(tmem_full, 0u, &s_abort, p.status, 4)) {
       tc_fence_after();
+      if (warp == 2 && lane == 0) TC_GT(3);
       if (p.splits == 1) {
 #pragma unroll
         for (int am = 0; am < AM; ++am) epilogue_tile<false>(p, tmem_base + am * BN, m0 + am * 128, n0, BN, warp, lane, sw_s, b_s);
       } else {
+        // every operand of the ring has been consumed (the accumulator is complete): the ring holds the partial tile now
 #pragma unroll
-        for (int am = 0; am < AM; ++am) epilogue_store_partial(p, tmem_base + am * BN, m0 + am * 128, n0, BN, warp, lane, blockIdx.y);
-        __threadfence();
-        asm volatile("bar.sync 1, %0;" ::"n"(kNumEpiWarps * 32) : "memory");        // the four epilogue warps
-        if (warp == 2 && lane == 0) {
-          const unsigned int prev = atomicAdd(p.counters + blockIdx.x, 1u);
-          s_last = (prev == (unsigned int)(p.splits - 1)) ? 1 : 0;
-          if (s_last) p.counters[blockIdx.x] = 0u;                                 // ready for the next launch
-        }
-        asm volatile("bar.sync 1, %0;" ::"n"(kNumEpiWarps * 32) : "memory");
-        if (s_last) {
-          __threadfence();
-#pragma unroll
-          for (int am = 0; am < AM; ++am) epilogue_reduce_partials(p, m0 + am * 128, n0, BN, warp, lane, sw_s, b_s);
-        }
+        for (int am = 0; am < AM; ++am) epilogue_dump_partial(tmem_base + am * BN, smem, am * (BN / 32) * 4, BN, warp, lane);
       }
     }
   } else {
-    // dequant warps: warp dw owns 32 columns (BN = 256) or 32 columns x half of the packed rows (BN = 128)
+    // dequant warps: warp dw owns 32 columns of a K tile
     const int dw = warp - 2 - kNumEpiWarps;
     constexpr int CBLOCKS = BN / 32;                       // 32-column blocks in the tile
-    constexpr int RSPLIT = deq_warps(BN) / CBLOCKS;        // warps sharing one column block (1 or 2)
-    constexpr int RPW = WROWS / RSPLIT;                    // packed rows per warp
+    // With more warps than column blocks (BN = 128) the warps form groups that take the K tiles in turn: the chain of a
+    // tile (wait, read, unpack, store, fence, arrive) is mostly latency, and two tiles in flight hide it.
+    constexpr int TSPLIT = deq_warps(BN) / CBLOCKS;        // warp groups (1 or 2)
+    constexpr int RPW = WROWS;                             // packed rows per warp: the whole K tile of its 32 columns
     const int nl = (dw % CBLOCKS) * 32 + lane;             // column inside the tile
-    const int c_begin = (dw / CBLOCKS) * RPW;
-    const int n = n0 + nl;
-    const bool n_ok = n < p.N;
+    constexpr int c_begin = 0;
     constexpr uint32_t kMagic = H2<XT>::MAGIC;
     uint32_t magic_bits = kMagic;
     const h2 magic = *reinterpret_cast<const h2*>(&magic_bits);
-    int g_cur = -1;
     h2 s2 = H2<XT>::from_float(1.f), z2 = H2<XT>::from_float(0.f);
     if (p.zero_is_scalar && p.gzeros) z2 = H2<XT>::from_float((float)(*reinterpret_cast<const int32_t*>(p.gzeros)));
-    const bool need_s = p.W_group_mode >= 2, need_z = (p.W_group_mode == 1 || p.W_group_mode >= 3) && !p.zero_is_scalar;
-    const int n_groups = (p.K + p.group_size - 1) / p.group_size;
-    XT s_next = XT(1.f), z_next = XT(0.f);
-    if (n_ok) {                                          // the first group of this CTA's K range
-      const size_t g_first = (size_t)((kt0 * 64) / p.group_size);
-      if (need_s) s_next = reinterpret_cast<const XT*>(p.gscales)[g_first * p.N + n];
-      if (need_z) z_next = reinterpret_cast<const XT*>(p.gzeros)[g_first * p.N + n];
-    }
-    for (int i = 0; i < nloc; ++i) {
-      const int s = i % STAGES, kt = kt0 + i;
-      if (!mbar_wait(wfull + s, (uint32_t)((i / STAGES) & 1), &s_abort, p.status, 6)) break;
-      const int g = (kt * 64) / p.group_size;
-      if (g != g_cur) {
-        // this group's scale / zero were requested one group ahead; request the next group's now so that their
-        // latency (a first touch in DRAM for every CTA that shares the column tile) is off the critical path
-        g_cur = g;
-        s2 = h2(s_next, s_next);
-        if (!p.zero_is_scalar) z2 = h2(z_next, z_next);
-        const int gn = g + 1;
-        if (n_ok && gn < n_groups) {
-          if (need_s) s_next = reinterpret_cast<const XT*>(p.gscales)[(size_t)gn * p.N + n];
-          if (need_z) z_next = reinterpret_cast<const XT*>(p.gzeros)[(size_t)gn * p.N + n];
-        }
-      }
+    for (int i = dw / CBLOCKS; i < nloc; i += TSPLIT) {
+      const int s = i % STAGES, ws = i % WS;
+      TC_CK(c0);
+      if (!mbar_wait(wfull + ws, (uint32_t)((i / WS) & 1), &s_abort, p.status, 6)) break;
+      TC_CK(c1); TC_ACC(acc0, c0, c1);
       unsigned char* st = smem + s * STAGE_BYTES;
-      const uint32_t* wst = reinterpret_cast<const uint32_t*>(st + A_BYTES + B_BYTES);
+      const uint32_t* wst = reinterpret_cast<const uint32_t*>(wring + ws * WSLOT_BYTES);
+      // this column's scale and zero of the tile's group arrived with the packed words
+      if (need_s) { const XT sv = reinterpret_cast<const XT*>(wring + ws * WSLOT_BYTES + W_BYTES)[nl]; s2 = h2(sv, sv); }
+      if (need_z) { const XT zv = reinterpret_cast<const XT*>(wring + ws * WSLOT_BYTES + W_BYTES + META_BYTES)[nl]; z2 = h2(zv, zv); }
       unsigned char* brow = st + A_BYTES + nl * 128;
+      // all packed words into registers first: the ring slot goes back to its producer at once, and the stores below may
+      // alias the words for the compiler
+      uint32_t wv[RPW];
+#pragma unroll
+      for (int cc = 0; cc < RPW; ++cc) wv[cc] = wst[(c_begin + cc) * BN + nl];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(wempty + ws);
+      TC_CK(c2);
+      // the dequantised tile of K tile i - STAGES must have been consumed before its slot is overwritten
+      if (!mbar_wait(empty + s, (uint32_t)(((i / STAGES) & 1) ^ 1), &s_abort, p.status, 8)) break;
+      TC_CK(c3); TC_ACC(acc1, c2, c3);
       // the mode is decided once per K tile, outside the unrolled loops: a branch per pair would serialise them
       auto unpack_tile = [&](auto fma_tag) {
         constexpr bool FMA = decltype(fma_tag)::value;
         const h2 zs2 = (p.W_group_mode == 1 || p.W_group_mode == 3) ? z2 : H2<XT>::from_float(0.f);
         const h2 ss2 = (p.W_group_mode >= 2) ? s2 : H2<XT>::from_float(1.f);
-        uint32_t wv[RPW];                                    // all packed words first: the stores below may alias them for the compiler
         uint32_t keep_lo = 0u, keep_hi = 0u;
-#pragma unroll
-        for (int cc = 0; cc < RPW; ++cc) wv[cc] = wst[(c_begin + cc) * BN + nl];
 #pragma unroll
         for (int cc = 0; cc < RPW; ++cc) {
           const int c = c_begin + cc;                        // packed row inside the K tile
@@ -617,13 +660,26 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
         }
       };
       if (p.W_group_mode == 4) unpack_tile(std::true_type{}); else unpack_tile(std::false_type{});
+      TC_CK(c4); TC_ACC(acc2, c3, c4);
       fence_proxy_async_smem();                            // generic-proxy stores -> visible to the tensor core
       __syncwarp();
       if (lane == 0) mbar_arrive(bready + s);
+      TC_CK(c5); TC_ACC(acc3, c4, c5);
     }
+    if (dw == 0 && lane == 0) { TC_GT(13); TC_PUT(8, acc0); TC_PUT(9, acc1); TC_PUT(10, acc2); TC_PUT(11, acc3); }
+  }
+  if (p.splits > 1) {
+    // all threads of all the tile's CTAs: partial tiles complete -> reduce -> nobody leaves while its tile is being read
+    __syncwarp();
+    cluster_barrier();
+    if (warp == 2 && lane == 0) TC_GT(4);
+    cluster_reduce_partials(p, smem, m0, n0, BN, AM, warp, (int)(blockDim.x >> 5), lane, sw_s, b_s);
+    __syncwarp();
+    cluster_barrier();
   }
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) TC_GT(14);
   if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
@@ -650,15 +706,41 @@ static int launch_tma_kernel(const CUtensorMap& tmA, const CUtensorMap& tmB, con
   return GL_OK;
 }
 
+// slots of the packed-word ring: what is left of the 227 KB after the activation / dequantised-tile stages, at most 16
+constexpr int a16_wslots(int NB, int BN, int STAGES, int AM) {
+  const int wslot = a16_wslot_bytes(NB, BN);
+  const int left = 232448 - 1024 - STAGES * (AM * 128 * 128 + BN * 128) - 4096;
+  return left / wslot > 16 ? 16 : left / wslot;
+}
+
 template <typename XT, int NB, int BN, int STAGES, int AM = 1>
-static int launch_a16_kernel(const CUtensorMap& tmA, const CUtensorMap& tmW, const TcParams& p, cudaStream_t st) {
+static int launch_a16_kernel(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMap& tmS, const CUtensorMap& tmZ, const TcParams& p,
+                             cudaStream_t st) {
   constexpr int WROWS = 64 / (32 / NB);
-  constexpr size_t stage = AM * 128 * 128 + BN * 128 + ((WROWS * BN * 4 + 1023) / 1024) * 1024;
-  const size_t smem = 1024 + STAGES * stage + (4 * STAGES + 1) * 8 + 32 + 2 * BN * 4 + 16;
-  auto kern = gl_gemm_tc_a16wn_kernel<XT, NB, BN, STAGES, AM>;
+  constexpr int WS = a16_wslots(NB, BN, STAGES, AM);
+  static_assert(WS >= 2, "packed-word ring needs two slots");
+  constexpr size_t stage = AM * 128 * 128 + BN * 128, wslot = a16_wslot_bytes(NB, BN);
+  constexpr size_t smem = 1024 + STAGES * stage + WS * wslot + (3 * STAGES + 2 * WS + 1) * 8 + 32 + 2 * BN * 4 + 16;
+  static_assert(smem <= 232448, "shared memory of the A16Wn kernel");
+  auto kern = gl_gemm_tc_a16wn_kernel<XT, NB, BN, STAGES, AM, WS>;
   if (int rc = set_smem(kern, smem)) return rc;
   const int tiles = ((p.M + 128 * AM - 1) / (128 * AM)) * ((p.N + BN - 1) / BN);
-  kern<<<dim3(tiles, p.splits), (6 + deq_warps(BN)) * 32, smem, st>>>(tmA, tmW, p);
+  // K splits: the CTAs of a tile are one cluster along y and add their partial tiles through distributed shared memory
+  if (p.splits > 1 && (p.splits > 8 || (size_t)AM * 128 * BN * 4 > STAGES * stage + WS * wslot))
+    GL_FAIL(GL_E_INVALID, "gl_matmul: %d K splits of a %d x %d tile do not fit the cluster reduction", p.splits, AM * 128, BN);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(tiles, p.splits);
+  cfg.blockDim = dim3((6 + deq_warps(BN)) * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = (unsigned)p.splits;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  GL_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, tmA, tmW, tmS, tmZ, p));
   GL_LAUNCH_CHECK("gl_gemm_tc_a16wn_kernel");
   return GL_OK;
 }
@@ -684,6 +766,10 @@ static TcPath classify(const gl_matmul_args* a) {
     if (need_z && !a->zero_is_scalar && a->zeros_dtype != a->x_dtype) return TC_NONE;
     if (need_z && a->zero_is_scalar && a->zeros_dtype != GL_INT32) return TC_NONE;
     if (a->channel_scale_mode == 1 && a->W_group_mode >= 2) return TC_NONE;
+    // the rows of group scales / zeros travel by TMA: 16-byte base and pitch
+    if ((need_s || (need_z && !a->zero_is_scalar)) && a->N % 8 != 0) return TC_NONE;
+    if (need_s && ((uintptr_t)a->scales & 15)) return TC_NONE;
+    if (need_z && !a->zero_is_scalar && ((uintptr_t)a->zeros & 15)) return TC_NONE;
     return TC_A16WN;
   }
   // A8W8: e4m3 x e4m3 or int8 x int8, weights [N, K] with K contiguous, optional per-token / per-channel scales
@@ -726,8 +812,6 @@ static int tc_tile_n(const gl_matmul_args* a) {
   return ((req == 128 || req == 256) && a->N >= req) ? req : dflt;
 }
 
-// K splits of the A16Wn kernel: when the tiles alone leave more than half of the SMs idle, the K range is divided
-// so that about one CTA per SM runs; every split gets at least 8 K tiles and none is empty
 // Shape of an A16Wn launch: columns per tile (BN), 128-row activation tiles per CTA (AM) and K splits.
 // More than 128 rows and words of at most 4 bits share one dequantised weight tile between two accumulators (AM = 2);
 // 256-column tiles when that still gives 96 CTAs; when the tiles alone leave more than half of the SMs idle, the K range
@@ -745,6 +829,7 @@ static A16Plan a16_plan(const gl_matmul_args* a) {
   const int nkt = (a->K + 63) / 64, sms = gl_num_sms();
   pl.splits = 1;
   if (tiles > 16384 || nkt < 16) return pl;
+  if (pl.AM == 2 && pl.BN == 256) return pl;           // a 256 x 256 fp32 partial tile does not fit the CTA's shared memory
   auto trim = [&](int s) { while (s > 1 && (s - 1) * ((nkt + s - 1) / s) >= nkt) --s; return s; };
   const int req = tc_cfg_int(a, "splits", 0);
   if (req >= 1 && req <= 8 && req <= nkt / 8) { pl.splits = trim(req); return pl; }
@@ -759,10 +844,6 @@ static A16Plan a16_plan(const gl_matmul_args* a) {
 
 uint64_t gl_gemm_tc_workspace(const gl_matmul_args* a) {
   uint64_t need = gl_matmul_counter_bytes();
-  if (classify(a) == TC_A16WN) {
-    const int s = a16_plan(a).splits;
-    if (s > 1) need += (uint64_t)s * a->M * a->N * sizeof(float);
-  }
   return need;
 }
 
@@ -787,18 +868,24 @@ int gl_gemm_tc_launch(const gl_matmul_args* a, cudaStream_t st) {
   if (path == TC_A16WN) {
     p.nkt = (a->K + 63) / 64;
     p.splits = a16.splits;
-    p.counters = reinterpret_cast<unsigned int*>(a->workspace);
-    p.partials = reinterpret_cast<float*>(reinterpret_cast<char*>(a->workspace) + gl_matmul_counter_bytes());
     p.idesc = gl_idesc(1, a->x_dtype == GL_BF16 ? 1 : 0, a->x_dtype == GL_BF16 ? 1 : 0, 128, BN);
     if (a->channel_scale_mode == 1) { p.scales_w = a->scales; p.scales_w_dtype = a->meta_dtype; }
     p.gscales = a->scales; p.gzeros = a->zeros; p.group_size = a->group_size; p.W_group_mode = a->W_group_mode; p.zero_is_scalar = a->zero_is_scalar;
     const int wrows = 64 / a->elements_per_sample;
     if (int rc = gl_make_tmap_2d(&tmA, a->x, a->x_dtype == GL_BF16 ? 1 : 2, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->K * 2, 64, 128, true)) return rc;
     if (int rc = gl_make_tmap_2d(&tmB, a->w, 3, (uint64_t)a->N, (uint64_t)(a->K / a->elements_per_sample), (uint64_t)a->N * 4, (uint32_t)BN, (uint32_t)wrows, false)) return rc;
+    // rows of group scales / zeros [groups][N]; modes without them never touch their map
+    CUtensorMap tmS = tmB, tmZ = tmB;
+    const int xkind = a->x_dtype == GL_BF16 ? 1 : 2;
+    const uint64_t n_groups = (uint64_t)(a->K / a->group_size);
+    if (a->W_group_mode >= 2)
+      if (int rc = gl_make_tmap_2d(&tmS, a->scales, xkind, (uint64_t)a->N, n_groups, (uint64_t)a->N * 2, (uint32_t)BN, 1, false)) return rc;
+    if ((a->W_group_mode == 1 || a->W_group_mode >= 3) && !a->zero_is_scalar)
+      if (int rc = gl_make_tmap_2d(&tmZ, a->zeros, xkind, (uint64_t)a->N, n_groups, (uint64_t)a->N * 2, (uint32_t)BN, 1, false)) return rc;
 #define GL_A16(XT, NB)                                                                              \
-    (BN == 256 ? launch_a16_kernel<XT, NB, 256, 3>(tmA, tmB, p, st) : launch_a16_kernel<XT, NB, 128, 4>(tmA, tmB, p, st))
+    (BN == 256 ? launch_a16_kernel<XT, NB, 256, 3>(tmA, tmB, tmS, tmZ, p, st) : launch_a16_kernel<XT, NB, 128, 4>(tmA, tmB, tmS, tmZ, p, st))
     if (a16.AM == 2) {      // (words of at most 4 bits: three 72 KB stages at BN = 256, four 52 KB stages at BN = 128)
-#define GL_A16_2(XT, NB) (BN == 256 ? launch_a16_kernel<XT, NB, 256, 3, 2>(tmA, tmB, p, st) : launch_a16_kernel<XT, NB, 128, 4, 2>(tmA, tmB, p, st))
+#define GL_A16_2(XT, NB) (BN == 256 ? launch_a16_kernel<XT, NB, 256, 3, 2>(tmA, tmB, tmS, tmZ, p, st) : launch_a16_kernel<XT, NB, 128, 4, 2>(tmA, tmB, tmS, tmZ, p, st))
       if (a->x_dtype == GL_BF16) {
         if (a->W_nbits == 4) return GL_A16_2(__nv_bfloat16, 4);
         if (a->W_nbits == 2) return GL_A16_2(__nv_bfloat16, 2);
