@@ -147,7 +147,9 @@ def enable_activation_scaling(batch_size):
 # grown on demand, never inside the C library.  Its counter head must be zero on first use.
 # ---------------------------------------------------------------------------------------------
 _WORKSPACES = {}
-_KERNEL_OVERRIDE = 0   # 1 routes every matmul to the general CUDA-core kernel (tests compare kernels with it)
+# 1 routes every matmul to the general CUDA-core kernel (tests compare kernels with it), 2 to the tensor-core kernel
+# wherever it covers the problem (decode sizes included)
+_KERNEL_OVERRIDE = int(os.environ.get("GEMLITE_B200_KERNEL_OVERRIDE", "0"))
 
 
 def set_kernel_override(value: int):

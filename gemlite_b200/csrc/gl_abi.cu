@@ -78,13 +78,12 @@ KernelId select(const gl_matmul_args* a, int* family_out) {
   if (family_out) *family_out = fam;
   if (mx && (fam == GL_MM_GEMV_REVSPLITK || fam == GL_MM_GEMV_SPLITK)) return K_INVALID;  // as the reference: MX only on GEMV / GEMM*
   if (a->kernel_override == 1) return K_GENERIC;
-  // decode sizes stream; from M = 17 the tensor-core kernel is faster (measured: M = 32 streams in 186 us, the
-  // 128-row tcgen05 tile takes 77 us), and the streaming kernel only covers what that kernel cannot take
+  if (a->kernel_override == 2 && gl_gemm_tc_supported(a)) return K_TC;
+  // decode sizes stream; from M = 17 the tensor-core kernel is faster (measured on 8192 x 8192 A16W4 at M = 32: 30 us
+  // with the operands swapped, 44 us as two 16-row launches of the streaming kernel), and the streaming kernel only
+  // covers what that kernel cannot take (17..32 rows as two launches of 16 rows where a plan exists)
   const bool stream_ok = !mx && gl_gemv_stream_supported(a);
   if (stream_ok && a->M <= 16) return K_STREAM;
-  // 17..32 rows: two launches of the warp-independent streaming kernel (16 rows each; the second reads the weights from
-  // L2) take about half the time of the 128-row tensor-core tile at these sizes
-  if (stream_ok && a->M <= 32 && gl_gemv_split_rows_ok(a)) return K_STREAM;
   if (gl_gemm_tc_supported(a)) return K_TC;
   if (stream_ok) return K_STREAM;
   return K_GENERIC;

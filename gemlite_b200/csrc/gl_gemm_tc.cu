@@ -157,12 +157,24 @@ __device__ __forceinline__ void epilogue_tile_swapped(const TcParams& p, uint32_
   }
 }
 
+// Operands swapped (at most 64 rows of x): the accumulator's lanes are output channels and its columns are tokens.
+// One block of 32 channels x 32 tokens: out[token][channel] = v * s_w[channel] + bias[channel]; the 32 lanes of a
+// warp write 32 consecutive channels of one token.
+__device__ __forceinline__ void finish_swapped_block(const TcParams& p, int ch, int ch_local, int tok0, const float (&v)[32], const float* sw_s,
+                                                     const float* b_s) {
+  if (ch >= p.N) return;
+  const float sc = sw_s[ch_local], bi = b_s[ch_local];
+#pragma unroll
+  for (int i = 0; i < 32; ++i)
+    if (tok0 + i < p.M) gl_store_out(p.out, (size_t)(tok0 + i) * p.N + ch, fmaf(v[i], sc, bi), p.out_dtype);
+}
+
 // split-K of the A16Wn kernel: the CTAs that share an output tile (one per K range) form a thread-block cluster.  Each
 // leaves its fp32 partial tile in its own shared memory (the operand ring is free by then) as 4 KB blocks of
 // 32 rows x 32 columns, [float4 index][row] so that a warp moves 512 contiguous bytes per instruction ...
 __device__ __forceinline__ void epilogue_dump_partial(uint32_t tmem_d, unsigned char* dump, int block0, int BN, int epi_warp, int lane) {
   const int quad = epi_warp & 3;                       // TMEM lane quadrant this warp may read
-  for (int c = 0; c < BN / 32; ++c) {
+  for (int c = 0; c < (BN + 31) / 32; ++c) {
     uint32_t rr[32];
     tmem_ld_32x32(tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32), rr);
     float4* dst = reinterpret_cast<float4*>(dump + (size_t)(block0 + c * 4 + quad) * 4096) + lane;
@@ -173,12 +185,13 @@ __device__ __forceinline__ void epilogue_dump_partial(uint32_t tmem_d, unsigned 
 }
 // ... and after a cluster barrier CTA r sums, in split order, every block b with b % splits == r out of all the CTAs'
 // shared memories and finishes those rows.  Every warp of the CTA takes part.
+// (swapped operands: BN is the number of token columns, a block's lanes are channels n0 + quad * 32 + lane)
 __device__ __forceinline__ void cluster_reduce_partials(const TcParams& p, const unsigned char* dump, int m0, int n0, int BN, int AM, int warp,
-                                                        int n_warps, int lane, const float* sw_s, const float* b_s) {
-  const int CB = BN / 32, blocks = AM * CB * 4, S = p.splits, r = blockIdx.y;
+                                                        int n_warps, int lane, const float* sw_s, const float* b_s, bool swapped) {
+  const int CB = (BN + 31) / 32, blocks = AM * CB * 4, S = p.splits, r = blockIdx.y;
   for (int b = r + S * warp; b < blocks; b += S * n_warps) {
     const int am = b / (CB * 4), c = (b >> 2) % CB, quad = b & 3;
-    const int mrow = m0 + am * 128 + quad * 32, nb = n0 + c * 32;
+    const int mrow = swapped ? c * 32 : m0 + am * 128 + quad * 32, nb = swapped ? n0 + quad * 32 : n0 + c * 32;
     if (mrow >= p.M || nb >= p.N) continue;            // warp-uniform
     float v[32];
 #pragma unroll
@@ -194,7 +207,8 @@ __device__ __forceinline__ void cluster_reduce_partials(const TcParams& p, const
         v[4 * q] += t.x; v[4 * q + 1] += t.y; v[4 * q + 2] += t.z; v[4 * q + 3] += t.w;
       }
     }
-    if (mrow + lane < p.M) finish_row_chunk(p, mrow + lane, nb, v, 1.f, sw_s + c * 32, b_s + c * 32);
+    if (swapped) finish_swapped_block(p, nb + lane, quad * 32 + lane, mrow, v, sw_s, b_s);
+    else if (mrow + lane < p.M) finish_row_chunk(p, mrow + lane, nb, v, 1.f, sw_s + c * 32, b_s + c * 32);
   }
 }
 __device__ __forceinline__ void cluster_barrier() {
@@ -420,14 +434,35 @@ extern "C" __attribute__((visibility("default"))) void gl_debug_tc_trace(void* b
 }
 #define TC_GT(i) do { if (g_tc_trace) { unsigned long long t_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_)); \
     g_tc_trace[(size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 16 + (i)] = t_; } } while (0)
+#if GL_TC_TRACE == 2   // light mode: no clock reads inside the loops, failed barrier polls are counted instead
+#define TC_CK(v) const long long v = 0
+#define TC_ACC(acc, a, b) do { } while (0)
+__device__ __forceinline__ bool mbar_wait_counted(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code, long long& polls) {
+  while (!mbar_try_wait(bar, parity)) {
+    if (((++polls) & 0xFFFFF) == 0) { *abort_flag = 1; if (status) atomicCAS(status, 0, code); return false; }
+    if (*abort_flag) return false;
+  }
+  return true;
+}
+#define TC_WAIT(bar, par, code, acc) mbar_wait_counted(bar, par, &s_abort, p.status, code, acc)
+#else
 #define TC_CK(v) const long long v = clock64()
 #define TC_ACC(acc, a, b) acc += (b) - (a)
+#define TC_WAIT(bar, par, code, acc) mbar_wait_spin(bar, par, &s_abort, p.status, code)
+#endif
 #define TC_PUT(i, acc) do { if (g_tc_trace) g_tc_trace[(size_t)(blockIdx.y * gridDim.x + blockIdx.x) * 16 + (i)] = (unsigned long long)(acc); } while (0)
 #else
 #define TC_GT(i) do { } while (0)
 #define TC_CK(v) do { } while (0)
 #define TC_ACC(acc, a, b) do { } while (0)
 #define TC_PUT(i, acc) do { } while (0)
+#define TC_WAIT(bar, par, code, acc) mbar_wait_spin(bar, par, &s_abort, p.status, code)
+#endif
+// waits of the dequant warps (32 lanes each)
+#ifdef GL_SPIN_DQ
+#define TC_WAIT_DQ(bar, par, code, acc) TC_WAIT(bar, par, code, acc)
+#else
+#define TC_WAIT_DQ(bar, par, code, acc) mbar_wait(bar, par, &s_abort, p.status, code)
 #endif
 
 // WS: slots of the packed-word ring.  The packed weights come from DRAM (every other operand of a stage is L2- or
@@ -436,19 +471,27 @@ extern "C" __attribute__((visibility("default"))) void gl_debug_tc_trace(void* b
 // A slot of that ring also carries the tile's row of group scales and of group zeros (BN values each): a dequant warp
 // that fetched them from global memory had the load's latency in its chain at every change of group, because the
 // mbarrier arrive that publishes its tile orders all of the thread's earlier memory operations.
-template <typename XT, int NB, int BN, int STAGES, int AM = 1, int WS = STAGES>
+// SW > 0: operands swapped for at most SW (32 / 64) rows of x.  The dequantised tile (128 channels x 64 k) is the MMA's
+// 128-row operand and is written straight to tensor memory (lane = channel, 32 columns of two k each) instead of
+// shared memory; x is the SW-column operand in shared memory; the accumulator holds [channel lane][token column].
+// Shared memory carries 128 bytes per clock: with both operands there, a 128 x 128 x 64 step moves 32 KB for the MMAs,
+// 16 KB of dequantised stores and 20 KB of TMA writes, which takes longer than its arithmetic.  This form moves the
+// x tile (SW x 128 bytes) in and out and the packed words, nothing else.
+template <typename XT, int NB, int BN, int STAGES, int AM = 1, int WS = STAGES, int SW = 0>
 __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_kernel(const __grid_constant__ CUtensorMap tmA,
                                                                   const __grid_constant__ CUtensorMap tmW,
                                                                   const __grid_constant__ CUtensorMap tmS,
                                                                   const __grid_constant__ CUtensorMap tmZ, const TcParams p) {
   constexpr int E = 32 / NB;                           // k values per packed word
   constexpr int WROWS = 64 / E;                        // packed rows per 64-wide K tile (8 for 4-bit)
-  constexpr int A_TILE = 128 * 128;
-  constexpr int A_BYTES = AM * A_TILE, B_BYTES = BN * 128, W_BYTES = WROWS * BN * 4;
+  static_assert(SW == 0 || (BN == 128 && AM == 1), "swapped operands: one 128-channel tile");
+  constexpr int A_TILE = (SW ? SW : 128) * 128;        // rows of x per tile x 64 k x 2 bytes
+  constexpr int A_BYTES = AM * A_TILE, B_BYTES = SW ? 0 : BN * 128, W_BYTES = WROWS * BN * 4;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t WT_COL0 = SW;                     // swapped: dequantised tiles of the STAGES slots follow the accumulator
   constexpr int META_BYTES = BN * 2;                   // one row of scales or zeros
   constexpr int WSLOT_BYTES = a16_wslot_bytes(NB, BN);
-  constexpr uint32_t TMEM_COLS = next_pow2_cols(AM * BN);
+  constexpr uint32_t TMEM_COLS = next_pow2_cols(SW ? SW + STAGES * 32 : AM * BN);
   constexpr int HALF = 16 / NB;                        // field a shares a 32-bit extraction with field a + HALF
   constexpr uint32_t FMASK = ((1u << NB) - 1u) * 0x00010001u;
   using h2 = typename H2<XT>::T;
@@ -456,9 +499,9 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
   unsigned char* wring = smem + STAGES * STAGE_BYTES;                           // [WS] packed-word tiles
-  uint64_t* full = reinterpret_cast<uint64_t*>(wring + WS * WSLOT_BYTES);       // A landed
-  uint64_t* bready = full + STAGES;                                             // B tile written by the dequant warps
-  uint64_t* empty = bready + STAGES;                                            // MMAs of the stage retired
+  // ready: the stage's operands are complete (the x tile landed and every dequant warp of the tile arrived)
+  uint64_t* ready = reinterpret_cast<uint64_t*>(wring + WS * WSLOT_BYTES);
+  uint64_t* empty = ready + STAGES;                                             // MMAs of the stage retired
   uint64_t* wfull = empty + STAGES;                                             // [WS] packed W landed
   uint64_t* wempty = wfull + WS;                                                // [WS] packed W read by every dequant warp
   uint64_t* tmem_full = wempty + WS;
@@ -468,7 +511,7 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
   __shared__ int s_abort;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_m = (p.M + 128 * AM - 1) / (128 * AM);
+  const int tiles_m = SW ? 1 : (p.M + 128 * AM - 1) / (128 * AM);
   const int m0 = (blockIdx.x % tiles_m) * (128 * AM), n0 = (blockIdx.x / tiles_m) * BN;
   // K tiles of this CTA: blockIdx.y picks one of p.splits equal ranges (the last one may be shorter)
   const int kt_per = (p.nkt + p.splits - 1) / p.splits;
@@ -480,7 +523,7 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
   if (threadIdx.x == 0) {
     s_abort = 0;
     // a K tile is dequantised by BN / 32 warps (one per 32 columns)
-    for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(bready + s, BN / 32); mbar_init(empty + s, 1); }
+    for (int s = 0; s < STAGES; ++s) { mbar_init(ready + s, 1 + BN / 32); mbar_init(empty + s, 1); }
     for (int s = 0; s < WS; ++s) { mbar_init(wfull + s, 1); mbar_init(wempty + s, BN / 32); }
     mbar_init(tmem_full, 1);
     fence_barrier_init();
@@ -505,68 +548,96 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
       for (int i = 0; i < nloc; ++i) {
         const int s = i % STAGES, kt = kt0 + i;
         TC_CK(c0);
-        if (!mbar_wait(empty + s, (uint32_t)(((i / STAGES) & 1) ^ 1), &s_abort, p.status, 2)) break;
+        if (!TC_WAIT(empty + s, (uint32_t)(((i / STAGES) & 1) ^ 1), 2, acc0)) break;
         TC_CK(c1); TC_ACC(acc0, c0, c1);
         unsigned char* st = smem + s * STAGE_BYTES;
-        mbar_expect_tx(full + s, A_BYTES);
+        mbar_expect_tx(ready + s, A_BYTES);
 #pragma unroll
-        for (int am = 0; am < AM; ++am) tma_load_2d(st + am * A_TILE, &tmA, full + s, kt * 64, m0 + am * 128);   // rows past M read as zeros
+        for (int am = 0; am < AM; ++am) tma_load_2d(st + am * A_TILE, &tmA, ready + s, kt * 64, m0 + am * 128);   // rows past M read as zeros
       }
       TC_PUT(12, acc0);
     }
   } else if (warp == 1) {
     if (lane == 0) {
       bool ok = true;
+      TC_CK(cl0);
       for (int i = 0; i < nloc && ok; ++i) {
         const int s = i % STAGES;
         const uint32_t ph = (uint32_t)((i / STAGES) & 1);
         TC_CK(c0);
-        if (!mbar_wait(full + s, ph, &s_abort, p.status, 3)) { ok = false; break; }
+        if (!TC_WAIT(ready + s, ph, 3, acc0)) { ok = false; break; }
         TC_CK(c1); TC_ACC(acc0, c0, c1);
-        if (!mbar_wait(bready + s, ph, &s_abort, p.status, 5)) { ok = false; break; }
         TC_CK(c2); TC_ACC(acc1, c1, c2);
         tc_fence_after();
         const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
         const uint64_t db = smem_desc_sw128(sa + A_BYTES);
+        if constexpr (SW > 0) {
+          const uint64_t dx = smem_desc_sw128(sa);
 #pragma unroll
-        for (int am = 0; am < AM; ++am) {
-          const uint64_t da = smem_desc_sw128(sa + am * A_TILE);
+          for (int j = 0; j < 4; ++j)                 // 16 k = 8 tensor-memory columns of the dequantised tile
+            mma_ts_f16(tmem_base, tmem_base + WT_COL0 + (uint32_t)(s * 32 + j * 8), dx + 2 * j, p.idesc, (i > 0 || j > 0) ? 1u : 0u);
+        } else {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) mma_ss<KIND_F16>(tmem_base + am * BN, da + 2 * j, db + 2 * j, p.idesc, (i > 0 || j > 0) ? 1u : 0u);
+          for (int am = 0; am < AM; ++am) {
+            const uint64_t da = smem_desc_sw128(sa + am * A_TILE);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) mma_ss<KIND_F16>(tmem_base + am * BN, da + 2 * j, db + 2 * j, p.idesc, (i > 0 || j > 0) ? 1u : 0u);
+          }
         }
+        TC_CK(c2b); TC_ACC(acc3, c2, c2b);
         tc_commit(empty + s);
         TC_CK(c3); TC_ACC(acc2, c2, c3);
       }
       if (ok) tc_commit(tmem_full);
-      TC_GT(2); TC_PUT(5, acc0); TC_PUT(6, acc1); TC_PUT(7, acc2);
+      TC_CK(cl1);
+      TC_GT(2); TC_PUT(5, acc0); TC_PUT(6, acc1); TC_PUT(7, acc2); TC_PUT(15, cl1 - cl0); TC_PUT(4, acc3);
     }
   } else if (warp < 2 + kNumEpiWarps) {
     if (warp == 2) {
-      // the first epilogue warp has nothing to do until the accumulator is complete: its lane 0 feeds the packed-word ring
-      if (lane == 0) {
+      // the first epilogue warp has nothing to do until the accumulator is complete: it feeds the packed-word ring.
+      // Lanes 0 / 1 / 2 issue the copies of the packed words / the scale row / the zero row in one warp instruction.
+      if (lane < 3) {
+        const CUtensorMap* tm = lane == 0 ? &tmW : lane == 1 ? &tmS : &tmZ;
+        const bool active = lane == 0 || (lane == 1 && need_s) || (lane == 2 && need_z);
+        const uint32_t off = lane == 0 ? 0u : lane == 1 ? (uint32_t)W_BYTES : (uint32_t)(W_BYTES + META_BYTES);
+        const uint32_t tx = W_BYTES + (need_s ? META_BYTES : 0) + (need_z ? META_BYTES : 0);
+        const int tiles_per_group = p.group_size / 64;
+        int g = (kt0 * 64) / p.group_size, g_left = tiles_per_group - kt0 % tiles_per_group;
         for (int i = 0; i < nloc; ++i) {
           const int ws = i % WS;
-          if (!mbar_wait(wempty + ws, (uint32_t)(((i / WS) & 1) ^ 1), &s_abort, p.status, 7)) break;
-          unsigned char* slot = wring + ws * WSLOT_BYTES;
-          const int g = ((kt0 + i) * 64) / p.group_size;
-          mbar_expect_tx(wfull + ws, W_BYTES + (need_s ? META_BYTES : 0) + (need_z ? META_BYTES : 0));
-          tma_load_2d(slot, &tmW, wfull + ws, n0, (kt0 + i) * WROWS);
-          if (need_s) tma_load_2d(slot + W_BYTES, &tmS, wfull + ws, n0, g);                  // columns past N read as zeros
-          if (need_z) tma_load_2d(slot + W_BYTES + META_BYTES, &tmZ, wfull + ws, n0, g);
+          if (!TC_WAIT(wempty + ws, (uint32_t)(((i / WS) & 1) ^ 1), 7, acc0)) break;
+          if (lane == 0) mbar_expect_tx(wfull + ws, tx);
+          if (active) tma_load_2d(wring + ws * WSLOT_BYTES + off, tm, wfull + ws, n0, lane == 0 ? (kt0 + i) * WROWS : g);   // columns past N read as zeros
+          if (--g_left == 0) { ++g; g_left = tiles_per_group; }
         }
+        if (lane == 0) TC_PUT(3, acc0);
       }
       __syncwarp();
     }
     if (mbar_wait(tmem_full, 0u, &s_abort, p.status, 4)) {
       tc_fence_after();
-      if (warp == 2 && lane == 0) TC_GT(3);
       if (p.splits == 1) {
+        if constexpr (SW > 0) {
+          const int quad = warp & 3;
+          for (int c0 = 0; c0 < SW && c0 < p.M; c0 += 32) {
+            uint32_t rr[32];
+            tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, rr);
+            float v[32];
 #pragma unroll
-        for (int am = 0; am < AM; ++am) epilogue_tile<false>(p, tmem_base + am * BN, m0 + am * 128, n0, BN, warp, lane, sw_s, b_s);
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(rr[i]);
+            finish_swapped_block(p, n0 + quad * 32 + lane, quad * 32 + lane, c0, v, sw_s, b_s);
+          }
+        } else {
+#pragma unroll
+          for (int am = 0; am < AM; ++am) epilogue_tile<false>(p, tmem_base + am * BN, m0 + am * 128, n0, BN, warp, lane, sw_s, b_s);
+        }
       } else {
         // every operand of the ring has been consumed (the accumulator is complete): the ring holds the partial tile now
+        if constexpr (SW > 0) epilogue_dump_partial(tmem_base, smem, 0, SW, warp, lane);
+        else {
 #pragma unroll
-        for (int am = 0; am < AM; ++am) epilogue_dump_partial(tmem_base + am * BN, smem, am * (BN / 32) * 4, BN, warp, lane);
+          for (int am = 0; am < AM; ++am) epilogue_dump_partial(tmem_base + am * BN, smem, am * (BN / 32) * 4, BN, warp, lane);
+        }
       }
     }
   } else {
@@ -577,7 +648,8 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
     // tile (wait, read, unpack, store, fence, arrive) is mostly latency, and two tiles in flight hide it.
     constexpr int TSPLIT = deq_warps(BN) / CBLOCKS;        // warp groups (1 or 2)
     constexpr int RPW = WROWS;                             // packed rows per warp: the whole K tile of its 32 columns
-    const int nl = (dw % CBLOCKS) * 32 + lane;             // column inside the tile
+    // (swapped: the warp writes the lane quadrant of tensor memory it may access, so its 32 channels are that quadrant's)
+    const int nl = (SW ? (warp & 3) : (dw % CBLOCKS)) * 32 + lane;             // column (channel) inside the tile
     constexpr int c_begin = 0;
     constexpr uint32_t kMagic = H2<XT>::MAGIC;
     uint32_t magic_bits = kMagic;
@@ -587,7 +659,7 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
     for (int i = dw / CBLOCKS; i < nloc; i += TSPLIT) {
       const int s = i % STAGES, ws = i % WS;
       TC_CK(c0);
-      if (!mbar_wait(wfull + ws, (uint32_t)((i / WS) & 1), &s_abort, p.status, 6)) break;
+      if (!TC_WAIT_DQ(wfull + ws, (uint32_t)((i / WS) & 1), 6, acc0)) break;
       TC_CK(c1); TC_ACC(acc0, c0, c1);
       unsigned char* st = smem + s * STAGE_BYTES;
       const uint32_t* wst = reinterpret_cast<const uint32_t*>(wring + ws * WSLOT_BYTES);
@@ -603,9 +675,16 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
       __syncwarp();
       if (lane == 0) mbar_arrive(wempty + ws);
       TC_CK(c2);
-      // the dequantised tile of K tile i - STAGES must have been consumed before its slot is overwritten
-      if (!mbar_wait(empty + s, (uint32_t)(((i / STAGES) & 1) ^ 1), &s_abort, p.status, 8)) break;
+      // the dequantised tile of K tile i - STAGES must have been consumed before its slot is overwritten (swapped: the
+      // tile is built in registers first and the wait comes before the store to tensor memory)
+      if constexpr (SW == 0) if (!TC_WAIT_DQ(empty + s, (uint32_t)(((i / STAGES) & 1) ^ 1), 8, acc1)) break;
       TC_CK(c3); TC_ACC(acc1, c2, c3);
+      uint32_t outr[SW ? 32 : 1];                          // swapped: this channel's 64 k, two per register
+      // 16-byte chunk `chunk` (8 consecutive k) of this channel's row
+      auto emit = [&](int chunk, uint32_t e0, uint32_t e1, uint32_t e2, uint32_t e3) {
+        if constexpr (SW > 0) { outr[4 * chunk] = e0; outr[4 * chunk + 1] = e1; outr[4 * chunk + 2] = e2; outr[4 * chunk + 3] = e3; }
+        else *reinterpret_cast<uint4*>(brow + ((chunk ^ (nl & 7)) << 4)) = make_uint4(e0, e1, e2, e3);
+      };
       // the mode is decided once per K tile, outside the unrolled loops: a branch per pair would serialise them
       auto unpack_tile = [&](auto fma_tag) {
         constexpr bool FMA = decltype(fma_tag)::value;
@@ -646,24 +725,31 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
           const int chunk0 = c * (E / 8);
           if constexpr (NB == 8) {                         // a word holds 4 k: two consecutive packed rows make one 16-byte chunk
             if ((cc & 1) == 0) { keep_lo = L[0]; keep_hi = Hh[0]; }
-            else *reinterpret_cast<uint4*>(brow + (((c >> 1) ^ (nl & 7)) << 4)) = make_uint4(keep_lo, keep_hi, L[0], Hh[0]);
+            else emit(c >> 1, keep_lo, keep_hi, L[0], Hh[0]);
           } else if constexpr (NB == 4) {
-            *reinterpret_cast<uint4*>(brow + (((chunk0) ^ (nl & 7)) << 4)) = make_uint4(L[0], L[1], Hh[0], Hh[1]);
+            emit(chunk0, L[0], L[1], Hh[0], Hh[1]);
           } else {
             constexpr int CH = HALF / 8;                     // chunks per half (1 for 2-bit, 2 for 1-bit)
 #pragma unroll
             for (int ch = 0; ch < CH; ++ch) {
-              *reinterpret_cast<uint4*>(brow + (((chunk0 + ch) ^ (nl & 7)) << 4)) = make_uint4(L[4 * ch], L[4 * ch + 1], L[4 * ch + 2], L[4 * ch + 3]);
-              *reinterpret_cast<uint4*>(brow + (((chunk0 + CH + ch) ^ (nl & 7)) << 4)) = make_uint4(Hh[4 * ch], Hh[4 * ch + 1], Hh[4 * ch + 2], Hh[4 * ch + 3]);
+              emit(chunk0 + ch, L[4 * ch], L[4 * ch + 1], L[4 * ch + 2], L[4 * ch + 3]);
+              emit(chunk0 + CH + ch, Hh[4 * ch], Hh[4 * ch + 1], Hh[4 * ch + 2], Hh[4 * ch + 3]);
             }
           }
         }
       };
       if (p.W_group_mode == 4) unpack_tile(std::true_type{}); else unpack_tile(std::false_type{});
       TC_CK(c4); TC_ACC(acc2, c3, c4);
-      fence_proxy_async_smem();                            // generic-proxy stores -> visible to the tensor core
+      if constexpr (SW > 0) {
+        if (!TC_WAIT_DQ(empty + s, (uint32_t)(((i / STAGES) & 1) ^ 1), 8, acc1)) break;
+        tc_fence_after();                                  // the MMAs that read this slot have retired
+        tmem_st_32x32(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + WT_COL0 + (uint32_t)(s * 32), outr);
+        tc_fence_before();
+      } else {
+        fence_proxy_async_smem();                          // generic-proxy stores -> visible to the tensor core
+      }
       __syncwarp();
-      if (lane == 0) mbar_arrive(bready + s);
+      if (lane == 0) mbar_arrive(ready + s);
       TC_CK(c5); TC_ACC(acc3, c4, c5);
     }
     if (dw == 0 && lane == 0) { TC_GT(13); TC_PUT(8, acc0); TC_PUT(9, acc1); TC_PUT(10, acc2); TC_PUT(11, acc3); }
@@ -672,8 +758,7 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
     // all threads of all the tile's CTAs: partial tiles complete -> reduce -> nobody leaves while its tile is being read
     __syncwarp();
     cluster_barrier();
-    if (warp == 2 && lane == 0) TC_GT(4);
-    cluster_reduce_partials(p, smem, m0, n0, BN, AM, warp, (int)(blockDim.x >> 5), lane, sw_s, b_s);
+    cluster_reduce_partials(p, smem, m0, n0, SW ? SW : BN, AM, warp, (int)(blockDim.x >> 5), lane, sw_s, b_s, SW > 0);
     __syncwarp();
     cluster_barrier();
   }
@@ -707,26 +792,26 @@ static int launch_tma_kernel(const CUtensorMap& tmA, const CUtensorMap& tmB, con
 }
 
 // slots of the packed-word ring: what is left of the 227 KB after the activation / dequantised-tile stages, at most 16
-constexpr int a16_wslots(int NB, int BN, int STAGES, int AM) {
+constexpr int a16_wslots(int NB, int BN, int STAGES, int AM, int SW = 0) {
   const int wslot = a16_wslot_bytes(NB, BN);
-  const int left = 232448 - 1024 - STAGES * (AM * 128 * 128 + BN * 128) - 4096;
+  const int left = 232448 - 1024 - STAGES * (AM * (SW ? SW : 128) * 128 + (SW ? 0 : BN * 128)) - 4096;
   return left / wslot > 16 ? 16 : left / wslot;
 }
 
-template <typename XT, int NB, int BN, int STAGES, int AM = 1>
+template <typename XT, int NB, int BN, int STAGES, int AM = 1, int SW = 0>
 static int launch_a16_kernel(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMap& tmS, const CUtensorMap& tmZ, const TcParams& p,
                              cudaStream_t st) {
   constexpr int WROWS = 64 / (32 / NB);
-  constexpr int WS = a16_wslots(NB, BN, STAGES, AM);
+  constexpr int WS = a16_wslots(NB, BN, STAGES, AM, SW);
   static_assert(WS >= 2, "packed-word ring needs two slots");
-  constexpr size_t stage = AM * 128 * 128 + BN * 128, wslot = a16_wslot_bytes(NB, BN);
+  constexpr size_t stage = AM * (SW ? SW : 128) * 128 + (SW ? 0 : BN * 128), wslot = a16_wslot_bytes(NB, BN);
   constexpr size_t smem = 1024 + STAGES * stage + WS * wslot + (3 * STAGES + 2 * WS + 1) * 8 + 32 + 2 * BN * 4 + 16;
   static_assert(smem <= 232448, "shared memory of the A16Wn kernel");
-  auto kern = gl_gemm_tc_a16wn_kernel<XT, NB, BN, STAGES, AM, WS>;
+  auto kern = gl_gemm_tc_a16wn_kernel<XT, NB, BN, STAGES, AM, WS, SW>;
   if (int rc = set_smem(kern, smem)) return rc;
-  const int tiles = ((p.M + 128 * AM - 1) / (128 * AM)) * ((p.N + BN - 1) / BN);
+  const int tiles = (SW ? 1 : (p.M + 128 * AM - 1) / (128 * AM)) * ((p.N + BN - 1) / BN);
   // K splits: the CTAs of a tile are one cluster along y and add their partial tiles through distributed shared memory
-  if (p.splits > 1 && (p.splits > 8 || (size_t)AM * 128 * BN * 4 > STAGES * stage + WS * wslot))
+  if (p.splits > 1 && (p.splits > 8 || (size_t)AM * 128 * (SW ? 64 : BN) * 4 > STAGES * stage + WS * wslot))
     GL_FAIL(GL_E_INVALID, "gl_matmul: %d K splits of a %d x %d tile do not fit the cluster reduction", p.splits, AM * 128, BN);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(tiles, p.splits);
@@ -817,14 +902,17 @@ static int tc_tile_n(const gl_matmul_args* a) {
 // 256-column tiles when that still gives 96 CTAs; when the tiles alone leave more than half of the SMs idle, the K range
 // is divided so that about one CTA per SM runs (every split gets at least 8 K tiles and none is empty).
 // Cache entry fields "tile_n", "am", "splits" override the three choices.
-struct A16Plan { int BN, AM, splits; };
+struct A16Plan { int BN, AM, splits, SW; };
 static A16Plan a16_plan(const gl_matmul_args* a) {
   A16Plan pl;
+  // at most 64 rows: operands swapped, the rows of x are the MMA's 32 or 64 columns ("swap": 0 in the cache entry turns it off)
+  pl.SW = (a->M <= 64 && tc_cfg_int(a, "swap", 1) != 0) ? (a->M <= 32 ? 32 : 64) : 0;
   pl.AM = (a->M > 128 && a->W_nbits <= 4 && tc_cfg_int(a, "am", 2) == 2) ? 2 : 1;
   const int64_t tiles_m = (a->M + 128 * pl.AM - 1) / (128 * pl.AM);
   const int req_bn = tc_cfg_int(a, "tile_n", 0);
   pl.BN = (a->N >= 256 && tiles_m * ((a->N + 255) / 256) >= 96) ? 256 : 128;
   if ((req_bn == 128 || req_bn == 256) && a->N >= req_bn) pl.BN = req_bn;
+  if (pl.SW) pl.BN = 128;
   const int64_t tiles = tiles_m * ((a->N + pl.BN - 1) / pl.BN);
   const int nkt = (a->K + 63) / 64, sms = gl_num_sms();
   pl.splits = 1;
@@ -860,7 +948,7 @@ int gl_gemm_tc_launch(const gl_matmul_args* a, cudaStream_t st) {
   p.out = a->out; p.out_dtype = a->out_dtype; p.bias = a->bias;
   p.status = reinterpret_cast<int*>(reinterpret_cast<char*>(a->workspace) + gl_matmul_counter_bytes() - 256);
   p.meta_scale = nullptr;
-  const A16Plan a16 = path == TC_A16WN ? a16_plan(a) : A16Plan{0, 1, 1};
+  const A16Plan a16 = path == TC_A16WN ? a16_plan(a) : A16Plan{0, 1, 1, 0};
   const int BN = path == TC_A16WN ? a16.BN : tc_tile_n(a);
   // decode sizes of the TMA formats swap the operands (16 or 32 token columns)
   const int swap_bn = (path != TC_A16WN && a->M <= 32 && a->N >= 128) ? (a->M <= 16 ? 16 : 32) : 0;
@@ -868,11 +956,11 @@ int gl_gemm_tc_launch(const gl_matmul_args* a, cudaStream_t st) {
   if (path == TC_A16WN) {
     p.nkt = (a->K + 63) / 64;
     p.splits = a16.splits;
-    p.idesc = gl_idesc(1, a->x_dtype == GL_BF16 ? 1 : 0, a->x_dtype == GL_BF16 ? 1 : 0, 128, BN);
+    p.idesc = gl_idesc(1, a->x_dtype == GL_BF16 ? 1 : 0, a->x_dtype == GL_BF16 ? 1 : 0, 128, a16.SW ? a16.SW : BN);
     if (a->channel_scale_mode == 1) { p.scales_w = a->scales; p.scales_w_dtype = a->meta_dtype; }
     p.gscales = a->scales; p.gzeros = a->zeros; p.group_size = a->group_size; p.W_group_mode = a->W_group_mode; p.zero_is_scalar = a->zero_is_scalar;
     const int wrows = 64 / a->elements_per_sample;
-    if (int rc = gl_make_tmap_2d(&tmA, a->x, a->x_dtype == GL_BF16 ? 1 : 2, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->K * 2, 64, 128, true)) return rc;
+    if (int rc = gl_make_tmap_2d(&tmA, a->x, a->x_dtype == GL_BF16 ? 1 : 2, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->K * 2, 64, a16.SW ? (uint32_t)a16.SW : 128u, true)) return rc;
     if (int rc = gl_make_tmap_2d(&tmB, a->w, 3, (uint64_t)a->N, (uint64_t)(a->K / a->elements_per_sample), (uint64_t)a->N * 4, (uint32_t)BN, (uint32_t)wrows, false)) return rc;
     // rows of group scales / zeros [groups][N]; modes without them never touch their map
     CUtensorMap tmS = tmB, tmZ = tmB;
@@ -884,6 +972,20 @@ int gl_gemm_tc_launch(const gl_matmul_args* a, cudaStream_t st) {
       if (int rc = gl_make_tmap_2d(&tmZ, a->zeros, xkind, (uint64_t)a->N, n_groups, (uint64_t)a->N * 2, (uint32_t)BN, 1, false)) return rc;
 #define GL_A16(XT, NB)                                                                              \
     (BN == 256 ? launch_a16_kernel<XT, NB, 256, 3>(tmA, tmB, tmS, tmZ, p, st) : launch_a16_kernel<XT, NB, 128, 4>(tmA, tmB, tmS, tmZ, p, st))
+    if (a16.SW) {
+#define GL_A16_SW(XT, NB) (a16.SW == 32 ? launch_a16_kernel<XT, NB, 128, 4, 1, 32>(tmA, tmB, tmS, tmZ, p, st) : launch_a16_kernel<XT, NB, 128, 4, 1, 64>(tmA, tmB, tmS, tmZ, p, st))
+      if (a->x_dtype == GL_BF16) {
+        if (a->W_nbits == 8) return GL_A16_SW(__nv_bfloat16, 8);
+        if (a->W_nbits == 4) return GL_A16_SW(__nv_bfloat16, 4);
+        if (a->W_nbits == 2) return GL_A16_SW(__nv_bfloat16, 2);
+        return GL_A16_SW(__nv_bfloat16, 1);
+      }
+      if (a->W_nbits == 8) return GL_A16_SW(__half, 8);
+      if (a->W_nbits == 4) return GL_A16_SW(__half, 4);
+      if (a->W_nbits == 2) return GL_A16_SW(__half, 2);
+      return GL_A16_SW(__half, 1);
+#undef GL_A16_SW
+    }
     if (a16.AM == 2) {      // (words of at most 4 bits: three 72 KB stages at BN = 256, four 52 KB stages at BN = 128)
 #define GL_A16_2(XT, NB) (BN == 256 ? launch_a16_kernel<XT, NB, 256, 3, 2>(tmA, tmB, tmS, tmZ, p, st) : launch_a16_kernel<XT, NB, 128, 4, 2>(tmA, tmB, tmS, tmZ, p, st))
       if (a->x_dtype == GL_BF16) {

@@ -117,7 +117,7 @@ typedef struct gl_matmul_args {
   int32_t      matmul_type;    /* GL_MM_* ; GL_MM_AUTO applies get_matmul_type()            */
   int64_t      w_stride_k, w_stride_n;
   int64_t      s_stride_g, s_stride_n;
-  int32_t      kernel_override; /* 0 = library picks the kernel; 1 = the general CUDA-core kernel (testing / debugging) */
+  int32_t      kernel_override; /* 0 = library picks the kernel; 1 = the general CUDA-core kernel; 2 = the tensor-core kernel where it covers the problem (testing / tuning) */
   int32_t      sx_layout;      /* layout of block-scaled `scales_x`: 0 = [Mpad, K/g] rows, 1 = 128x4 scale atoms */
   int32_t      reserved[2];    /* must be 0 */
   const void*  w_scales_atoms; /* optional copy of the MX / NV weight scales as 128x4 scale atoms, or NULL   */

@@ -40,7 +40,8 @@ CASES = [  # (N, K, nbits, gs, M, expected kernel, element tolerance in units of
     (2048, 4096, 4, 128, 5, "gl_gemv_warp_kernel", 2e-4),
     (2048, 4096, 2, 64, 16, "gl_gemv_warp_kernel", 2e-4),
     (2048, 4096, 8, 128, 16, "gl_gemv_warp_kernel", 2e-4),
-    (2048, 4096, 4, 128, 32, "gl_gemv_warp_kernel", 2e-4),
+    (2048, 4096, 4, 32, 32, "gl_gemv_warp_kernel", 2e-4),     # groups of 32: two 16-row launches of the streaming kernel
+    (2048, 4096, 4, 128, 32, "gl_gemm_tc_kernel", 3e-2),      # operands swapped
     (2032, 3968, 4, 128, 33, "gl_gemm_tc_kernel", 3e-2),      # weights rounded to bf16 after dequantisation, as the reference does
     (2032, 3968, 4, 128, 130, "gl_gemm_tc_kernel", 3e-2),
     (2032, 3968, 2, 64, 130, "gl_gemm_tc_kernel", 3e-2),

@@ -46,6 +46,29 @@ def test_a16wn_prefill_ragged(lib, nbits, gs, dtype):
         assert rel_fro(y, want) < 1e-2, (M, nbits, rel_fro(y, want))
 
 
+@pytest.mark.parametrize("nbits,gs", [(4, 128), (2, 64), (1, 128), (8, 128)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_a16wn_swapped_operands_small_batches(lib, nbits, gs, dtype):
+    """At most 64 rows run with the operands swapped (32 or 64 token columns).  The library sends up to 32 rows to the
+    streaming kernel, so those sizes are forced onto the tensor-core kernel here (kernel_override = 2)."""
+    from gemlite_b200 import core, helper
+    core.set_kernel_override(2)
+    try:
+        for (N, K) in ((2032, 3968), (1024, 8192)):          # ragged channel tile with 31 K tiles; a split-K cluster
+            for M in (1, 17, 32, 33, 47, 64):
+                x, W_q, s, z, b = make_a16wn(N, K, nbits, gs, dtype, seed=3100 + M + nbits, M=M)
+                layer = helper.A16Wn_HQQ_INT(device="cuda:0", dtype=dtype, W_nbits=nbits).from_weights(W_q.cuda(), s.cuda(), z.cuda(), bias=b.cuda())
+                assert _kernel_name(layer, x.cuda()) == "gl_gemm_tc_kernel"
+                y = layer(x.cuda())
+                y2 = layer(x.cuda())
+                assert _status_word() == 0
+                assert torch.equal(y, y2)
+                want = exact_a16wn(x, W_q, s, z, b, gs)
+                assert rel_fro(y.float().cpu().numpy(), want) < 1e-2, (N, K, M, nbits, rel_fro(y.float().cpu().numpy(), want))
+    finally:
+        core.set_kernel_override(0)
+
+
 @pytest.mark.parametrize("mode", ["sym", "shift_scalar", "asym_nofma", "channelwise_post", "no_meta"])
 def test_a16wn_prefill_modes(lib, mode):
     from gemlite_b200 import GemLiteLinear, DType
@@ -164,8 +187,9 @@ def test_scale_atom_layout_matches_reference_shuffle(lib):
 
 
 def test_a16wn_split_k_is_deterministic_and_sized(lib):
-    """Few-tile problems split K over several CTAs per tile; partial tiles are added in split order by the CTA that
-    arrives last, so two runs give identical bits, and the workspace the library asks for covers the partial tiles."""
+    """Few-tile problems split K over the CTAs of a cluster; each CTA adds its share of the partial tiles in split
+    order out of the cluster's shared memories, so two runs give identical bits and no workspace beyond the counter
+    block is needed."""
     import ctypes
     from gemlite_b200 import core, helper
     N, K, M = 1024, 4096, 48
@@ -182,7 +206,7 @@ def test_a16wn_split_k_is_deterministic_and_sized(lib):
     a = core._fill_args(xs, layer.bias, layer.W_q, layer.scales, layer.zeros, None, None, out, layer.get_meta_args(), -1)
     assert lib.gl_matmul_kernel_name(ctypes.byref(a)) == b"gl_gemm_tc_kernel"
     need = lib.gl_matmul_workspace_bytes(ctypes.byref(a))
-    assert need >= lib.gl_matmul_counter_bytes() + 2 * M * N * 4          # at least two partial tiles
+    assert need == lib.gl_matmul_counter_bytes()
     a.workspace, a.workspace_bytes = core._workspace(torch.device("cuda", 0), int(need)).data_ptr(), int(need) - 16
     from gemlite_b200 import _lib
     assert lib.gl_matmul(ctypes.byref(a), torch.cuda.current_stream().cuda_stream) == _lib.GL_E_WORKSPACE   # too small: an error, no fallback

@@ -51,9 +51,7 @@ def test_benchmark_shapes_land_on_their_kernels():
         assert _plan(M, 8192, 8192, 4, 128)[0] == "gl_gemv_warp_kernel"
         assert _plan(M, 8192, 8192, 2, 64)[0] == "gl_gemv_warp_kernel"
         assert _plan(M, 8192, 8192, 8, 128)[0] == "gl_gemv_warp_kernel"
-    for M in (17, 32):      # two launches of the streaming kernel, 16 rows each
-        assert _plan(M, 8192, 8192, 4, 128)[0] == "gl_gemv_warp_kernel"
-    for M in (33, 64, 256, 1024, 4096, 8192):
+    for M in (17, 32, 33, 64, 256, 1024, 4096, 8192):
         assert _plan(M, 8192, 8192, 4, 128)[0] == "gl_gemm_tc_kernel"
     # Llama-70B shard shapes at decode size
     for N, K in ((8192, 3584), (1280, 8192), (8192, 1024), (7168, 8192)):
