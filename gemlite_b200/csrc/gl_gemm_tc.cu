@@ -973,7 +973,10 @@ int gl_gemm_tc_launch(const gl_matmul_args* a, cudaStream_t st) {
 #define GL_A16(XT, NB)                                                                              \
     (BN == 256 ? launch_a16_kernel<XT, NB, 256, 3>(tmA, tmB, tmS, tmZ, p, st) : launch_a16_kernel<XT, NB, 128, 4>(tmA, tmB, tmS, tmZ, p, st))
     if (a16.SW) {
-#define GL_A16_SW(XT, NB) (a16.SW == 32 ? launch_a16_kernel<XT, NB, 128, 4, 1, 32>(tmA, tmB, tmS, tmZ, p, st) : launch_a16_kernel<XT, NB, 128, 4, 1, 64>(tmA, tmB, tmS, tmZ, p, st))
+#ifndef GL_SW_STAGES
+#define GL_SW_STAGES 4      // stages of the x / tensor-memory ring of the swapped form
+#endif
+#define GL_A16_SW(XT, NB) (a16.SW == 32 ? launch_a16_kernel<XT, NB, 128, GL_SW_STAGES, 1, 32>(tmA, tmB, tmS, tmZ, p, st) : launch_a16_kernel<XT, NB, 128, GL_SW_STAGES, 1, 64>(tmA, tmB, tmS, tmZ, p, st))
       if (a->x_dtype == GL_BF16) {
         if (a->W_nbits == 8) return GL_A16_SW(__nv_bfloat16, 8);
         if (a->W_nbits == 4) return GL_A16_SW(__nv_bfloat16, 4);

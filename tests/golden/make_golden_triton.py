@@ -4,9 +4,11 @@ seeded inputs the parity tests regenerate, into tests/golden/triton_golden.npz.
 Run on a GPU machine with a checkout of the reference (it is not part of this repository):
     python tests/golden/make_golden_triton.py --ref /path/to/gemlite-checkout --out <file.npz> [--time]
 The reference package is imported from --ref; nothing of this repository's kernels is used.
-With --time the reference's kernels are also timed (CUDA events, 256 MB L2 flush between calls, the
+With --time the reference's kernels are also timed, eager and as a CUDA-graph replay over distinct layers (CUDA events, 256 MB L2 flush between calls, the
 protocol of the reference's examples/benchmark_triton.py:48-64) on the headline shapes and the numbers
 are written next to the fixture as JSON.
+With --baseline only the benchmark configurations at their own sizes (tests/golden_inputs.py BASELINE_CASES) are
+captured, as sampled rows and columns, into tests/golden/triton_golden_baseline.npz.
 """
 import argparse
 import json
@@ -56,6 +58,7 @@ def main():
     ap.add_argument("--ref", required=True)
     ap.add_argument("--out", required=True)
     ap.add_argument("--time", action="store_true")
+    ap.add_argument("--baseline", action="store_true", help="capture only the benchmark configurations at their own sizes (sampled rows / columns)")
     args = ap.parse_args()
     sys.path.insert(0, args.ref)
     import gemlite                                   # the reference
@@ -70,6 +73,38 @@ def main():
             fn()
         except Exception as e:  # record and go on: one broken reference kernel must not lose the rest
             log["errors"].append("%s: %s: %s" % (name, type(e).__name__, str(e)[:300]))
+
+    # ---- the benchmark configurations at their own sizes: sampled rows / columns of the reference's outputs ----
+    if args.baseline:
+        from tests import golden_inputs as gi
+        for tag, kind, N, K, nbits, gs, fams_by_M in gi.BASELINE_CASES:
+            layer = None
+            for M, fams in fams_by_M.items():
+                ops = gi.baseline_inputs(tag, M)
+                x = ops[0]
+                if layer is None:
+                    if kind == "a16":
+                        layer = rh.A16Wn_HQQ_INT(device="cuda:0", dtype=torch.bfloat16, W_nbits=nbits).from_weights(ops[1].cuda(), ops[2].cuda(), ops[3].cuda())
+                    else:
+                        lin = torch.nn.Linear(K, N, bias=False, dtype=torch.bfloat16)
+                        lin.weight.data = ops[1].clone()
+                        proc = rh.A8W8_FP8_dynamic if kind == "fp8" else rh.A4W4_MXFP_dynamic
+                        layer = proc(device="cuda:0", dtype=torch.bfloat16).from_linear(lin.cuda())
+                out["%s_M%d_x_sum" % (tag, M)] = np.array([float(x.double().sum())])
+                rows, cols = gi.kept_rows(M), gi.kept_cols(N)
+                for fam in fams:
+                    def run(fam=fam, M=M, x=x, tag=tag):
+                        y = layer.forward_manual(x.cuda(), fam)
+                        torch.cuda.synchronize()
+                        out["%s_M%d_%s" % (tag, M, fam)] = y.float().cpu().numpy()[rows][:, cols].astype(np.float32)
+                    guard("%s M%d %s" % (tag, M, fam), run)
+            del layer
+            torch.cuda.empty_cache()
+        out["reference_errors"] = np.array(log["errors"])
+        out["reference_env"] = np.array([torch.cuda.get_device_name(0), "triton " + __import__("triton").__version__])
+        np.savez_compressed(args.out, **out)
+        print("baseline fixture:", len(out), "arrays,", os.path.getsize(args.out), "bytes, errors:", log["errors"])
+        return
 
     # ---- A16Wn, every family ----
     for seed, N, K, nbits, gs, dt, Ms in A16_CASES:
@@ -186,6 +221,65 @@ def main():
                 time_case("FP8_4096x14336_M%d" % M, layer, 4096, M)
         guard("time fp8", fp8)
         log["timings"] = timings
+
+        # ---- the same kernels as a CUDA-graph replay over distinct layers (together larger than L2): the protocol
+        # bench.py uses for decode sizes, so that both sides of a comparison are measured the same way ----
+        timings_graph = {}
+        def graph_case(tag, make_layer, K, M, n_layers, reps=20):
+            layers = [make_layer(i) for i in range(n_layers)]
+            x = torch.randn(M, K, dtype=torch.bfloat16, device="cuda")
+            for _ in range(2):
+                for l in layers:
+                    l(x)                                   # JIT + autotune before the capture
+            torch.cuda.synchronize()
+            st = torch.cuda.Stream()
+            with torch.cuda.stream(st):
+                for l in layers:
+                    l(x)
+                st.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=st):
+                    for l in layers:
+                        l(x)
+                for _ in range(3):
+                    g.replay()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(st)
+                for _ in range(reps):
+                    g.replay()
+                b.record(st)
+                st.synchronize()
+            timings_graph[tag] = {"ms_per_layer": a.elapsed_time(b) / reps / n_layers, "layers": n_layers, "replays": reps}
+            del layers, g
+            torch.cuda.empty_cache()
+        def a16_layer(i):
+            gen = torch.Generator(device="cuda").manual_seed(100 + i)
+            N = K = 8192
+            W_q = torch.randint(0, 16, (N, K), generator=gen, device="cuda", dtype=torch.int32).to(torch.uint8)
+            s = (torch.randn(N * K // 128, 1, generator=gen, device="cuda").abs() * 0.02).to(torch.bfloat16)
+            z = (torch.rand(N * K // 128, 1, generator=gen, device="cuda") * 15).to(torch.bfloat16)
+            return rh.A16W4_HQQ_INT(device="cuda:0", dtype=torch.bfloat16).from_weights(W_q, s, z)
+        for M, n in ((1, 32), (16, 8), (64, 8), (256, 8)):
+            guard("graph a16 M%d" % M, lambda M=M, n=n: graph_case("A16W4_8192x8192_M%d" % M, a16_layer, 8192, M, n))
+        def fp8_layer(i):
+            lin = torch.nn.Linear(4096, 14336, bias=False, dtype=torch.bfloat16, device="cuda")
+            lin.weight.data.normal_(0, 0.02)
+            return rh.A8W8_FP8_dynamic(device="cuda:0", dtype=torch.bfloat16).from_linear(lin)
+        guard("graph fp8 M1", lambda: graph_case("FP8_4096x14336_M1", fp8_layer, 4096, 1, 4))
+        def mx_layer(i):
+            lin = torch.nn.Linear(16384, 16384, bias=False, dtype=torch.bfloat16, device="cuda")
+            lin.weight.data.normal_(0, 0.02)
+            return rh.A4W4_MXFP_dynamic(device="cuda:0", dtype=torch.bfloat16).from_linear(lin)
+        guard("graph mxfp4 M1", lambda: graph_case("MXFP4_16384x16384_M1", mx_layer, 16384, 1, 2))
+        log["timings_graph"] = timings_graph
+        log["timings_graph_protocol"] = "CUDA-graph replay of layer(x) over distinct layers, CUDA events around 20 replays"
+        log["date"] = time.strftime("%Y-%m-%d")
+        try:
+            import subprocess
+            log["clocks"] = subprocess.run(["nvidia-smi", "--query-gpu=clocks.sm,clocks.max.sm,clocks_event_reasons.active", "--format=csv,noheader"],
+                                           capture_output=True, text=True, timeout=20).stdout.strip()
+        except Exception as e:
+            log["clocks"] = "unavailable: %s" % e
     with open(os.path.splitext(args.out)[0] + ".json", "w") as fh:
         json.dump(log, fh, indent=1)
     print(json.dumps(log)[:2000])

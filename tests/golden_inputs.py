@@ -52,3 +52,39 @@ def lin_inputs(gold, name):
             assert abs(float(xs[M].double().sum()) - float(gold["lin_%s_M%d_x_sum" % (name, M)][0])) < 1e-6
         return W, xs
     raise KeyError(name)
+
+
+# ---- the benchmark configurations at their own sizes (tests/golden/triton_golden_baseline.npz) ----
+GOLDEN_BASELINE = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "triton_golden_baseline.npz")
+# (tag, kind, N, K, nbits, group size, {M: reference kernel families})
+BASELINE_CASES = [
+    ("cfg2_a16w4", "a16", 8192, 8192, 4, 128, {1: ("GEMV_REVSPLITK", "GEMM_SPLITK"), 64: ("GEMM_SPLITK", "GEMM"), 256: ("GEMM",)}),
+    ("cfg2_a16w2", "a16", 8192, 8192, 2, 64, {1: ("GEMV_REVSPLITK",), 64: ("GEMM",)}),
+    ("cfg3_fp8_up", "fp8", 14336, 4096, 8, 0, {1: ("GEMM_SPLITK",), 64: ("GEMM",)}),
+    ("cfg3_fp8_down", "fp8", 4096, 14336, 8, 0, {1: ("GEMM_SPLITK",), 64: ("GEMM",)}),
+    ("cfg4_mxfp4", "mxfp4", 16384, 16384, 4, 32, {1: ("GEMM_SPLITK",), 64: ("GEMM",)}),
+]
+
+
+def kept_rows(M):
+    """Rows of an [M, N] output the fixture keeps: the first two, the middle one, the last two."""
+    return sorted(set(r for r in (0, 1, M // 2, M - 2, M - 1) if 0 <= r < M))
+
+
+def kept_cols(N):
+    """Columns the fixture keeps: every 16th, shifted by 5 so that no tile boundary is favoured."""
+    return list(range(5, N, 16))
+
+
+def baseline_inputs(tag, M):
+    """The operands of one baseline case, regenerated from its seed: a16 -> (x, W_q, scales, zeros); fp8 / mxfp4 -> (x, W bf16)."""
+    idx = [c[0] for c in BASELINE_CASES].index(tag)
+    _, kind, N, K, nbits, gs, _ = BASELINE_CASES[idx]
+    if kind == "a16":
+        x, W_q, s, z, _ = make_a16wn(N, K, nbits, gs, torch.bfloat16, 5000 + 10 * idx + 1, M=1, with_bias=False)
+        g = torch.Generator().manual_seed(5500 + 10 * idx + M)
+        return torch.randn(M, K, generator=g).to(torch.bfloat16), W_q, s, z
+    g = torch.Generator().manual_seed(6000 + idx)
+    W = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16)
+    gx = torch.Generator().manual_seed(6500 + 10 * idx + M)
+    return torch.randn(M, K, generator=gx).to(torch.bfloat16), W

@@ -55,3 +55,37 @@ def test_dynamic_formats_match_reference_triton_outputs(lib, name):
                 assert rel_fro(y[: ref.shape[0]], ref) < 3e-2, (key, rel_fro(y[: ref.shape[0]], ref))
                 n += 1
     assert n >= 2
+
+
+
+@pytest.mark.parametrize("tag", [c[0] for c in gi.BASELINE_CASES])
+def test_baseline_shapes_match_reference_triton_outputs(lib, tag):
+    """The benchmark configurations at their own sizes against sampled rows / columns of the reference's outputs."""
+    import os
+    from gemlite_b200 import helper
+    if not os.path.exists(gi.GOLDEN_BASELINE):
+        pytest.skip("baseline fixture not captured")
+    gold = np.load(gi.GOLDEN_BASELINE)
+    _, kind, N, K, nbits, gs, fams_by_M = gi.BASELINE_CASES[[c[0] for c in gi.BASELINE_CASES].index(tag)]
+    layer, n = None, 0
+    for M, fams in fams_by_M.items():
+        ops = gi.baseline_inputs(tag, M)
+        x = ops[0]
+        assert abs(float(x.double().sum()) - float(gold["%s_M%d_x_sum" % (tag, M)][0])) < 1e-6
+        if layer is None:
+            if kind == "a16":
+                layer = helper.A16Wn_HQQ_INT(device="cuda:0", dtype=torch.bfloat16, W_nbits=nbits).from_weights(ops[1].cuda(), ops[2].cuda(), ops[3].cuda())
+            else:
+                lin = torch.nn.Linear(K, N, bias=False, dtype=torch.bfloat16, device="cuda:0")
+                lin.weight.data.copy_(ops[1])
+                P = helper.A8W8_FP8_dynamic if kind == "fp8" else helper.A4W4_MXFP_dynamic
+                layer = P(device="cuda:0", dtype=torch.bfloat16).from_linear(lin)
+        y = layer(x.cuda()).float().cpu().numpy()[gi.kept_rows(M)][:, gi.kept_cols(N)]
+        for fam in fams:
+            key = "%s_M%d_%s" % (tag, M, fam)
+            if key not in gold.files:
+                continue
+            tol = (3e-2 if fam.startswith("GEMV") else 1e-2) if kind == "a16" else 3e-2
+            assert rel_fro(y, gold[key]) < tol, (key, rel_fro(y, gold[key]))
+            n += 1
+    assert n >= 1

@@ -43,6 +43,27 @@ def test_a16wn_oracle_matches_reference_kernels():
     assert checked >= 30
 
 
+def test_a16wn_oracle_matches_reference_kernels_at_benchmark_size():
+    """cfg2 (8192 x 8192, 4-bit, groups of 128) at M = 1: the oracle against sampled columns of the reference's output."""
+    import os
+    import pytest
+    if not os.path.exists(gi.GOLDEN_BASELINE):
+        pytest.skip("baseline fixture not captured")
+    gold = np.load(gi.GOLDEN_BASELINE)
+    tag, _, N, K, nbits, gs, fams_by_M = gi.BASELINE_CASES[0]
+    x, W_q, s, z = gi.baseline_inputs(tag, 1)
+    zp = (-z.float() * s.float()).to(torch.bfloat16)
+    y = oracle.matmul_int(x, W_q.t().long(), s.view(N, -1).t(), zp.view(N, -1).t(), 4, 0, gs, x_dtype=torch.bfloat16).numpy()
+    y = y[gi.kept_rows(1)][:, gi.kept_cols(N)]
+    n = 0
+    for fam in fams_by_M[1]:
+        key = "%s_M1_%s" % (tag, fam)
+        if key in gold.files:
+            assert rel_fro(y, gold[key]) < (3e-2 if fam.startswith("GEMV") else 1e-2), (key, rel_fro(y, gold[key]))
+            n += 1
+    assert n >= 1
+
+
 def test_activation_quantisers_match_reference_kernels():
     gold = gi.load()
     xs, _ = gi.quant_inputs(gold)
