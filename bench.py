@@ -564,6 +564,7 @@ def sweep_gemm(device, only=None, mma_peaks=None):
     reference's own Triton kernel timed on a B200 when the golden fixtures were captured."""
     from gemlite_b200 import helper
     ref = bench_reference().get("reference_triton_timings", {}).get("timings", {})
+    ref_graph = bench_reference().get("reference_triton_timings_graph", {}).get("timings", {})
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.int8, device=device)
     dense_peak = {"A16W4": 2250.0, "A16W2": 2250.0, "A16W8": 2250.0, "FP8": 4500.0, "MXFP4": 9000.0, "NVFP4": 9000.0}     # nominal dense TFLOP/s
 
@@ -640,8 +641,12 @@ def sweep_gemm(device, only=None, mma_peaks=None):
                 pk = (mma_peaks or {}).get({"FP8": "fp8", "MXFP4": "mxfp4", "NVFP4": "nvfp4"}.get(fmt, "bf16"))
                 if pk:
                     row["frac_measured_mma_peak"] = tf / pk
-                r = ref.get("%s_%dx%d_M%d" % (fmt, K if fmt == "FP8" else N, N if fmt == "FP8" else K, M))
-                if r:
+                key = "%s_%dx%d_M%d" % (fmt, K if fmt == "FP8" else N, N if fmt == "FP8" else K, M)
+                r, rg = ref.get(key), ref_graph.get(key)
+                if rg and M <= 512:          # same protocol as this row: graph replay over distinct layers
+                    row["ref_triton_ms"] = rg["ms_per_layer"]
+                    row["ref_triton_protocol"] = "CUDA-graph replay over %d distinct layers (separate capture)" % rg["layers"]
+                elif r:
                     row["ref_triton_ms"] = r["min_ms"]
                     row["ref_triton_protocol"] = "eager call, L2 flushed (separate capture)"
                 res.append(row)

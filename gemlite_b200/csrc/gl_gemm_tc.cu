@@ -486,12 +486,15 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
   constexpr int WROWS = 64 / E;                        // packed rows per 64-wide K tile (8 for 4-bit)
   static_assert(SW == 0 || (BN == 128 && AM == 1), "swapped operands: one 128-channel tile");
   constexpr int A_TILE = (SW ? SW : 128) * 128;        // rows of x per tile x 64 k x 2 bytes
-  constexpr int A_BYTES = AM * A_TILE, B_BYTES = SW ? 0 : BN * 128, W_BYTES = WROWS * BN * 4;
+  // K tiles per stage: the swapped form pairs them, which halves the barrier round trips, commits and waits per tile
+  // (its stage is small: KT x tiles and KT x 32 tensor-memory columns)
+  constexpr int KT = SW ? 2 : 1;
+  constexpr int A_BYTES = KT * AM * A_TILE, B_BYTES = SW ? 0 : BN * 128, W_BYTES = WROWS * BN * 4;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr uint32_t WT_COL0 = SW;                     // swapped: dequantised tiles of the STAGES slots follow the accumulator
   constexpr int META_BYTES = BN * 2;                   // one row of scales or zeros
   constexpr int WSLOT_BYTES = a16_wslot_bytes(NB, BN);
-  constexpr uint32_t TMEM_COLS = next_pow2_cols(SW ? SW + STAGES * 32 : AM * BN);
+  constexpr uint32_t TMEM_COLS = next_pow2_cols(SW ? SW + STAGES * KT * 32 : AM * BN);
   constexpr int HALF = 16 / NB;                        // field a shares a 32-bit extraction with field a + HALF
   constexpr uint32_t FMASK = ((1u << NB) - 1u) * 0x00010001u;
   using h2 = typename H2<XT>::T;
@@ -517,6 +520,7 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
   const int kt_per = (p.nkt + p.splits - 1) / p.splits;
   const int kt0 = blockIdx.y * kt_per;
   const int nloc = min(kt_per, p.nkt - kt0);
+  const int nstages = (nloc + KT - 1) / KT;            // stages of KT K tiles
   if (threadIdx.x == 0) TC_GT(0);
   stage_epilogue_consts(p, sw_s, b_s, n0, BN);
 
@@ -545,15 +549,17 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int i = 0; i < nloc; ++i) {
-        const int s = i % STAGES, kt = kt0 + i;
+      for (int j = 0; j < nstages; ++j) {
+        const int s = j % STAGES, kt = kt0 + j * KT;
+        const int nt = min(KT, nloc - j * KT);             // K tiles of this stage (the last one may be short)
         TC_CK(c0);
-        if (!TC_WAIT(empty + s, (uint32_t)(((i / STAGES) & 1) ^ 1), 2, acc0)) break;
+        if (!TC_WAIT(empty + s, (uint32_t)(((j / STAGES) & 1) ^ 1), 2, acc0)) break;
         TC_CK(c1); TC_ACC(acc0, c0, c1);
         unsigned char* st = smem + s * STAGE_BYTES;
-        mbar_expect_tx(ready + s, A_BYTES);
+        mbar_expect_tx(ready + s, (uint32_t)(nt * AM * A_TILE));
+        for (int t = 0; t < nt; ++t)
 #pragma unroll
-        for (int am = 0; am < AM; ++am) tma_load_2d(st + am * A_TILE, &tmA, ready + s, kt * 64, m0 + am * 128);   // rows past M read as zeros
+          for (int am = 0; am < AM; ++am) tma_load_2d(st + (t * AM + am) * A_TILE, &tmA, ready + s, (kt + t) * 64, m0 + am * 128);   // rows past M read as zeros
       }
       TC_PUT(12, acc0);
     }
@@ -561,7 +567,7 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
     if (lane == 0) {
       bool ok = true;
       TC_CK(cl0);
-      for (int i = 0; i < nloc && ok; ++i) {
+      for (int i = 0; i < nstages && ok; ++i) {
         const int s = i % STAGES;
         const uint32_t ph = (uint32_t)((i / STAGES) & 1);
         TC_CK(c0);
@@ -572,10 +578,13 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
         const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
         const uint64_t db = smem_desc_sw128(sa + A_BYTES);
         if constexpr (SW > 0) {
-          const uint64_t dx = smem_desc_sw128(sa);
+          const int nt = min(KT, nloc - i * KT);
+          for (int t = 0; t < nt; ++t) {
+            const uint64_t dx = smem_desc_sw128(sa + t * A_TILE);
 #pragma unroll
-          for (int j = 0; j < 4; ++j)                 // 16 k = 8 tensor-memory columns of the dequantised tile
-            mma_ts_f16(tmem_base, tmem_base + WT_COL0 + (uint32_t)(s * 32 + j * 8), dx + 2 * j, p.idesc, (i > 0 || j > 0) ? 1u : 0u);
+            for (int j = 0; j < 4; ++j)               // 16 k = 8 tensor-memory columns of the dequantised tile
+              mma_ts_f16(tmem_base, tmem_base + WT_COL0 + (uint32_t)((s * KT + t) * 32 + j * 8), dx + 2 * j, p.idesc, (i > 0 || t > 0 || j > 0) ? 1u : 0u);
+          }
         } else {
 #pragma unroll
           for (int am = 0; am < AM; ++am) {
@@ -656,8 +665,12 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
     const h2 magic = *reinterpret_cast<const h2*>(&magic_bits);
     h2 s2 = H2<XT>::from_float(1.f), z2 = H2<XT>::from_float(0.f);
     if (p.zero_is_scalar && p.gzeros) z2 = H2<XT>::from_float((float)(*reinterpret_cast<const int32_t*>(p.gzeros)));
-    for (int i = dw / CBLOCKS; i < nloc; i += TSPLIT) {
-      const int s = i % STAGES, ws = i % WS;
+    // the group's n-th K tile: stages (of KT tiles) go to the groups in turn
+    for (int n = 0;; ++n) {
+      const int j = dw / CBLOCKS + (n / KT) * TSPLIT, t = n % KT, i = j * KT + t;
+      if (i >= nloc) break;
+      const int s = j % STAGES, ws = i % WS;
+      const bool first_of_stage = (t == 0), last_of_stage = (t == KT - 1) || (i + 1 >= nloc);
       TC_CK(c0);
       if (!TC_WAIT_DQ(wfull + ws, (uint32_t)((i / WS) & 1), 6, acc0)) break;
       TC_CK(c1); TC_ACC(acc0, c0, c1);
@@ -677,7 +690,7 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
       TC_CK(c2);
       // the dequantised tile of K tile i - STAGES must have been consumed before its slot is overwritten (swapped: the
       // tile is built in registers first and the wait comes before the store to tensor memory)
-      if constexpr (SW == 0) if (!TC_WAIT_DQ(empty + s, (uint32_t)(((i / STAGES) & 1) ^ 1), 8, acc1)) break;
+      if constexpr (SW == 0) if (!TC_WAIT_DQ(empty + s, (uint32_t)(((j / STAGES) & 1) ^ 1), 8, acc1)) break;
       TC_CK(c3); TC_ACC(acc1, c2, c3);
       uint32_t outr[SW ? 32 : 1];                          // swapped: this channel's 64 k, two per register
       // 16-byte chunk `chunk` (8 consecutive k) of this channel's row
@@ -741,15 +754,19 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
       if (p.W_group_mode == 4) unpack_tile(std::true_type{}); else unpack_tile(std::false_type{});
       TC_CK(c4); TC_ACC(acc2, c3, c4);
       if constexpr (SW > 0) {
-        if (!TC_WAIT_DQ(empty + s, (uint32_t)(((i / STAGES) & 1) ^ 1), 8, acc1)) break;
-        tc_fence_after();                                  // the MMAs that read this slot have retired
-        tmem_st_32x32(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + WT_COL0 + (uint32_t)(s * 32), outr);
-        tc_fence_before();
+        if (first_of_stage) {
+          if (!TC_WAIT_DQ(empty + s, (uint32_t)(((j / STAGES) & 1) ^ 1), 8, acc1)) break;
+          tc_fence_after();                                // the MMAs that read this slot have retired
+        }
+        tmem_st_32x32(tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + WT_COL0 + (uint32_t)((s * KT + t) * 32), outr);
+        if (last_of_stage) tc_fence_before();
       } else {
         fence_proxy_async_smem();                          // generic-proxy stores -> visible to the tensor core
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(ready + s);
+      if (last_of_stage) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(ready + s);
+      }
       TC_CK(c5); TC_ACC(acc3, c4, c5);
     }
     if (dw == 0 && lane == 0) { TC_GT(13); TC_PUT(8, acc0); TC_PUT(9, acc1); TC_PUT(10, acc2); TC_PUT(11, acc3); }
@@ -794,7 +811,7 @@ static int launch_tma_kernel(const CUtensorMap& tmA, const CUtensorMap& tmB, con
 // slots of the packed-word ring: what is left of the 227 KB after the activation / dequantised-tile stages, at most 16
 constexpr int a16_wslots(int NB, int BN, int STAGES, int AM, int SW = 0) {
   const int wslot = a16_wslot_bytes(NB, BN);
-  const int left = 232448 - 1024 - STAGES * (AM * (SW ? SW : 128) * 128 + (SW ? 0 : BN * 128)) - 4096;
+  const int left = 232448 - 1024 - STAGES * (SW ? 2 * SW * 128 : AM * 128 * 128 + BN * 128) - 4096;
   return left / wslot > 16 ? 16 : left / wslot;
 }
 
@@ -804,7 +821,7 @@ static int launch_a16_kernel(const CUtensorMap& tmA, const CUtensorMap& tmW, con
   constexpr int WROWS = 64 / (32 / NB);
   constexpr int WS = a16_wslots(NB, BN, STAGES, AM, SW);
   static_assert(WS >= 2, "packed-word ring needs two slots");
-  constexpr size_t stage = AM * (SW ? SW : 128) * 128 + (SW ? 0 : BN * 128), wslot = a16_wslot_bytes(NB, BN);
+  constexpr size_t stage = SW ? 2 * SW * 128 : AM * 128 * 128 + BN * 128, wslot = a16_wslot_bytes(NB, BN);   // (swapped: two x tiles per stage)
   constexpr size_t smem = 1024 + STAGES * stage + WS * wslot + (3 * STAGES + 2 * WS + 1) * 8 + 32 + 2 * BN * 4 + 16;
   static_assert(smem <= 232448, "shared memory of the A16Wn kernel");
   auto kern = gl_gemm_tc_a16wn_kernel<XT, NB, BN, STAGES, AM, WS, SW>;
