@@ -72,6 +72,8 @@ __global__ void __launch_bounds__(256) per_token_kernel(const void* __restrict__
                                                         float* __restrict__ scales, int M, int K, int x_dtype) {
   __shared__ float s_red[8];
   __shared__ float s_scale;
+  gl_launch_dependents();          // the matmul that follows may set itself up and prefetch weights meanwhile
+  gl_grid_dependency_wait();       // x comes from the previous kernel of the stream; q / scales may still be read by it
   const float qmax = INT8 ? 127.f : 448.f, qmin = INT8 ? -128.f : -448.f;
   for (int m = blockIdx.x; m < M; m += gridDim.x) {
     float amax = 0.f;
@@ -116,6 +118,8 @@ __global__ void __launch_bounds__(256) per_token_kernel(const void* __restrict__
 template <bool FP4>
 __global__ void __launch_bounds__(256) mx_quant_kernel(const void* __restrict__ x, uint8_t* __restrict__ q,
                                                        uint8_t* __restrict__ scales, int M, int Mpad, int K, int x_dtype, int layout) {
+  gl_launch_dependents();
+  gl_grid_dependency_wait();
   const int64_t units_per_row = K / 8;
   const int64_t total = (int64_t)Mpad * units_per_row;
   // the loop bound is warp-uniform so that every lane takes part in the group shuffles
@@ -163,6 +167,8 @@ __global__ void __launch_bounds__(256) mx_quant_kernel(const void* __restrict__ 
 __global__ void __launch_bounds__(256) amax_kernel(const void* __restrict__ x, uint32_t* __restrict__ amax_bits,
                                                    int64_t total_units, int x_dtype) {
   float amax = 0.f;
+  gl_launch_dependents();
+  gl_grid_dependency_wait();
   for (int64_t u = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; u < total_units; u += (int64_t)gridDim.x * blockDim.x) {
     float v[8];
     load8(x, u * 8, x_dtype, v);
@@ -187,6 +193,8 @@ __global__ void __launch_bounds__(256) nvfp4_quant_kernel(const void* __restrict
                                                           const uint32_t* __restrict__ amax_bits, int M, int Mpad, int K,
                                                           int x_dtype, int layout) {
   float meta;
+  gl_launch_dependents();
+  gl_grid_dependency_wait();       // the tensor-wide amax comes from the previous kernel
   if (meta_in != nullptr) meta = *meta_in;
   else meta = (448.f * 6.0f) / fmaxf(__uint_as_float(*amax_bits), 1e-6f);
   if (blockIdx.x == 0 && threadIdx.x == 0) *meta_out = meta;
@@ -247,9 +255,8 @@ extern "C" int gl_scale_activations_per_token(const void* x, void* q, float* sca
   cudaStream_t st = (cudaStream_t)stream;
   const int cap = gl_num_sms() * 8;
   const unsigned grid = (unsigned)(M < cap ? M : cap);
-  if (q_dtype == GL_INT8) per_token_kernel<true><<<grid, 256, 0, st>>>(x, (uint8_t*)q, scales, M, K, x_dtype);
-  else per_token_kernel<false><<<grid, 256, 0, st>>>(x, (uint8_t*)q, scales, M, K, x_dtype);
-  GL_LAUNCH_CHECK("per_token_kernel");
+  if (q_dtype == GL_INT8) GL_CUDA_CHECK(gl_launch_pdl(per_token_kernel<true>, dim3(grid), dim3(256), 0, st, x, (uint8_t*)q, scales, M, K, x_dtype));
+  else GL_CUDA_CHECK(gl_launch_pdl(per_token_kernel<false>, dim3(grid), dim3(256), 0, st, x, (uint8_t*)q, scales, M, K, x_dtype));
   return GL_OK;
 }
 
@@ -266,8 +273,7 @@ extern "C" int gl_scale_activations_mxfp4(const void* x, uint8_t* q, uint8_t* sc
   if (!q || !scales || ((uintptr_t)q & 3)) GL_FAIL(GL_E_INVALID, "gl_scale_activations_mxfp4: null or misaligned output");
   if (int rc = check_layout("gl_scale_activations_mxfp4", scale_layout, K / 32)) return rc;
   const int Mpad = scale_layout ? (M + 127) / 128 * 128 : (M + 31) / 32 * 32;
-  mx_quant_kernel<true><<<grid_units((int64_t)Mpad * (K / 8)), 256, 0, (cudaStream_t)stream>>>(x, q, scales, M, Mpad, K, x_dtype, scale_layout);
-  GL_LAUNCH_CHECK("mx_quant_kernel<fp4>");
+  GL_CUDA_CHECK(gl_launch_pdl(mx_quant_kernel<true>, dim3(grid_units((int64_t)Mpad * (K / 8))), dim3(256), 0, (cudaStream_t)stream, x, q, scales, M, Mpad, K, x_dtype, scale_layout));
   return GL_OK;
 }
 
@@ -278,8 +284,7 @@ extern "C" int gl_scale_activations_mxfp8(const void* x, uint8_t* q, uint8_t* sc
   if (!q || !scales || ((uintptr_t)q & 7)) GL_FAIL(GL_E_INVALID, "gl_scale_activations_mxfp8: null or misaligned output");
   if (int rc = check_layout("gl_scale_activations_mxfp8", scale_layout, K / 32)) return rc;
   const int Mpad = scale_layout ? (M + 127) / 128 * 128 : (M + 31) / 32 * 32;
-  mx_quant_kernel<false><<<grid_units((int64_t)Mpad * (K / 8)), 256, 0, (cudaStream_t)stream>>>(x, q, scales, M, Mpad, K, x_dtype, scale_layout);
-  GL_LAUNCH_CHECK("mx_quant_kernel<fp8>");
+  GL_CUDA_CHECK(gl_launch_pdl(mx_quant_kernel<false>, dim3(grid_units((int64_t)Mpad * (K / 8))), dim3(256), 0, (cudaStream_t)stream, x, q, scales, M, Mpad, K, x_dtype, scale_layout));
   return GL_OK;
 }
 
@@ -296,10 +301,8 @@ extern "C" int gl_scale_activations_nvfp4(const void* x, uint8_t* q, uint8_t* sc
   if (meta_in == nullptr) {
     GL_CUDA_CHECK(cudaMemsetAsync(amax_scratch, 0, sizeof(uint32_t), st));
     const int64_t units = (int64_t)M * (K / 8);
-    amax_kernel<<<grid_units(units), 256, 0, st>>>(x, amax_scratch, units, x_dtype);
-    GL_LAUNCH_CHECK("amax_kernel");
+    GL_CUDA_CHECK(gl_launch_pdl(amax_kernel, dim3(grid_units(units)), dim3(256), 0, st, x, amax_scratch, units, x_dtype));
   }
-  nvfp4_quant_kernel<<<grid_units((int64_t)Mpad * (K / 8)), 256, 0, st>>>(x, q, scales, meta_scale, meta_in, amax_scratch, M, Mpad, K, x_dtype, scale_layout);
-  GL_LAUNCH_CHECK("nvfp4_quant_kernel");
+  GL_CUDA_CHECK(gl_launch_pdl(nvfp4_quant_kernel, dim3(grid_units((int64_t)Mpad * (K / 8))), dim3(256), 0, st, x, q, scales, meta_scale, meta_in, amax_scratch, M, Mpad, K, x_dtype, scale_layout));
   return GL_OK;
 }

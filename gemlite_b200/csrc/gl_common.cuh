@@ -18,6 +18,25 @@ void gl_set_error(const char* fmt, ...);
 #define GL_LAUNCH_CHECK(name) do { cudaError_t _e = cudaGetLastError(); if (_e != cudaSuccess) { \
   gl_set_error("launch of %s failed: %s", name, cudaGetErrorString(_e)); return GL_E_CUDA; } } while (0)
 
+// Launch with the programmatic-stream-serialization attribute: the kernel may become resident while the previous
+// kernel of the stream drains.  Such a kernel executes griddepcontrol.wait before it touches anything the previous
+// kernel wrote or may still read (gl_grid_dependency_wait), and griddepcontrol.launch_dependents once its own
+// successor may start.
+#ifdef __CUDACC__
+template <typename K, typename... A>
+static inline cudaError_t gl_launch_pdl(K kern, dim3 grid, dim3 block, size_t smem, cudaStream_t st, A... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+__device__ __forceinline__ void gl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void gl_grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#endif
+
 static inline int gl_dtype_size(int dt) {
   switch (dt) {
     case GL_FP32: case GL_INT32: case GL_UINT32: return 4;

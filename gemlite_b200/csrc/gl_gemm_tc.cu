@@ -280,42 +280,72 @@ __global__ void __launch_bounds__(192, 1) gl_gemm_tc_kernel(const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  gl_launch_dependents();
+  if (warp >= 2) gl_grid_dependency_wait();            // the epilogue reads activation scales of, and overwrites buffers known to, the previous kernel
 
   if (warp == 0) {
     if (lane == 0) {
       uint32_t it = 0;                                   // K tiles issued so far, over all tiles of this CTA
       bool ok = true;
+      auto stage_bytes = [&](int kt, int valid_nb) {
+        uint32_t bytes = A_BYTES + B_BYTES;
+        if (MX) {
+          const int atoms = min(KT::SF_ATOMS, p.sf_kblocks - kt * KT::SF_ATOMS);
+          bytes += WIDE_A ? (uint32_t)SFA_BYTES : (uint32_t)atoms * 512u;            // wide boxes are always whole
+          bytes += WIDE_B ? (uint32_t)SFB_BYTES : (uint32_t)atoms * 512u * valid_nb;
+        }
+        return bytes;
+      };
+      auto load_a = [&](int kt, int s, int m0) {           // operand A of the kernel and its scale atoms
+        unsigned char* st = smem + s * STAGE_BYTES;
+        tma_load_2d(st, &tmA, full + s, kt * 128, m0);
+        if (MX) {
+          const int atoms = min(KT::SF_ATOMS, p.sf_kblocks - kt * KT::SF_ATOMS);
+          const size_t koff = (size_t)kt * KT::SF_ATOMS;
+          if (WIDE_A) tma_load_4d(st + A_BYTES + B_BYTES, &tmSFA, full + s, 0, 0, kt * KT::SF_ATOMS, m0 / 128);
+          else bulk_load_1d(st + A_BYTES + B_BYTES, p.sfa + ((size_t)(m0 / 128) * p.sf_kblocks + koff) * 512, (uint32_t)atoms * 512u, full + s);
+        }
+      };
+      auto load_b = [&](int kt, int s, int n0, int valid_nb) {
+        unsigned char* st = smem + s * STAGE_BYTES;
+        tma_load_2d(st + A_BYTES, &tmB, full + s, kt * 128, n0);
+        if (MX) {
+          const int atoms = min(KT::SF_ATOMS, p.sf_kblocks - kt * KT::SF_ATOMS);
+          const size_t koff = (size_t)kt * KT::SF_ATOMS;
+          if (WIDE_B) {
+#pragma unroll
+            for (int nb = 0; nb < NBLK; ++nb)
+              tma_load_4d(st + A_BYTES + B_BYTES + SFA_BYTES + nb * (SFB_BYTES / NBLK), &tmSFB, full + s, 0, 0, kt * KT::SF_ATOMS, n0 / 128 + nb);
+          } else {
+            for (int nb = 0; nb < valid_nb; ++nb)
+              bulk_load_1d(st + A_BYTES + B_BYTES + SFA_BYTES + nb * KT::SF_ATOMS * 512,
+                           p.sfb + ((size_t)(n0 / 128 + nb) * p.sf_kblocks + koff) * 512, (uint32_t)atoms * 512u, full + s);
+          }
+        }
+      };
+      // Decode sizes (operands swapped): operand A is the weights, which do not depend on the previous kernel of the
+      // stream, so the first stages' weight tiles are requested before the dependency wait and overlap that kernel's tail.
+      int pre = 0;
+      if (p.swap && (int)blockIdx.x < tiles) {
+        const int m0 = ((int)blockIdx.x % tiles_m) * 128, n0 = ((int)blockIdx.x / tiles_m) * BN;
+        const int valid_nb = min(NBLK, (p.N - n0 + 127) / 128);
+        pre = min(STAGES, p.nkt);
+        for (int kt = 0; kt < pre; ++kt) {
+          mbar_expect_tx(full + kt, stage_bytes(kt, valid_nb));
+          load_a(kt, kt, m0);
+        }
+      }
+      gl_grid_dependency_wait();
       for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
         const int m0 = (tile % tiles_m) * 128, n0 = (tile / tiles_m) * BN;
         const int valid_nb = min(NBLK, (p.N - n0 + 127) / 128);   // 128-column blocks of this tile that exist
         for (int kt = 0; kt < p.nkt; ++kt, ++it) {
           const int s = it % STAGES;
+          if ((int)it < pre) { load_b(kt, s, n0, valid_nb); continue; }      // the other half of a stage opened above
           if (!mbar_wait(empty + s, ((it / STAGES) & 1u) ^ 1u, &s_abort, p.status, 2)) { ok = false; break; }
-          unsigned char* st = smem + s * STAGE_BYTES;
-          uint32_t bytes = A_BYTES + B_BYTES;
-          int atoms = 0;
-          if (MX) {
-            atoms = min(KT::SF_ATOMS, p.sf_kblocks - kt * KT::SF_ATOMS);
-            bytes += WIDE_A ? (uint32_t)SFA_BYTES : (uint32_t)atoms * 512u;            // wide boxes are always whole
-            bytes += WIDE_B ? (uint32_t)SFB_BYTES : (uint32_t)atoms * 512u * valid_nb;
-          }
-          mbar_expect_tx(full + s, bytes);
-          tma_load_2d(st, &tmA, full + s, kt * 128, m0);
-          tma_load_2d(st + A_BYTES, &tmB, full + s, kt * 128, n0);
-          if (MX) {
-            const size_t koff = (size_t)kt * KT::SF_ATOMS;
-            if (WIDE_A) tma_load_4d(st + A_BYTES + B_BYTES, &tmSFA, full + s, 0, 0, kt * KT::SF_ATOMS, m0 / 128);
-            else bulk_load_1d(st + A_BYTES + B_BYTES, p.sfa + ((size_t)(m0 / 128) * p.sf_kblocks + koff) * 512, (uint32_t)atoms * 512u, full + s);
-            if (WIDE_B) {
-#pragma unroll
-              for (int nb = 0; nb < NBLK; ++nb)
-                tma_load_4d(st + A_BYTES + B_BYTES + SFA_BYTES + nb * (SFB_BYTES / NBLK), &tmSFB, full + s, 0, 0, kt * KT::SF_ATOMS, n0 / 128 + nb);
-            } else {
-              for (int nb = 0; nb < valid_nb; ++nb)
-                bulk_load_1d(st + A_BYTES + B_BYTES + SFA_BYTES + nb * KT::SF_ATOMS * 512,
-                             p.sfb + ((size_t)(n0 / 128 + nb) * p.sf_kblocks + koff) * 512, (uint32_t)atoms * 512u, full + s);
-            }
-          }
+          mbar_expect_tx(full + s, stage_bytes(kt, valid_nb));
+          load_a(kt, s, m0);
+          load_b(kt, s, n0, valid_nb);
         }
       }
     }
@@ -547,8 +577,10 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
   long long acc0 = 0, acc1 = 0, acc2 = 0, acc3 = 0;
 #endif
 
+  gl_launch_dependents();
   if (warp == 0) {
     if (lane == 0) {
+      gl_grid_dependency_wait();                           // x is the previous kernel's output; the packed words (warp 2) are not
       for (int j = 0; j < nstages; ++j) {
         const int s = j % STAGES, kt = kt0 + j * KT;
         const int nt = min(KT, nloc - j * KT);             // K tiles of this stage (the last one may be short)
@@ -565,37 +597,47 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
     }
   } else if (warp == 1) {
     if (lane == 0) {
+      // The issuing thread's instruction count per stage is what this loop is written for: the stage index is a
+      // compile-time constant (the loop over stages is unrolled inside a loop over ring revolutions), descriptors are
+      // the ring base's low word plus constants, and only the very first MMA has a run-time accumulate flag.
       bool ok = true;
       TC_CK(cl0);
-      for (int i = 0; i < nstages && ok; ++i) {
-        const int s = i % STAGES;
-        const uint32_t ph = (uint32_t)((i / STAGES) & 1);
-        TC_CK(c0);
-        if (!TC_WAIT(ready + s, ph, 3, acc0)) { ok = false; break; }
-        TC_CK(c1); TC_ACC(acc0, c0, c1);
-        TC_CK(c2); TC_ACC(acc1, c1, c2);
-        tc_fence_after();
-        const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
-        const uint64_t db = smem_desc_sw128(sa + A_BYTES);
-        if constexpr (SW > 0) {
-          const int nt = min(KT, nloc - i * KT);
-          for (int t = 0; t < nt; ++t) {
-            const uint64_t dx = smem_desc_sw128(sa + t * A_TILE);
+      const uint64_t d0 = smem_desc_sw128(smem_u32(smem));
+      const uint32_t d_lo = (uint32_t)d0, d_hi = (uint32_t)(d0 >> 32);
+      const uint32_t idesc = p.idesc;
+      for (int i0 = 0; i0 < nstages && ok; i0 += STAGES) {
+        const uint32_t ph = (uint32_t)((i0 / STAGES) & 1);
 #pragma unroll
-            for (int j = 0; j < 4; ++j)               // 16 k = 8 tensor-memory columns of the dequantised tile
-              mma_ts_f16(tmem_base, tmem_base + WT_COL0 + (uint32_t)((s * KT + t) * 32 + j * 8), dx + 2 * j, p.idesc, (i > 0 || t > 0 || j > 0) ? 1u : 0u);
+        for (int s = 0; s < STAGES; ++s) {
+          const int i = i0 + s;
+          if (i >= nstages) break;
+          TC_CK(c0);
+          if (!TC_WAIT(ready + s, ph, 3, acc0)) { ok = false; break; }
+          TC_CK(c1); TC_ACC(acc0, c0, c1);
+          TC_CK(c2); TC_ACC(acc1, c1, c2);
+          tc_fence_after();
+          const uint32_t st_lo = d_lo + (uint32_t)(s * STAGE_BYTES / 16);      // (the start-address field counts 16-byte units)
+          if constexpr (SW > 0) {
+#pragma unroll
+            for (int t = 0; t < KT; ++t) {
+              if (t > 0 && i * KT + t >= nloc) break;         // short last stage
+#pragma unroll
+              for (int j = 0; j < 4; ++j)                     // 16 k = 8 tensor-memory columns of the dequantised tile, 32 bytes of the x rows
+                mma_ts_f16_lohi(tmem_base, tmem_base + WT_COL0 + (uint32_t)((s * KT + t) * 32 + j * 8), st_lo + (uint32_t)(t * A_TILE / 16 + 2 * j),
+                                d_hi, idesc, (t > 0 || j > 0) ? 1u : (uint32_t)(i > 0));
+            }
+          } else {
+#pragma unroll
+            for (int am = 0; am < AM; ++am)
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                mma_ss_f16_lohi(tmem_base + am * BN, st_lo + (uint32_t)(am * A_TILE / 16 + 2 * j), st_lo + (uint32_t)(A_BYTES / 16 + 2 * j), d_hi, idesc,
+                                j > 0 ? 1u : (uint32_t)(i > 0));
           }
-        } else {
-#pragma unroll
-          for (int am = 0; am < AM; ++am) {
-            const uint64_t da = smem_desc_sw128(sa + am * A_TILE);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) mma_ss<KIND_F16>(tmem_base + am * BN, da + 2 * j, db + 2 * j, p.idesc, (i > 0 || j > 0) ? 1u : 0u);
-          }
+          TC_CK(c2b); TC_ACC(acc3, c2, c2b);
+          tc_commit(empty + s);
+          TC_CK(c3); TC_ACC(acc2, c2, c3);
         }
-        TC_CK(c2b); TC_ACC(acc3, c2, c2b);
-        tc_commit(empty + s);
-        TC_CK(c3); TC_ACC(acc2, c2, c3);
       }
       if (ok) tc_commit(tmem_full);
       TC_CK(cl1);
@@ -623,6 +665,7 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
       }
       __syncwarp();
     }
+    gl_grid_dependency_wait();
     if (mbar_wait(tmem_full, 0u, &s_abort, p.status, 4)) {
       tc_fence_after();
       if (p.splits == 1) {
@@ -803,8 +846,7 @@ static int launch_tma_kernel(const CUtensorMap& tmA, const CUtensorMap& tmB, con
   if (int rc = set_smem(kern, smem)) return rc;
   const int tiles = ((p.M + 127) / 128) * ((p.N + BN - 1) / BN);
   const int grid = tiles < gl_num_sms() ? tiles : gl_num_sms();
-  kern<<<grid, 192, smem, st>>>(tmA, tmB, tmSFA ? *tmSFA : tmA, tmSFB ? *tmSFB : tmB, p);
-  GL_LAUNCH_CHECK("gl_gemm_tc_kernel");
+  GL_CUDA_CHECK(gl_launch_pdl(kern, dim3(grid), dim3(192), smem, st, tmA, tmB, tmSFA ? *tmSFA : tmA, tmSFB ? *tmSFB : tmB, p));
   return GL_OK;
 }
 
@@ -835,13 +877,15 @@ static int launch_a16_kernel(const CUtensorMap& tmA, const CUtensorMap& tmW, con
   cfg.blockDim = dim3((6 + deq_warps(BN)) * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = (unsigned)p.splits;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;       // the packed-word ring fills while the previous kernel drains
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   GL_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, tmA, tmW, tmS, tmZ, p));
   GL_LAUNCH_CHECK("gl_gemm_tc_a16wn_kernel");
   return GL_OK;
