@@ -50,6 +50,7 @@ SIGNATURES = {
     "gl_get_matmul_type": (c_int32, [c_int32, c_int32, c_int32]),
     "gl_matmul_workspace_bytes": (c_uint64, [ctypes.POINTER(GLMatmulArgs)]),
     "gl_matmul_counter_bytes": (c_uint64, []),
+    "gl_matmul_status_offset": (c_uint64, []),
     "gl_matmul": (c_int32, [ctypes.POINTER(GLMatmulArgs), c_void_p]),
     "gl_matmul_kernel_name": (c_char_p, [ctypes.POINTER(GLMatmulArgs)]),
     "gl_matmul_noalloc": (c_int32, [ctypes.POINTER(GLMatmulArgs), c_void_p]),

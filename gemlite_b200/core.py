@@ -169,6 +169,23 @@ def _workspace(device, nbytes):
     return ws
 
 
+def matmul_status(device=None, clear: bool = True) -> int:
+    """Status word of the tensor-core kernels for the current stream's workspace on `device`: 0 after clean launches,
+    else the code of the bounded wait that gave up (the outputs of that launch are undefined).  Synchronises the
+    stream.  With `clear`, a non-zero status re-zeroes the workspace's counter block so that it can be used again."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    L = _lib.lib()
+    ws = _WORKSPACES.get((device.index, torch.cuda.current_stream(device).cuda_stream))
+    if ws is None:
+        return 0
+    torch.cuda.current_stream(device).synchronize()
+    off = int(L.gl_matmul_status_offset())
+    code = int(ws[off:off + 4].view(torch.int32).item())
+    if code != 0 and clear:
+        ws[: int(L.gl_matmul_counter_bytes())].zero_()
+    return code
+
+
 def _make_scale_atoms(scales):
     """MX / NV weight scales [N, G] as 128x4 scale atoms (the reference's 5-D pre-shuffle,
     gemlite/core.py:748-752): [N/128, G/4, 32, 4, 4] bytes.  None when the shape does not tile."""

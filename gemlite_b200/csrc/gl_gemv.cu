@@ -1063,6 +1063,7 @@ int gl_gemv_stream_supported(const gl_matmul_args* a) {
 }
 
 uint64_t gl_matmul_counter_bytes(void) { return (uint64_t)kMaxTiles * sizeof(unsigned int) + kStatusBytes; }
+extern "C" uint64_t gl_matmul_status_offset(void) { return gl_matmul_counter_bytes() - 256; }
 
 // 17 to 32 batch rows: two launches of the warp-independent kernel (rows 0..15, then the rest).  The packed weights of
 // one layer are a fraction of the 126 MB L2, so the second launch reads them from there; together they take about half

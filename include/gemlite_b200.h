@@ -147,6 +147,12 @@ GL_API int gl_get_matmul_type(int32_t M, int32_t W_nbits, int32_t is_mx_dtype);
  * (gemlite/triton_kernels/gemv_revsplitK_kernels.py:460-485). */
 GL_API uint64_t gl_matmul_workspace_bytes(const gl_matmul_args* a);
 GL_API uint64_t gl_matmul_counter_bytes(void);
+/* Byte offset, inside a workspace, of the 32-bit status word of the tensor-core kernels: 0 after a clean launch; a
+ * bounded wait that gave up leaves its code there (the launch's output is then undefined).  The library never reads
+ * it (no synchronisation): a host that wants to check copies the word after it has synchronised the stream, and after
+ * a non-zero status clears the first gl_matmul_counter_bytes() bytes before it uses the workspace again.  No
+ * counterpart in the reference (its kernels have no bounded waits). */
+GL_API uint64_t gl_matmul_status_offset(void);
 
 /* Launch on `stream`.  Replaces GEMLITE_TRITON_MAPPING[type].forward(...) + the bias add,
  * gemlite/core.py:263-272. */

@@ -24,11 +24,8 @@ def _kernel_name(layer, x):
 
 def _status_word():
     """Device status word of the workspace: non-zero when a bounded wait in a kernel gave up."""
-    from gemlite_b200 import core, _lib
-    torch.cuda.synchronize()
-    ws = core._workspace(torch.device("cuda", 0), int(_lib.lib().gl_matmul_counter_bytes()))
-    off = int(_lib.lib().gl_matmul_counter_bytes()) - 256
-    return int(ws[off:off + 4].view(torch.int32).item())
+    from gemlite_b200 import core
+    return core.matmul_status("cuda:0", clear=False)
 
 
 @pytest.mark.parametrize("nbits,gs", [(4, 128), (2, 64), (1, 128), (4, 64), (8, 128)])
