@@ -29,9 +29,6 @@ using namespace gltc;
 namespace {
 
 constexpr int kNumEpiWarps = 4;
-// dequantiser warps of the A16Wn kernel (16 for 256-column tiles measured no faster: the stage is bound by
-// shared-memory traffic, 112 KB per 128 x 256 x 64 step, not by the unpack instructions)
-constexpr int deq_warps(int) { return 8; }
 
 struct TcParams {
   int M, N, K, nkt;
@@ -507,8 +504,11 @@ __device__ __forceinline__ bool mbar_wait_counted(uint64_t* bar, uint32_t parity
 // Shared memory carries 128 bytes per clock: with both operands there, a 128 x 128 x 64 step moves 32 KB for the MMAs,
 // 16 KB of dequantised stores and 20 KB of TMA writes, which takes longer than its arithmetic.  This form moves the
 // x tile (SW x 128 bytes) in and out and the packed words, nothing else.
-template <typename XT, int NB, int BN, int STAGES, int AM = 1, int WS = STAGES, int SW = 0>
-__global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_kernel(const __grid_constant__ CUtensorMap tmA,
+// DQW: dequant warps.  4 (one per 32 channels of a 128-channel tile, 10 warps in all, at most 102 registers) lets two
+// CTAs share an SM: at decode sizes a CTA's pipeline is a chain of barrier round trips that leaves every unit of
+// the SM mostly idle, and a second, independent chain on the same SM fills the gaps.
+template <typename XT, int NB, int BN, int STAGES, int AM = 1, int WS = STAGES, int SW = 0, int DQW = 8>
+__global__ void __launch_bounds__((6 + DQW) * 32, DQW == 4 ? 2 : 1) gl_gemm_tc_a16wn_kernel(const __grid_constant__ CUtensorMap tmA,
                                                                   const __grid_constant__ CUtensorMap tmW,
                                                                   const __grid_constant__ CUtensorMap tmS,
                                                                   const __grid_constant__ CUtensorMap tmZ, const TcParams p) {
@@ -698,7 +698,8 @@ __global__ void __launch_bounds__((6 + deq_warps(BN)) * 32, 1) gl_gemm_tc_a16wn_
     constexpr int CBLOCKS = BN / 32;                       // 32-column blocks in the tile
     // With more warps than column blocks (BN = 128) the warps form groups that take the K tiles in turn: the chain of a
     // tile (wait, read, unpack, store, fence, arrive) is mostly latency, and two tiles in flight hide it.
-    constexpr int TSPLIT = deq_warps(BN) / CBLOCKS;        // warp groups (1 or 2)
+    constexpr int TSPLIT = DQW / CBLOCKS;                  // warp groups (1 or 2)
+    static_assert(DQW % CBLOCKS == 0 && TSPLIT >= 1, "dequant warps: a multiple of the 32-column blocks");
     constexpr int RPW = WROWS;                             // packed rows per warp: the whole K tile of its 32 columns
     // (swapped: the warp writes the lane quadrant of tensor memory it may access, so its 32 channels are that quadrant's)
     const int nl = (SW ? (warp & 3) : (dw % CBLOCKS)) * 32 + lane;             // column (channel) inside the tile
@@ -851,22 +852,22 @@ static int launch_tma_kernel(const CUtensorMap& tmA, const CUtensorMap& tmB, con
 }
 
 // slots of the packed-word ring: what is left of the 227 KB after the activation / dequantised-tile stages, at most 16
-constexpr int a16_wslots(int NB, int BN, int STAGES, int AM, int SW = 0) {
+constexpr int a16_wslots(int NB, int BN, int STAGES, int AM, int SW = 0, int ctas_per_sm = 1) {
   const int wslot = a16_wslot_bytes(NB, BN);
-  const int left = 232448 - 1024 - STAGES * (SW ? 2 * SW * 128 : AM * 128 * 128 + BN * 128) - 4096;
+  const int left = (ctas_per_sm == 2 ? 113 * 1024 : 232448) - 1024 - STAGES * (SW ? 2 * SW * 128 : AM * 128 * 128 + BN * 128) - 4096;
   return left / wslot > 16 ? 16 : left / wslot;
 }
 
-template <typename XT, int NB, int BN, int STAGES, int AM = 1, int SW = 0>
+template <typename XT, int NB, int BN, int STAGES, int AM = 1, int SW = 0, int DQW = 8>
 static int launch_a16_kernel(const CUtensorMap& tmA, const CUtensorMap& tmW, const CUtensorMap& tmS, const CUtensorMap& tmZ, const TcParams& p,
                              cudaStream_t st) {
   constexpr int WROWS = 64 / (32 / NB);
-  constexpr int WS = a16_wslots(NB, BN, STAGES, AM, SW);
+  constexpr int WS = a16_wslots(NB, BN, STAGES, AM, SW, DQW == 4 ? 2 : 1);
   static_assert(WS >= 2, "packed-word ring needs two slots");
   constexpr size_t stage = SW ? 2 * SW * 128 : AM * 128 * 128 + BN * 128, wslot = a16_wslot_bytes(NB, BN);   // (swapped: two x tiles per stage)
   constexpr size_t smem = 1024 + STAGES * stage + WS * wslot + (3 * STAGES + 2 * WS + 1) * 8 + 32 + 2 * BN * 4 + 16;
-  static_assert(smem <= 232448, "shared memory of the A16Wn kernel");
-  auto kern = gl_gemm_tc_a16wn_kernel<XT, NB, BN, STAGES, AM, WS, SW>;
+  static_assert(smem <= (DQW == 4 ? 113 * 1024 : 232448), "shared memory of the A16Wn kernel");
+  auto kern = gl_gemm_tc_a16wn_kernel<XT, NB, BN, STAGES, AM, WS, SW, DQW>;
   if (int rc = set_smem(kern, smem)) return rc;
   const int tiles = (SW ? 1 : (p.M + 128 * AM - 1) / (128 * AM)) * ((p.N + BN - 1) / BN);
   // K splits: the CTAs of a tile are one cluster along y and add their partial tiles through distributed shared memory
@@ -874,7 +875,7 @@ static int launch_a16_kernel(const CUtensorMap& tmA, const CUtensorMap& tmW, con
     GL_FAIL(GL_E_INVALID, "gl_matmul: %d K splits of a %d x %d tile do not fit the cluster reduction", p.splits, AM * 128, BN);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(tiles, p.splits);
-  cfg.blockDim = dim3((6 + deq_warps(BN)) * 32);
+  cfg.blockDim = dim3((6 + DQW) * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   cudaLaunchAttribute attr[2];
@@ -963,7 +964,7 @@ static int tc_tile_n(const gl_matmul_args* a) {
 // 256-column tiles when that still gives 96 CTAs; when the tiles alone leave more than half of the SMs idle, the K range
 // is divided so that about one CTA per SM runs (every split gets at least 8 K tiles and none is empty).
 // Cache entry fields "tile_n", "am", "splits" override the three choices.
-struct A16Plan { int BN, AM, splits, SW; };
+struct A16Plan { int BN, AM, splits, SW, ctas; };
 static A16Plan a16_plan(const gl_matmul_args* a) {
   A16Plan pl;
   // at most 64 rows: operands swapped, the rows of x are the MMA's 32 or 64 columns ("swap": 0 in the cache entry turns it off)
@@ -974,6 +975,8 @@ static A16Plan a16_plan(const gl_matmul_args* a) {
   pl.BN = (a->N >= 256 && tiles_m * ((a->N + 255) / 256) >= 96) ? 256 : 128;
   if ((req_bn == 128 || req_bn == 256) && a->N >= req_bn) pl.BN = req_bn;
   if (pl.SW) pl.BN = 128;
+  // swapped form: two CTAs per SM (4 dequant warps each) unless the cache entry says "ctas": 1
+  pl.ctas = (pl.SW && tc_cfg_int(a, "ctas", 2) == 2) ? 2 : 1;
   const int64_t tiles = tiles_m * ((a->N + pl.BN - 1) / pl.BN);
   const int nkt = (a->K + 63) / 64, sms = gl_num_sms();
   pl.splits = 1;
@@ -982,8 +985,8 @@ static A16Plan a16_plan(const gl_matmul_args* a) {
   auto trim = [&](int s) { while (s > 1 && (s - 1) * ((nkt + s - 1) / s) >= nkt) --s; return s; };
   const int req = tc_cfg_int(a, "splits", 0);
   if (req >= 1 && req <= 8 && req <= nkt / 8) { pl.splits = trim(req); return pl; }
-  if (tiles * 2 > sms) return pl;
-  int s = (int)(sms / tiles);
+  if (tiles * 2 > sms * pl.ctas) return pl;
+  int s = (int)(sms * pl.ctas / tiles);
   if (s > 8) s = 8;
   if (s > nkt / 8) s = nkt / 8;
   if (s < 1) s = 1;
@@ -1009,7 +1012,7 @@ int gl_gemm_tc_launch(const gl_matmul_args* a, cudaStream_t st) {
   p.out = a->out; p.out_dtype = a->out_dtype; p.bias = a->bias;
   p.status = reinterpret_cast<int*>(reinterpret_cast<char*>(a->workspace) + gl_matmul_counter_bytes() - 256);
   p.meta_scale = nullptr;
-  const A16Plan a16 = path == TC_A16WN ? a16_plan(a) : A16Plan{0, 1, 1, 0};
+  const A16Plan a16 = path == TC_A16WN ? a16_plan(a) : A16Plan{0, 1, 1, 0, 1};
   const int BN = path == TC_A16WN ? a16.BN : tc_tile_n(a);
   // decode sizes of the TMA formats swap the operands (16 or 32 token columns)
   const int swap_bn = (path != TC_A16WN && a->M <= 32 && a->N >= 128) ? (a->M <= 16 ? 16 : 32) : 0;
@@ -1037,7 +1040,8 @@ int gl_gemm_tc_launch(const gl_matmul_args* a, cudaStream_t st) {
 #ifndef GL_SW_STAGES
 #define GL_SW_STAGES 4      // stages of the x / tensor-memory ring of the swapped form
 #endif
-#define GL_A16_SW(XT, NB) (a16.SW == 32 ? launch_a16_kernel<XT, NB, 128, GL_SW_STAGES, 1, 32>(tmA, tmB, tmS, tmZ, p, st) : launch_a16_kernel<XT, NB, 128, GL_SW_STAGES, 1, 64>(tmA, tmB, tmS, tmZ, p, st))
+#define GL_A16_SW(XT, NB) (a16.ctas == 2 ? (a16.SW == 32 ? launch_a16_kernel<XT, NB, 128, 2, 1, 32, 4>(tmA, tmB, tmS, tmZ, p, st) : launch_a16_kernel<XT, NB, 128, 2, 1, 64, 4>(tmA, tmB, tmS, tmZ, p, st)) \
+                                         : (a16.SW == 32 ? launch_a16_kernel<XT, NB, 128, GL_SW_STAGES, 1, 32>(tmA, tmB, tmS, tmZ, p, st) : launch_a16_kernel<XT, NB, 128, GL_SW_STAGES, 1, 64>(tmA, tmB, tmS, tmZ, p, st)))
       if (a->x_dtype == GL_BF16) {
         if (a->W_nbits == 8) return GL_A16_SW(__nv_bfloat16, 8);
         if (a->W_nbits == 4) return GL_A16_SW(__nv_bfloat16, 4);
