@@ -27,7 +27,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 DEFAULT_SHAPES = [(8192, 8192, 4, 128), (8192, 8192, 2, 64)] + [
     s for tp in (1, 2, 4, 8) for s in (((64 + 16) * 128 // tp, 8192, 4, 128), (8192, 8192 // tp, 4, 128),
                                       (2 * 28672 // tp, 8192, 4, 128), (8192, 28672 // tp, 4, 128))]
-CANDIDATES = [(8, 1, 1), (4, 1, 1), (4, 2, 1), (2, 4, 1), (4, 2, 2), (2, 4, 4), (2, 2, 4), (1, 8, 8), (1, 8, 4), (1, 4, 8), (4, 1, 2), (2, 4, 2)]
+# (K slices per CTA, 32-column groups per CTA, CTAs per cluster along K): every shape of at most 16 warps; the planner
+# rejects the ones a problem cannot use (slice length, shared memory)
+CANDIDATES = [(s, c, cl) for s in (1, 2, 4, 8, 16) for c in (1, 2, 4, 8) for cl in (1, 2, 4, 8) if s * c <= 16]
 
 
 def gpu_tag(device=0):
