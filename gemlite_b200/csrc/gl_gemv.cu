@@ -827,39 +827,45 @@ static bool plan_warp_with(const gl_matmul_args* a, GemvPlan* pl, const char* js
   }
   while (c_in > 1 && colgroups % c_in != 0) c_in >>= 1;
   if (c_in < 1 || c_in > 16 || colgroups % c_in != 0) return false;
+  // staged activations + per-warp group constants + partial sums of a CTA of s slices x c column groups, nit iterations per slice
+  auto smem_of = [&](int s, int c, int nit) {
+    const int nseg = (nit + gi - 1) / gi;
+    const size_t x_bytes = a->W_nbits == 8 ? (size_t)nit * a->M * 32 : (size_t)nit * H * a->M * 64;
+    return (size_t)s * x_bytes + (size_t)s * c * (nseg * 32 * 12 + 16) + (size_t)s * a->M * c * 32 * 4 + 16;
+  };
   if (s_in <= 0 || cluster <= 0) {
     // slices: fewest "waves x (iterations per warp + fixed per-warp cost)" over every split into equal slices that fit
-    // (K = 3584 has 112 iterations: 7 slices of 16 fill the machine where the power-of-two choice, 2 of 56, cannot)
+    // the CTA shape rules and the shared-memory budget
+    // (K = 3584 has 112 iterations: 7 slices of 16 fill the machine where the power-of-two choice, 2 of 56, cannot;
+    //  a very wide layer must not fall back to one whole-K slice per CTA whose staged activations do not fit)
     const int64_t warp_slots = (int64_t)gl_num_sms() * 16;
     const int max_warps = a->M <= 8 ? 16 : 8;
+    // CTA shape for S slices: prefer CTAs of at most 8 warps (two per SM), then up to max_warps
+    auto shape_of = [&](int S, int* s_out, int* cl_out) {
+      for (int lim = 8; lim <= max_warps; lim <<= 1)
+        for (int cl = 1; cl <= 8; cl <<= 1)
+          if (S % cl == 0 && (S / cl) * c_in <= lim && (32 * c_in) % cl == 0 && (c_in == 1 || S / cl <= 15) &&
+              smem_of(S / cl, c_in, T / S) <= smem_limit) { *s_out = S / cl; *cl_out = cl; return true; }
+      return false;
+    };
     int S = 0;
     int64_t best_cost = 0;
     for (int cand = 1; cand <= 64; ++cand) {
       if (!slice_ok(cand)) continue;
-      // cand = s_in x cluster with a power-of-two cluster of at most 8 and a CTA of at most max_warps warps
-      bool fits = false;
-      for (int cl = 1; cl <= 8; cl <<= 1)
-        if (cand % cl == 0 && (cand / cl) * c_in <= max_warps && (32 * c_in) % cl == 0) { fits = true; break; }
-      if (!fits) continue;
+      int s_c, cl_c;
+      if (!shape_of(cand, &s_c, &cl_c)) continue;
       const int64_t waves = ((int64_t)colgroups * cand + warp_slots - 1) / warp_slots;
       const int64_t cost = waves * (T / cand + 12);
       if (S == 0 || cost < best_cost) { S = cand; best_cost = cost; }
     }
     if (S == 0) return false;
-    // prefer CTAs of at most 8 warps (two per SM), then up to max_warps
-    s_in = 0;
-    for (int lim = 8; lim <= max_warps && s_in == 0; lim <<= 1)
-      for (int cl = 1; cl <= 8; cl <<= 1)
-        if (S % cl == 0 && (S / cl) * c_in <= lim && (32 * c_in) % cl == 0) { cluster = cl; s_in = S / cl; break; }
-    if (s_in == 0) return false;
+    if (!shape_of(S, &s_in, &cluster)) return false;
   }
   if (cluster < 1 || cluster > 8 || (cluster & (cluster - 1)) != 0 || s_in < 1 || s_in * c_in > (a->M <= 8 ? 16 : 8)) return false;
   if (c_in > 1 && s_in > 15) return false;                          // one named barrier per slice
   if (!slice_ok(s_in * cluster) || (32 * c_in) % cluster != 0) return false;
   const int nit = T / (s_in * cluster), nseg = (nit + gi - 1) / gi;
-  const size_t x_bytes = a->W_nbits == 8 ? (size_t)nit * a->M * 32 : (size_t)nit * H * a->M * 64;   // staged activations per slice
-  const size_t smem = (size_t)s_in * x_bytes + (size_t)s_in * c_in * (nseg * 32 * 12 + 16) +
-                      (size_t)s_in * a->M * c_in * 32 * 4 + 16;
+  const size_t smem = smem_of(s_in, c_in, nit);
   if (smem > smem_limit) return false;
   pl->warp_kernel = 1; pl->gi = gi; pl->s_in = s_in; pl->c_in = c_in; pl->cluster = cluster; pl->splitK = cluster;
   pl->MT = a->M <= 8 ? 1 : 2;
@@ -879,6 +885,9 @@ static bool plan_warp(const gl_matmul_args* a, GemvPlan* pl, const char* js) {
   for (int b = 0; b < 2; ++b)
     for (int c = first; c <= 8; c <<= 1)
       if (plan_warp_with(a, pl, js, c, budgets[b])) return true;
+  // long K with many batch rows: narrower CTAs (more K slices per CTA, fewer column groups) keep the staged activations in budget
+  for (int c = first >> 1; c >= 1; c >>= 1)
+    if (plan_warp_with(a, pl, js, c, budgets[1])) return true;
   return false;
 }
 

@@ -97,7 +97,7 @@ def tune(shapes=DEFAULT_SHAPES, Ms=(1, 2, 4, 8, 16), device="cuda:0", verbose=Tr
             L.gl_cfg_set(b"GEMV_REVSPLITK", sig.encode(), b"{}")
             base_us, name = _time_layers(layers, x, stream)
             best = (base_us, None)
-            if name == "gl_gemv_warp_kernel":
+            if name in ("gl_gemv_warp_kernel", "gl_gemv_stream_kernel"):
                 for (s_in, c_in, cl) in CANDIDATES:
                     entry = {"s_in": s_in, "c_in": c_in, "cluster_k": cl}
                     L.gl_cfg_set(b"GEMV_REVSPLITK", sig.encode(), json.dumps(entry).encode())
