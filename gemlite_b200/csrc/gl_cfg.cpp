@@ -12,6 +12,7 @@
 #include <stdio.h>
 #include <string.h>
 #include <map>
+#include <atomic>
 #include <mutex>
 #include <string>
 #include <stdlib.h>
@@ -169,6 +170,7 @@ std::string dump(const Cache& c) {
 }
 
 const char* kFamilies[5] = {"GEMV", "GEMV_REVSPLITK", "GEMV_SPLITK", "GEMM_SPLITK", "GEMM"};
+std::atomic<uint64_t> g_generation{1};          // bumped by every change of the cache: planners memoise against it
 
 }  // namespace
 
@@ -181,6 +183,7 @@ extern "C" int gl_cfg_load(const char* filename, int32_t overwrite) {
   if (!parse_cache(text, &parsed)) { gl_set_error("Failed to load the cache file '%s': not a {family: {signature: config}} JSON object", filename); return GL_E_IO; }
   if (overwrite) g_cache.swap(parsed);
   else for (auto& fam : parsed) { SigMap& dst = g_cache[fam.first]; for (auto& e : fam.second) dst[e.first] = e.second; }
+  g_generation.fetch_add(1);
   return GL_OK;
 }
 
@@ -204,6 +207,7 @@ extern "C" int gl_cfg_save(const char* filename) {
 extern "C" void gl_cfg_reset(void) {
   std::lock_guard<std::mutex> lk(g_mu);
   g_cache.clear();
+  g_generation.fetch_add(1);
 }
 
 extern "C" int gl_cfg_set(const char* family, const char* signature, const char* json_object) {
@@ -217,6 +221,7 @@ extern "C" int gl_cfg_set(const char* family, const char* signature, const char*
   if (p.i != p.n) { gl_set_error("gl_cfg_set: trailing characters after the JSON value"); return GL_E_INVALID; }
   std::lock_guard<std::mutex> lk(g_mu);
   g_cache[family][signature] = std::string(json_object + a, b - a);
+  g_generation.fetch_add(1);
   return GL_OK;
 }
 
@@ -247,6 +252,8 @@ int gl_cfg_int(const char* family, const char* signature, const char* key, int d
   if (pos == std::string::npos) return dflt;
   return atoi(e->second.c_str() + pos + 1);
 }
+
+uint64_t gl_cfg_generation() { return g_generation.load(); }
 
 extern "C" int64_t gl_cfg_size(const char* family) {
   std::lock_guard<std::mutex> lk(g_mu);

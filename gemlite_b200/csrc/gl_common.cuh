@@ -55,6 +55,7 @@ static inline int64_t gl_cdiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
 // number of SMs of the current device (cached per device id)
 int gl_num_sms();
 // integer field of a tile-config cache entry, or dflt (gl_cfg.cpp)
+uint64_t gl_cfg_generation();   // changes whenever the config cache changes
 int gl_cfg_int(const char* family, const char* signature, const char* key, int dflt);
 
 // ---- family launchers (each returns GL_OK / GL_E_*; GL_E_UNSUPPORTED = "not my case") -----

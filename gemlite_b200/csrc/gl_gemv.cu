@@ -891,7 +891,27 @@ static bool plan_warp(const gl_matmul_args* a, GemvPlan* pl, const char* js) {
   return false;
 }
 
+static void plan_for_uncached(const gl_matmul_args* a, GemvPlan* pl, bool force_workspace);
+
+// The plan depends on the problem's shape and modes and on the config cache only; an eager forward asks for it two or
+// three times per layer (workspace size, kernel choice, launch), so the last few are kept per thread.
 static void plan_for(const gl_matmul_args* a, GemvPlan* pl, bool force_workspace = false) {
+  struct Key { int M, N, K, gs, e, nbits, idt, force, dev; uint64_t gen; };
+  struct Slot { Key k; GemvPlan pl; bool used; };
+  static thread_local Slot slots[8] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); dev = 0; }
+  const Key k = {a->M, a->N, a->K, a->group_size, a->elements_per_sample, a->W_nbits, a->input_dtype, force_workspace ? 1 : 0, dev, gl_cfg_generation()};
+  const unsigned h = ((unsigned)k.M * 31u + (unsigned)k.N * 7u + (unsigned)k.K + (unsigned)k.nbits * 3u + (unsigned)k.force) & 7u;
+  Slot& sl = slots[h];
+  const Key& c = sl.k;
+  if (sl.used && c.M == k.M && c.N == k.N && c.K == k.K && c.gs == k.gs && c.e == k.e && c.nbits == k.nbits && c.idt == k.idt &&
+      c.force == k.force && c.dev == k.dev && c.gen == k.gen) { *pl = sl.pl; return; }
+  plan_for_uncached(a, pl, force_workspace);
+  sl.k = k; sl.pl = *pl; sl.used = true;
+}
+
+static void plan_for_uncached(const gl_matmul_args* a, GemvPlan* pl, bool force_workspace) {
   const int e = a->elements_per_sample;
   const int T = a->K / (4 * e);
   pl->MT = a->M <= 8 ? 1 : (a->M <= 16 ? 2 : 4);
