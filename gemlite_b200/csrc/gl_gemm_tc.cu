@@ -448,6 +448,13 @@ template <> struct H2<__half> {
 // AM: 128-row activation tiles per CTA (1 or 2).  The kernel is bound by the dequantisation of the weight tile (unpack,
 // HFMA2, swizzled stores: the same work whatever the batch), so with AM = 2 one dequantised tile feeds two 128-row
 // accumulators (2 x BN TMEM columns): half the dequantisation per flop and half the re-reads of the packed weights.
+// K tiles per stage of the A16Wn kernel: the swapped form groups them (fewer barrier round trips, commits and waits per
+// tile for the single MMA-issuing thread): 2 with two CTAs per SM, GL_SW_KT with one
+#ifndef GL_SW_KT
+#define GL_SW_KT 2
+#endif
+constexpr int a16_tiles_per_stage(int SW, int DQW) { return SW ? (DQW == 8 ? GL_SW_KT : 2) : 1; }
+
 // bytes of a slot of the A16Wn kernel's packed-word ring: the packed words of a 64-deep K tile, a row of scales and a row of zeros
 constexpr int a16_wslot_bytes(int NB, int BN) { return ((64 / (32 / NB) * BN * 4 + 2 * BN * 2 + 255) / 256) * 256; }
 
@@ -518,7 +525,7 @@ __global__ void __launch_bounds__((6 + DQW) * 32, DQW == 4 ? 2 : 1) gl_gemm_tc_a
   constexpr int A_TILE = (SW ? SW : 128) * 128;        // rows of x per tile x 64 k x 2 bytes
   // K tiles per stage: the swapped form pairs them, which halves the barrier round trips, commits and waits per tile
   // (its stage is small: KT x tiles and KT x 32 tensor-memory columns)
-  constexpr int KT = SW ? 2 : 1;
+  constexpr int KT = a16_tiles_per_stage(SW, DQW);
   constexpr int A_BYTES = KT * AM * A_TILE, B_BYTES = SW ? 0 : BN * 128, W_BYTES = WROWS * BN * 4;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr uint32_t WT_COL0 = SW;                     // swapped: dequantised tiles of the STAGES slots follow the accumulator
@@ -854,7 +861,8 @@ static int launch_tma_kernel(const CUtensorMap& tmA, const CUtensorMap& tmB, con
 // slots of the packed-word ring: what is left of the 227 KB after the activation / dequantised-tile stages, at most 16
 constexpr int a16_wslots(int NB, int BN, int STAGES, int AM, int SW = 0, int ctas_per_sm = 1) {
   const int wslot = a16_wslot_bytes(NB, BN);
-  const int left = (ctas_per_sm == 2 ? 113 * 1024 : 232448) - 1024 - STAGES * (SW ? 2 * SW * 128 : AM * 128 * 128 + BN * 128) - 4096;
+  const int left = (ctas_per_sm == 2 ? 113 * 1024 : 232448) - 1024 -
+                   STAGES * (SW ? a16_tiles_per_stage(SW, ctas_per_sm == 2 ? 4 : 8) * SW * 128 : AM * 128 * 128 + BN * 128) - 4096;
   return left / wslot > 16 ? 16 : left / wslot;
 }
 
@@ -864,7 +872,7 @@ static int launch_a16_kernel(const CUtensorMap& tmA, const CUtensorMap& tmW, con
   constexpr int WROWS = 64 / (32 / NB);
   constexpr int WS = a16_wslots(NB, BN, STAGES, AM, SW, DQW == 4 ? 2 : 1);
   static_assert(WS >= 2, "packed-word ring needs two slots");
-  constexpr size_t stage = SW ? 2 * SW * 128 : AM * 128 * 128 + BN * 128, wslot = a16_wslot_bytes(NB, BN);   // (swapped: two x tiles per stage)
+  constexpr size_t stage = SW ? a16_tiles_per_stage(SW, DQW) * SW * 128 : AM * 128 * 128 + BN * 128, wslot = a16_wslot_bytes(NB, BN);
   constexpr size_t smem = 1024 + STAGES * stage + WS * wslot + (3 * STAGES + 2 * WS + 1) * 8 + 32 + 2 * BN * 4 + 16;
   static_assert(smem <= (DQW == 4 ? 113 * 1024 : 232448), "shared memory of the A16Wn kernel");
   auto kern = gl_gemm_tc_a16wn_kernel<XT, NB, BN, STAGES, AM, WS, SW, DQW>;
@@ -1088,8 +1096,11 @@ int gl_gemm_tc_launch(const gl_matmul_args* a, cudaStream_t st) {
       p.idesc = (path == TC_FP8) ? gl_idesc(1, 0, 0, 128, swap_bn) : gl_idesc(2, 1, 1, 128, swap_bn);
       if (int rc = gl_make_tmap_2d(&tmA, a->w, 0, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)a->K, 128, 128, true)) return rc;
       if (int rc = gl_make_tmap_2d(&tmB, a->x, 0, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->K, 128, (uint32_t)swap_bn, true)) return rc;
-      if (path == TC_FP8) return swap_bn == 16 ? launch_tma_kernel<KIND_F8F6F4, 16, 8>(tmA, tmB, p, st) : launch_tma_kernel<KIND_F8F6F4, 32, 8>(tmA, tmB, p, st);
-      return swap_bn == 16 ? launch_tma_kernel<KIND_I8, 16, 8>(tmA, tmB, p, st) : launch_tma_kernel<KIND_I8, 32, 8>(tmA, tmB, p, st);
+#ifndef GL_SWAP_STAGES
+#define GL_SWAP_STAGES 8     // ring depth of the swapped (decode) form: 8 x 18 KB
+#endif
+      if (path == TC_FP8) return swap_bn == 16 ? launch_tma_kernel<KIND_F8F6F4, 16, GL_SWAP_STAGES>(tmA, tmB, p, st) : launch_tma_kernel<KIND_F8F6F4, 32, GL_SWAP_STAGES>(tmA, tmB, p, st);
+      return swap_bn == 16 ? launch_tma_kernel<KIND_I8, 16, GL_SWAP_STAGES>(tmA, tmB, p, st) : launch_tma_kernel<KIND_I8, 32, GL_SWAP_STAGES>(tmA, tmB, p, st);
     }
     if (int rc = gl_make_tmap_2d(&tmA, a->x, 0, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->K, 128, 128, true)) return rc;
     if (int rc = gl_make_tmap_2d(&tmB, a->w, 0, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)a->K, 128, (uint32_t)BN, true)) return rc;
