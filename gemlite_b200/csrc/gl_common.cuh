@@ -65,6 +65,9 @@ const char* gl_gemv_stream_kernel_name(const gl_matmul_args* a);
 int gl_gemv_stream_launch(const gl_matmul_args* a, cudaStream_t st);
 int gl_gemv_split_rows_ok(const gl_matmul_args* a);   // 17..32 rows served by two launches of the warp-independent kernel
 int gl_generic_launch(const gl_matmul_args* a, cudaStream_t st);
+// weight-only 8-bit layers (unpacked INT8 / FP8 weights, one scale per channel) at decode sizes (gl_w8.cu)
+bool gl_w8_gemv_supported(const gl_matmul_args* a);
+int gl_w8_gemv_launch(const gl_matmul_args* a, cudaStream_t st);
 int gl_validate_matmul_args(const gl_matmul_args* a);
 int gl_gemm_tc_supported(const gl_matmul_args* a);
 uint64_t gl_gemm_tc_workspace(const gl_matmul_args* a);

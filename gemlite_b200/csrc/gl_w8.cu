@@ -1,0 +1,174 @@
+// Decode-size kernel for weight-only 8-bit layers: fp16 / bf16 activations, INT8 or FP8 (e4m3) weights stored
+// unpacked [N, K] with K contiguous, one scale per output channel (the reference's A16W8 processors,
+// gemlite/helper.py:89-171: W_group_mode 2 with one group = K, or channel_scale_mode 1; its kernels for them are the
+// GEMV / GEMM families of gemlite/triton_kernels with W_nbits = 8, elements_per_sample = 1).
+//
+// HBM-bound: N * K weight bytes are read once.  A warp owns four output channels; a lane reads 16 weight bytes of each
+// per step (a warp instruction covers 512 contiguous bytes of a row), keeps two steps in flight (4 KB per warp), and
+// multiplies them with activations that were staged in shared memory as fp32 in the order the lanes consume them
+// (conflict-free 16-byte reads).  INT8 weights become fp32 with a PRMT and an FADD each (0x4B0000bb = 2^23 + b for the
+// biased byte b = w ^ 0x80, minus 2^23 + 128: exact); FP8 weights go through cvt.f16x2.e4m3x2.  fp32 accumulation, the channel scale and the bias are applied to the finished sum:
+// out = scale[n] * sum_k x[m,k] * w[n,k] + bias[n]  (for W_group_mode 2 the reference rounds w * scale to the
+// activation dtype per element first; the difference is below the output rounding).
+#include "gl_common.cuh"
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+
+namespace {
+
+constexpr int kWarps = 8;             // warps per CTA
+constexpr int kRows = 4;              // output channels per warp
+constexpr int kMaxM = 4;
+constexpr size_t kSmemLimit = 200 * 1024;
+
+struct W8Params {
+  const void* x; const uint8_t* w; const void* scales; const void* bias; void* out;
+  int M, N, K, x_dtype, out_dtype, scales_dtype, is_fp8, has_scale;
+};
+
+__device__ __forceinline__ float x_as_float(const void* x, int64_t i, int dt) {
+  return dt == GL_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(x)[i]) : __half2float(reinterpret_cast<const __half*>(x)[i]);
+}
+
+template <int MM, bool FP8>
+__global__ void __launch_bounds__(kWarps * 32) gl_w8_gemv_kernel(const W8Params p) {
+  extern __shared__ float xs[];                       // [MM][steps][4][32] float4-interleaved activations
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int units = p.K / 16;                         // 16-byte units per weight row
+  const int steps = (units + 31) / 32;
+  const int n0 = (blockIdx.x * kWarps + warp) * kRows;
+  const uint4* wrow[kRows];
+#pragma unroll
+  for (int r = 0; r < kRows; ++r) wrow[r] = reinterpret_cast<const uint4*>(p.w + (size_t)min(n0 + r, p.N - 1) * p.K);
+  // the first two steps of weights are requested before the dependency wait: they do not depend on the previous kernel
+  uint4 buf[2][kRows];
+#pragma unroll
+  for (int s = 0; s < 2; ++s)
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) {
+      const int u = s * 32 + lane;
+      buf[s][r] = (s < steps && u < units) ? __ldg(wrow[r] + u) : make_uint4(0u, 0u, 0u, 0u);
+    }
+  gl_launch_dependents();
+  gl_grid_dependency_wait();
+  // stage x: unit u = 32 * i + l holds k = 16 u .. 16 u + 15; its four float4 go to xs[m][i][j][l]
+  for (int m = 0; m < MM; ++m) {
+    for (int idx = threadIdx.x; idx < steps * 128; idx += blockDim.x) {        // one float4 per index
+      const int i = idx >> 7, j = (idx >> 5) & 3, l = idx & 31;
+      const int k = 16 * (32 * i + l) + 4 * j;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (k < p.K) {
+        const int64_t o = (int64_t)m * p.K + k;
+        v = make_float4(x_as_float(p.x, o, p.x_dtype), x_as_float(p.x, o + 1, p.x_dtype), x_as_float(p.x, o + 2, p.x_dtype), x_as_float(p.x, o + 3, p.x_dtype));
+      }
+      reinterpret_cast<float4*>(xs)[(size_t)m * steps * 128 + idx] = v;
+    }
+  }
+  __syncthreads();
+  float acc[kRows][MM];
+#pragma unroll
+  for (int r = 0; r < kRows; ++r)
+#pragma unroll
+    for (int m = 0; m < MM; ++m) acc[r][m] = 0.f;
+  // one step: consume the 16 bytes per row held in `b`, then refill `b` with step i + 2
+  auto step = [&](int i, uint4 (&b)[kRows]) {
+    uint4 wv[kRows];
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) wv[r] = b[r];
+    {
+      const int u = (i + 2) * 32 + lane;
+#pragma unroll
+      for (int r = 0; r < kRows; ++r) b[r] = (i + 2 < steps && u < units) ? __ldg(wrow[r] + u) : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float4 xv[MM];
+#pragma unroll
+      for (int m = 0; m < MM; ++m) xv[m] = reinterpret_cast<const float4*>(xs)[((size_t)m * steps + i) * 128 + j * 32 + lane];
+#pragma unroll
+      for (int r = 0; r < kRows; ++r) {
+        const uint32_t w4 = j == 0 ? wv[r].x : j == 1 ? wv[r].y : j == 2 ? wv[r].z : wv[r].w;
+        float f0, f1, f2, f3;
+        if (FP8) {
+          const __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w4 & 0xFFFFu), __NV_E4M3);
+          const __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w4 >> 16), __NV_E4M3);
+          const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&lo)), c = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+          f0 = a.x; f1 = a.y; f2 = c.x; f3 = c.y;
+        } else {
+          const uint32_t u4 = w4 ^ 0x80808080u;        // signed byte -> byte + 128
+          f0 = __uint_as_float(__byte_perm(u4, 0x4B000000u, 0x7540)) - 8388736.f;      // (2^23 + 128 + w) - (2^23 + 128)
+          f1 = __uint_as_float(__byte_perm(u4, 0x4B000000u, 0x7541)) - 8388736.f;
+          f2 = __uint_as_float(__byte_perm(u4, 0x4B000000u, 0x7542)) - 8388736.f;
+          f3 = __uint_as_float(__byte_perm(u4, 0x4B000000u, 0x7543)) - 8388736.f;
+        }
+#pragma unroll
+        for (int m = 0; m < MM; ++m)
+          acc[r][m] = fmaf(xv[m].x, f0, fmaf(xv[m].y, f1, fmaf(xv[m].z, f2, fmaf(xv[m].w, f3, acc[r][m]))));
+      }
+    }
+  };
+  for (int i = 0; i < steps; i += 2) {
+    step(i, buf[0]);
+    if (i + 1 < steps) step(i + 1, buf[1]);
+  }
+#pragma unroll
+  for (int r = 0; r < kRows; ++r)
+#pragma unroll
+    for (int m = 0; m < MM; ++m) {
+      float v = acc[r][m];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      acc[r][m] = v;
+    }
+  if (lane == 0) {
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) {
+      const int n = n0 + r;
+      if (n >= p.N) break;
+      const float sc = p.has_scale ? gl_load_as_float(p.scales, n, p.scales_dtype) : 1.f;
+      const float bi = p.bias != nullptr ? gl_load_as_float(p.bias, n, p.out_dtype) : 0.f;
+#pragma unroll
+      for (int m = 0; m < MM; ++m) {
+        gl_store_out(p.out, (int64_t)m * p.N + n, fmaf(acc[r][m], sc, bi), p.out_dtype);
+      }
+    }
+  }
+}
+
+size_t smem_bytes(int M, int K) { return (size_t)M * ((K / 16 + 31) / 32) * 512 * sizeof(float); }
+
+}  // namespace
+
+bool gl_w8_gemv_supported(const gl_matmul_args* a) {
+  if (a->M < 1 || a->M > kMaxM || a->W_nbits != 8 || a->elements_per_sample != 1) return false;
+  if (!(a->w_dtype == GL_INT8 || a->w_dtype == GL_FP8)) return false;
+  if (!(a->x_dtype == GL_FP16 || a->x_dtype == GL_BF16) || a->input_dtype != a->x_dtype) return false;
+  if (a->w_stride_k != 1 || a->w_stride_n != a->K || a->K % 16 != 0 || ((uintptr_t)a->w & 15)) return false;
+  const bool pre = a->W_group_mode == 2 && a->channel_scale_mode == 0 && a->group_size == a->K;   // one scale per channel, applied to the weights
+  const bool post = a->W_group_mode == 0 && a->channel_scale_mode == 1;
+  const bool none = a->W_group_mode == 0 && a->channel_scale_mode == 0;
+  if (!(pre || post || none)) return false;
+  if ((pre || post) && a->scales == nullptr) return false;
+  if (pre && a->s_stride_n != 1) return false;
+  return smem_bytes(a->M, a->K) <= kSmemLimit;
+}
+
+int gl_w8_gemv_launch(const gl_matmul_args* a, cudaStream_t st) {
+  W8Params p;
+  p.x = a->x; p.w = reinterpret_cast<const uint8_t*>(a->w); p.scales = a->scales; p.bias = a->bias; p.out = a->out;
+  p.M = a->M; p.N = a->N; p.K = a->K; p.x_dtype = a->x_dtype; p.out_dtype = a->out_dtype; p.scales_dtype = a->meta_dtype;
+  p.is_fp8 = a->w_dtype == GL_FP8; p.has_scale = (a->W_group_mode == 2 || a->channel_scale_mode == 1) ? 1 : 0;
+  const size_t smem = smem_bytes(a->M, a->K);
+  const dim3 grid((unsigned)gl_cdiv(a->N, kWarps * kRows)), block(kWarps * 32);
+#define GL_W8(MM)                                                                                                   \
+  case MM: {                                                                                                        \
+    if (p.is_fp8) { GL_CUDA_CHECK(cudaFuncSetAttribute(gl_w8_gemv_kernel<MM, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit)); \
+                    GL_CUDA_CHECK(gl_launch_pdl(gl_w8_gemv_kernel<MM, true>, grid, block, smem, st, p)); }          \
+    else          { GL_CUDA_CHECK(cudaFuncSetAttribute(gl_w8_gemv_kernel<MM, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit)); \
+                    GL_CUDA_CHECK(gl_launch_pdl(gl_w8_gemv_kernel<MM, false>, grid, block, smem, st, p)); }         \
+    return GL_OK; }
+  switch (a->M) { GL_W8(1) GL_W8(2) GL_W8(3) GL_W8(4) }
+#undef GL_W8
+  GL_FAIL(GL_E_UNSUPPORTED, "gl_matmul: weight-only 8-bit decode kernel takes 1..4 rows");
+}

@@ -61,6 +61,43 @@ def test_a16w8(lib, fp8):
         assert rel_fro(y, (x.double() @ Wd.T).numpy()) < 1e-2
 
 
+@pytest.mark.parametrize("fp8", [True, False])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_a16w8_decode_kernel(lib, fp8, dtype):
+    """Weight-only INT8 / FP8 with one scale per channel at 1..4 rows runs on the streaming decode kernel of its own
+    (the general kernel above that); ragged N and a K that is not a multiple of 512, with and without bias, both scale
+    placements, against the fp64 product of the stored operands and against the general kernel."""
+    import ctypes
+    from gemlite_b200 import core, helper, _lib
+    for (N, K) in ((2032, 3968), (4096, 8192)):
+        g = torch.Generator().manual_seed(900 + N)
+        W = (torch.randn(N, K, generator=g) * 0.05).to(dtype)
+        bias = (torch.randn(N, generator=g) * 3.0).to(dtype)
+        for post_scale in (False, True):
+            proc = (helper.A16W8_FP8 if fp8 else helper.A16W8_INT8)(device="cuda:0", dtype=dtype, post_scale=post_scale)
+            layer = proc.from_weights(W.cuda(), bias=bias.cuda() if post_scale else None)
+            Wd = layer.W_q.t().float().cpu().double() * layer.scales.cpu().double().view(-1, 1)
+            for M in (1, 2, 3, 4, 5):
+                x = torch.randn(M, K, generator=g).to(dtype)
+                xd = x.cuda()
+                out = torch.empty((M, N), dtype=dtype, device="cuda")
+                a = core._fill_args(xd, layer.bias, layer.W_q, layer.scales, layer.zeros, None, None, out, layer.get_meta_args(), -1)
+                name = _lib.lib().gl_matmul_kernel_name(ctypes.byref(a)).decode()
+                assert name == ("gl_w8_gemv_kernel" if M <= 4 else "gl_generic_kernel"), (M, name)
+                y = layer(xd)
+                assert torch.equal(y, layer(xd))                                   # deterministic
+                want = (x.double() @ Wd.T).numpy() + (bias.double().numpy() if post_scale else 0.0)
+                yn = y.float().cpu().numpy()
+                assert rel_fro(yn, want) < 1e-2, (N, K, M, post_scale, rel_fro(yn, want))
+                assert rel_fro(yn[-1], want[-1]) < 1e-2 and rel_fro(yn[:, -40:], want[:, -40:]) < 1e-2     # last row, ragged tail columns
+                core.set_kernel_override(1)
+                try:
+                    yg = layer(xd).float().cpu().numpy()
+                finally:
+                    core.set_kernel_override(0)
+                assert rel_fro(yn, yg) < 1e-2
+
+
 @pytest.mark.parametrize("fmt", ["mxfp4", "nvfp4"])
 @pytest.mark.parametrize("M", [1, 3, 16, 64, 100])
 def test_a4w4_block_scaled(lib, fmt, M):
