@@ -43,7 +43,7 @@ extern "C" int gl_get_matmul_type(int32_t M, int32_t W_nbits, int32_t is_mx_dtyp
   return (W_nbits < 8) ? GL_MM_GEMV_REVSPLITK : GL_MM_GEMV_SPLITK;
 }
 
-enum KernelId { K_INVALID = 0, K_STREAM, K_TC, K_W8, K_GENERIC };
+enum KernelId { K_INVALID = 0, K_STREAM, K_TC, K_W8, K_W4MX, K_GENERIC };
 
 int gl_validate_matmul_args(const gl_matmul_args* a) {
   if (a == nullptr) GL_FAIL(GL_E_INVALID, "gl_matmul: null argument struct");
@@ -87,6 +87,7 @@ KernelId select(const gl_matmul_args* a, int* family_out) {
   if (gl_gemm_tc_supported(a)) return K_TC;
   if (stream_ok) return K_STREAM;
   if (!mx && gl_w8_gemv_supported(a)) return K_W8;
+  if (mx && gl_w4mx_gemv_supported(a)) return K_W4MX;
   return K_GENERIC;
 }
 
@@ -108,6 +109,7 @@ extern "C" const char* gl_matmul_kernel_name(const gl_matmul_args* a) {
     case K_STREAM: return gl_gemv_stream_kernel_name(a);
     case K_TC: return "gl_gemm_tc_kernel";
     case K_W8: return "gl_w8_gemv_kernel";
+    case K_W4MX: return "gl_w4mx_gemv_kernel";
     case K_GENERIC: return "gl_generic_kernel";
     default: return "invalid";
   }
@@ -122,6 +124,7 @@ extern "C" int gl_matmul(const gl_matmul_args* a, void* stream) {
     case K_STREAM: return gl_gemv_stream_launch(a, st);
     case K_TC: return gl_gemm_tc_launch(a, st);
     case K_W8: return gl_w8_gemv_launch(a, st);
+    case K_W4MX: return gl_w4mx_gemv_launch(a, st);
     case K_GENERIC: return gl_generic_launch(a, st);
     default:
       GL_FAIL(GL_E_UNSUPPORTED, "gl_matmul: kernel family %d does not support MX / NV block-scaled dtypes", fam);

@@ -68,6 +68,9 @@ int gl_generic_launch(const gl_matmul_args* a, cudaStream_t st);
 // weight-only 8-bit layers (unpacked INT8 / FP8 weights, one scale per channel) at decode sizes (gl_w8.cu)
 bool gl_w8_gemv_supported(const gl_matmul_args* a);
 int gl_w8_gemv_launch(const gl_matmul_args* a, cudaStream_t st);
+// weight-only block-scaled fp4 (e2m1 + e8m0 / e4m3 group scales, 16-bit activations) at decode sizes (gl_w8.cu)
+bool gl_w4mx_gemv_supported(const gl_matmul_args* a);
+int gl_w4mx_gemv_launch(const gl_matmul_args* a, cudaStream_t st);
 int gl_validate_matmul_args(const gl_matmul_args* a);
 int gl_gemm_tc_supported(const gl_matmul_args* a);
 uint64_t gl_gemm_tc_workspace(const gl_matmul_args* a);

@@ -98,6 +98,43 @@ def test_a16w8_decode_kernel(lib, fp8, dtype):
                 assert rel_fro(yn, yg) < 1e-2
 
 
+@pytest.mark.parametrize("which", ["A16W4_MXFP", "A16W4_NVFP"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_weight_only_fp4_decode_kernel(lib, which, dtype):
+    """Weight-only MXFP4 / NVFP4 (16-bit activations) at 1..4 rows runs on a streaming decode kernel; checked against the
+    general kernel (which decodes every weight and scale individually) and against the unquantised product, on the
+    reference's test shape 4224 -> 2048 (K is 132 groups of 32: a ragged last step) and a larger one."""
+    import ctypes
+    from gemlite_b200 import core, helper, _lib
+    for (N, K) in ((2048, 4224), (4096, 8192)):
+        g = torch.Generator().manual_seed(950 + N)
+        lin = torch.nn.Linear(K, N, bias=True, dtype=dtype)
+        lin.weight.data = (torch.randn(N, K, generator=g) / 10.0 / (K ** 0.5) * 8).to(dtype)
+        lin.bias.data = torch.randn(N, generator=g).to(dtype) * 0.1
+        W, b = lin.weight.data.clone(), lin.bias.data.clone()
+        layer = getattr(helper, which)(device="cuda:0", dtype=dtype).from_linear(lin.cuda())
+        for M in (1, 2, 4, 5):
+            x = torch.randn(M, K, generator=g).to(dtype)
+            xd = x.cuda()
+            out = torch.empty((M, N), dtype=dtype, device="cuda")
+            a = core._fill_args(xd, layer.bias, layer.W_q, layer.scales, layer.zeros, None,
+                                layer.meta_scale.reshape(1) if which == "A16W4_NVFP" else None, out, layer.get_meta_args(), -1)
+            name = _lib.lib().gl_matmul_kernel_name(ctypes.byref(a)).decode()
+            assert name == ("gl_w4mx_gemv_kernel" if M <= 4 else "gl_generic_kernel"), (M, name)
+            y = layer(xd)
+            assert torch.equal(y, layer(xd))
+            core.set_kernel_override(1)
+            try:
+                yg = layer(xd).float().cpu().numpy()
+            finally:
+                core.set_kernel_override(0)
+            yn = y.float().cpu().numpy()
+            assert rel_fro(yn, yg) < 5e-3, (which, N, K, M, rel_fro(yn, yg))
+            assert rel_fro(yn[-1], yg[-1]) < 5e-3 and rel_fro(yn[:, -33:], yg[:, -33:]) < 5e-3
+            want = (x.double() @ W.double().T + b.double()).numpy()
+            assert rel_fro(yn, want) < 0.2
+
+
 @pytest.mark.parametrize("fmt", ["mxfp4", "nvfp4"])
 @pytest.mark.parametrize("M", [1, 3, 16, 64, 100])
 def test_a4w4_block_scaled(lib, fmt, M):
