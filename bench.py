@@ -566,7 +566,8 @@ def sweep_gemm(device, only=None, mma_peaks=None):
     ref = bench_reference().get("reference_triton_timings", {}).get("timings", {})
     ref_graph = bench_reference().get("reference_triton_timings_graph", {}).get("timings", {})
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.int8, device=device)
-    dense_peak = {"A16W4": 2250.0, "A16W2": 2250.0, "A16W8": 2250.0, "FP8": 4500.0, "MXFP4": 9000.0, "NVFP4": 9000.0}     # nominal dense TFLOP/s
+    dense_peak = {"A16W4": 2250.0, "A16W2": 2250.0, "A16W8": 2250.0, "FP8": 4500.0, "MXFP4": 9000.0, "NVFP4": 9000.0,
+                  "A16W8c": 2250.0, "A16W4MX": 2250.0}     # nominal dense TFLOP/s
 
     def timed(fn, reps=10):
         for _ in range(3):
@@ -591,23 +592,27 @@ def sweep_gemm(device, only=None, mma_peaks=None):
             z = (torch.rand(N * K // gs, 1, generator=g, device=device) * (2 ** nbits - 1)).to(torch.bfloat16)
             b = (torch.randn(N, generator=g, device=device) * 0.01).to(torch.bfloat16)
             return helper.A16Wn_HQQ_INT(device=str(device), dtype=torch.bfloat16, W_nbits=nbits).from_weights(W_q, sc, z, bias=b), K, N
-        K, N = (4096, 14336) if fmt == "FP8" else (16384, 16384)
+        K, N = (4096, 14336) if fmt == "FP8" else ((8192, 8192) if fmt in ("A16W8c", "A16W4MX") else (16384, 16384))
         lin = torch.nn.Linear(K, N, bias=False, dtype=torch.bfloat16, device=device)
         lin.weight.data.normal_(0, 0.02, generator=g)
-        P = {"FP8": helper.A8W8_FP8_dynamic, "MXFP4": helper.A4W4_MXFP_dynamic, "NVFP4": helper.A4W4_NVFP_dynamic}[fmt]
+        # A16W8c: weight-only INT8 with one scale per channel; A16W4MX: weight-only MXFP4 (16-bit activations)
+        P = {"FP8": helper.A8W8_FP8_dynamic, "MXFP4": helper.A4W4_MXFP_dynamic, "NVFP4": helper.A4W4_NVFP_dynamic,
+             "A16W8c": helper.A16W8_INT8, "A16W4MX": helper.A16W4_MXFP}[fmt]
         return P(device=str(device), dtype=torch.bfloat16).from_linear(lin), K, N
 
     res = []
     stream = torch.cuda.Stream(device)
     cases = (("A16W4", (32, 64, 256, 1024, 4096, 8192)), ("A16W2", (1, 16, 64, 256, 1024, 4096, 8192)), ("A16W8", (1, 16, 1024)), ("FP8", (1, 16, 128, 1024, 4096)),
-             ("MXFP4", (1, 64, 512, 4096, 16384)), ("NVFP4", (1, 64, 512, 4096, 16384)))
+             ("MXFP4", (1, 64, 512, 4096, 16384)), ("NVFP4", (1, 64, 512, 4096, 16384)), ("A16W8c", (1, 4)), ("A16W4MX", (1, 4)))
     if only is not None:
         cases = ((only[0], (only[1],)),)
     for fmt, Ms in cases:
         try:
             layer, K, N = make(fmt)
-            wbytes = N * K // {"FP8": 1, "A16W8": 1, "A16W2": 4}.get(fmt, 2)
-            W_ref = _dequant_packed_int(layer) if fmt.startswith("A16") else (
+            wbytes = N * K // {"FP8": 1, "A16W8": 1, "A16W8c": 1, "A16W2": 4}.get(fmt, 2)
+            W_ref = (layer.W_q.float() * layer.scales.float().view(1, -1)) if fmt == "A16W8c" else (
+                _decode_fp4(layer.W_q.t().contiguous(), layer.scales.contiguous().view(torch.uint8), 32, True).t().contiguous()) if fmt == "A16W4MX" else (
+                _dequant_packed_int(layer)) if fmt.startswith("A16") else (
                 None if fmt == "FP8" else _decode_fp4(layer.W_q.t().contiguous(), layer.scales.contiguous().view(torch.uint8),
                                                       32 if fmt == "MXFP4" else 16, fmt == "MXFP4"))
             for M in Ms:
