@@ -86,7 +86,7 @@ KernelId select(const gl_matmul_args* a, int* family_out) {
   if (stream_ok && a->M <= 16) return K_STREAM;
   if (gl_gemm_tc_supported(a)) return K_TC;
   if (stream_ok) return K_STREAM;
-  if (!mx && gl_w8_gemv_supported(a)) return K_W8;
+  if (gl_w8_gemv_supported(a)) return K_W8;                // (also weight-only MXFP8)
   if (mx && gl_w4mx_gemv_supported(a)) return K_W4MX;
   return K_GENERIC;
 }

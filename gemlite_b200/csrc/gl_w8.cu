@@ -26,13 +26,16 @@ constexpr size_t kSmemLimit = 200 * 1024;
 struct W8Params {
   const void* x; const uint8_t* w; const void* scales; const void* bias; void* out;
   int M, N, K, x_dtype, out_dtype, scales_dtype, is_fp8, has_scale;
+  long long s_stride_g, s_stride_n;                    // grouped (MXFP8 weights): e8m0 scale of (group, channel)
 };
 
 __device__ __forceinline__ float x_as_float(const void* x, int64_t i, int dt) {
   return dt == GL_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(x)[i]) : __half2float(reinterpret_cast<const __half*>(x)[i]);
 }
 
-template <int MM, bool FP8>
+// GROUPED: weight-only MXFP8 (e4m3 weights, one e8m0 scale per 32 weights, the reference's A16W8_MXFP processor): a
+// lane's 16 weights are half a group, so the group scale multiplies the lane's partial sum of the step.
+template <int MM, bool FP8, bool GROUPED = false>
 __global__ void __launch_bounds__(kWarps * 32) gl_w8_gemv_kernel(const W8Params p) {
   extern __shared__ float xs[];                       // [MM][steps][4][32] float4-interleaved activations
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -40,17 +43,26 @@ __global__ void __launch_bounds__(kWarps * 32) gl_w8_gemv_kernel(const W8Params 
   const int steps = (units + 31) / 32;
   const int n0 = (blockIdx.x * kWarps + warp) * kRows;
   const uint4* wrow[kRows];
+  int nrow[kRows];
 #pragma unroll
-  for (int r = 0; r < kRows; ++r) wrow[r] = reinterpret_cast<const uint4*>(p.w + (size_t)min(n0 + r, p.N - 1) * p.K);
+  for (int r = 0; r < kRows; ++r) {
+    nrow[r] = min(n0 + r, p.N - 1);
+    wrow[r] = reinterpret_cast<const uint4*>(p.w + (size_t)nrow[r] * p.K);
+  }
   // the first two steps of weights are requested before the dependency wait: they do not depend on the previous kernel
   uint4 buf[2][kRows];
-#pragma unroll
-  for (int s = 0; s < 2; ++s)
+  uint32_t sbuf[2][kRows];                            // grouped: the unit's scale byte
+  auto fetch = [&](int i, uint4 (&b)[kRows], uint32_t (&sb)[kRows]) {
+    const int u = i * 32 + lane;
+    const bool ok = i < steps && u < units;
 #pragma unroll
     for (int r = 0; r < kRows; ++r) {
-      const int u = s * 32 + lane;
-      buf[s][r] = (s < steps && u < units) ? __ldg(wrow[r] + u) : make_uint4(0u, 0u, 0u, 0u);
+      b[r] = ok ? __ldg(wrow[r] + u) : make_uint4(0u, 0u, 0u, 0u);
+      if (GROUPED) sb[r] = ok ? (uint32_t)__ldg(reinterpret_cast<const uint8_t*>(p.scales) + (long long)(u >> 1) * p.s_stride_g + (long long)nrow[r] * p.s_stride_n) : 0u;
     }
+  };
+  fetch(0, buf[0], sbuf[0]);
+  fetch(1, buf[1], sbuf[1]);
   gl_launch_dependents();
   gl_grid_dependency_wait();
   // stage x: unit u = 32 * i + l holds k = 16 u .. 16 u + 15; its four float4 go to xs[m][i][j][l]
@@ -73,15 +85,17 @@ __global__ void __launch_bounds__(kWarps * 32) gl_w8_gemv_kernel(const W8Params 
 #pragma unroll
     for (int m = 0; m < MM; ++m) acc[r][m] = 0.f;
   // one step: consume the 16 bytes per row held in `b`, then refill `b` with step i + 2
-  auto step = [&](int i, uint4 (&b)[kRows]) {
+  auto step = [&](int i, uint4 (&b)[kRows], uint32_t (&sb)[kRows]) {
     uint4 wv[kRows];
+    uint32_t sv[kRows];
 #pragma unroll
-    for (int r = 0; r < kRows; ++r) wv[r] = b[r];
-    {
-      const int u = (i + 2) * 32 + lane;
+    for (int r = 0; r < kRows; ++r) { wv[r] = b[r]; sv[r] = GROUPED ? sb[r] : 0u; }
+    fetch(i + 2, b, sb);
+    float part[kRows][MM];                             // grouped: the step's partial sums, scaled once below
 #pragma unroll
-      for (int r = 0; r < kRows; ++r) b[r] = (i + 2 < steps && u < units) ? __ldg(wrow[r] + u) : make_uint4(0u, 0u, 0u, 0u);
-    }
+    for (int r = 0; r < kRows; ++r)
+#pragma unroll
+      for (int m = 0; m < MM; ++m) part[r][m] = 0.f;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       float4 xv[MM];
@@ -104,14 +118,24 @@ __global__ void __launch_bounds__(kWarps * 32) gl_w8_gemv_kernel(const W8Params 
           f3 = __uint_as_float(__byte_perm(u4, 0x4B000000u, 0x7543)) - 8388736.f;
         }
 #pragma unroll
-        for (int m = 0; m < MM; ++m)
-          acc[r][m] = fmaf(xv[m].x, f0, fmaf(xv[m].y, f1, fmaf(xv[m].z, f2, fmaf(xv[m].w, f3, acc[r][m]))));
+        for (int m = 0; m < MM; ++m) {
+          if (GROUPED) part[r][m] = fmaf(xv[m].x, f0, fmaf(xv[m].y, f1, fmaf(xv[m].z, f2, fmaf(xv[m].w, f3, part[r][m]))));
+          else acc[r][m] = fmaf(xv[m].x, f0, fmaf(xv[m].y, f1, fmaf(xv[m].z, f2, fmaf(xv[m].w, f3, acc[r][m]))));
+        }
+      }
+    }
+    if (GROUPED) {
+#pragma unroll
+      for (int r = 0; r < kRows; ++r) {
+        const float sc = gl_e8m0_to_float(sv[r]);
+#pragma unroll
+        for (int m = 0; m < MM; ++m) acc[r][m] = fmaf(part[r][m], sc, acc[r][m]);
       }
     }
   };
   for (int i = 0; i < steps; i += 2) {
-    step(i, buf[0]);
-    if (i + 1 < steps) step(i + 1, buf[1]);
+    step(i, buf[0], sbuf[0]);
+    if (i + 1 < steps) step(i + 1, buf[1], sbuf[1]);
   }
 #pragma unroll
   for (int r = 0; r < kRows; ++r)
@@ -263,11 +287,18 @@ size_t smem_bytes(int M, int K) { return (size_t)M * ((K / 16 + 31) / 32) * 512 
 
 }  // namespace
 
+static bool w8_grouped(const gl_matmul_args* a) {       // weight-only MXFP8: e4m3 weights, e8m0 scale per 32, 16-bit activations
+  return gl_is_mx(a->input_dtype) && a->w_dtype == GL_FP8 && a->group_size == 32 && a->channel_scale_mode == 0 &&
+         a->scales != nullptr && a->scales_x == nullptr && a->K % 32 == 0;
+}
+
 bool gl_w8_gemv_supported(const gl_matmul_args* a) {
   if (a->M < 1 || a->M > kMaxM || a->W_nbits != 8 || a->elements_per_sample != 1) return false;
   if (!(a->w_dtype == GL_INT8 || a->w_dtype == GL_FP8)) return false;
-  if (!(a->x_dtype == GL_FP16 || a->x_dtype == GL_BF16) || a->input_dtype != a->x_dtype) return false;
+  if (!(a->x_dtype == GL_FP16 || a->x_dtype == GL_BF16)) return false;
   if (a->w_stride_k != 1 || a->w_stride_n != a->K || a->K % 16 != 0 || ((uintptr_t)a->w & 15)) return false;
+  if (gl_is_mx(a->input_dtype)) return w8_grouped(a) && smem_bytes(a->M, a->K) <= kSmemLimit;
+  if (a->input_dtype != a->x_dtype) return false;
   const bool pre = a->W_group_mode == 2 && a->channel_scale_mode == 0 && a->group_size == a->K;   // one scale per channel, applied to the weights
   const bool post = a->W_group_mode == 0 && a->channel_scale_mode == 1;
   const bool none = a->W_group_mode == 0 && a->channel_scale_mode == 0;
@@ -281,12 +312,16 @@ int gl_w8_gemv_launch(const gl_matmul_args* a, cudaStream_t st) {
   W8Params p;
   p.x = a->x; p.w = reinterpret_cast<const uint8_t*>(a->w); p.scales = a->scales; p.bias = a->bias; p.out = a->out;
   p.M = a->M; p.N = a->N; p.K = a->K; p.x_dtype = a->x_dtype; p.out_dtype = a->out_dtype; p.scales_dtype = a->meta_dtype;
-  p.is_fp8 = a->w_dtype == GL_FP8; p.has_scale = (a->W_group_mode == 2 || a->channel_scale_mode == 1) ? 1 : 0;
+  const bool grouped = gl_is_mx(a->input_dtype);
+  p.is_fp8 = a->w_dtype == GL_FP8; p.has_scale = (!grouped && (a->W_group_mode == 2 || a->channel_scale_mode == 1)) ? 1 : 0;
+  p.s_stride_g = a->s_stride_g; p.s_stride_n = a->s_stride_n;
   const size_t smem = smem_bytes(a->M, a->K);
   const dim3 grid((unsigned)gl_cdiv(a->N, kWarps * kRows)), block(kWarps * 32);
 #define GL_W8(MM)                                                                                                   \
   case MM: {                                                                                                        \
-    if (p.is_fp8) { GL_CUDA_CHECK(cudaFuncSetAttribute(gl_w8_gemv_kernel<MM, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit)); \
+    if (grouped)  { GL_CUDA_CHECK(cudaFuncSetAttribute(gl_w8_gemv_kernel<MM, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit)); \
+                    GL_CUDA_CHECK(gl_launch_pdl(gl_w8_gemv_kernel<MM, true, true>, grid, block, smem, st, p)); }    \
+    else if (p.is_fp8) { GL_CUDA_CHECK(cudaFuncSetAttribute(gl_w8_gemv_kernel<MM, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit)); \
                     GL_CUDA_CHECK(gl_launch_pdl(gl_w8_gemv_kernel<MM, true>, grid, block, smem, st, p)); }          \
     else          { GL_CUDA_CHECK(cudaFuncSetAttribute(gl_w8_gemv_kernel<MM, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit)); \
                     GL_CUDA_CHECK(gl_launch_pdl(gl_w8_gemv_kernel<MM, false>, grid, block, smem, st, p)); }         \
