@@ -60,3 +60,29 @@ def test_benchmark_shapes_land_on_their_kernels():
     counter = int(_lib.lib().gl_matmul_counter_bytes())
     assert _plan(64, 8192, 8192, 4, 128)[1] == counter
     assert _plan(4096, 8192, 8192, 4, 128)[1] == counter
+
+
+def test_weight_only_decode_kernels_are_selected():
+    """Unpacked 8-bit weights with one scale per channel and weight-only block-scaled fp4 / fp8 at 1..4 rows go to the
+    streaming decode kernels of their own; more rows stay on the general kernel."""
+    L = _lib.lib()
+
+    def name(M, N, K, w_dtype, nbits, e, gs, input_dtype, wgm, csm, w_stride_n):
+        a = _args(M, N, K, 4, 128)
+        a.W_nbits, a.elements_per_sample, a.group_size = nbits, e, gs
+        a.w_dtype, a.input_dtype = w_dtype.value, input_dtype.value
+        a.W_group_mode, a.channel_scale_mode = wgm, csm
+        a.w_stride_k, a.w_stride_n = 1, w_stride_n
+        a.meta_dtype = DType.FP32.value
+        return L.gl_matmul_kernel_name(ctypes.byref(a)).decode()
+
+    for M, want8, want4 in ((1, "gl_w8_gemv_kernel", "gl_w4mx_gemv_kernel"), (4, "gl_w8_gemv_kernel", "gl_w4mx_gemv_kernel"),
+                            (5, "gl_generic_kernel", "gl_generic_kernel")):
+        assert name(M, 8192, 8192, DType.INT8, 8, 1, 8192, DType.BF16, 2, 0, 8192) == want8          # A16W8_INT8, scale on the weights
+        assert name(M, 2032, 3968, DType.FP8, 8, 1, 3968, DType.BF16, 0, 1, 3968) == want8           # A16W8_FP8, scale on the sums
+        assert name(M, 4096, 8192, DType.FP8, 8, 1, 32, DType.MXBF16, 0, 0, 8192) == want8           # A16W8_MXFP
+        assert name(M, 4096, 8192, DType.UINT8, 4, 2, 32, DType.MXBF16, 0, 0, 4096) == want4         # A16W4_MXFP
+        assert name(M, 4096, 8192, DType.UINT8, 4, 2, 16, DType.NVFP4, 0, 0, 4096) == want4          # A16W4_NVFP
+    # grouped zeros or a K that is not a multiple of 16 bytes are not what these kernels take
+    assert name(1, 8192, 8192, DType.INT8, 8, 1, 128, DType.BF16, 4, 0, 8192) == "gl_generic_kernel"
+    assert name(1, 512, 1000, DType.INT8, 8, 1, 1000, DType.BF16, 2, 0, 1000) == "gl_generic_kernel"
