@@ -260,6 +260,57 @@ extern "C" int gl_scale_activations_per_token(const void* x, void* q, float* sca
   return GL_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// per block: one scale per (row, 128 consecutive k) -- the activation side of 128 x 128 block quantisation
+// (gemlite/quant_utils.py:2504-2522).  Sixteen lanes own a block (8 elements each): amax by four shuffles inside the
+// half warp, scale = max(amax / qmax, 1e-6), q = clamp(x / scale) cast (FP8) or rounded half away from zero (INT8, as
+// the reference's active kernel does: quant_utils.py:2613-2675 with libdevice.round).
+template <bool INT8>
+__global__ void __launch_bounds__(256) per_block_kernel(const void* __restrict__ x, uint8_t* __restrict__ q,
+                                                        float* __restrict__ scales, int64_t total_units, int K, int x_dtype) {
+  gl_launch_dependents();
+  gl_grid_dependency_wait();
+  const float qmax = INT8 ? 127.f : 448.f, qmin = INT8 ? -128.f : -448.f;
+  const int units_per_row = K / 8;
+  // the loop bound is half-warp-uniform: a block's sixteen units are either all inside or all outside
+  for (int64_t u0 = blockIdx.x * (int64_t)blockDim.x + (threadIdx.x & ~15); u0 < total_units; u0 += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t u = u0 + (threadIdx.x & 15);
+    const int m = (int)(u / units_per_row), k = (int)(u % units_per_row) * 8;
+    float v[8];
+    load8(x, (int64_t)m * K + k, x_dtype, v);
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    const unsigned half_mask = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;     // the other half warp may be past the end
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(half_mask, amax, o));
+    const float s = fmaxf(amax / qmax, 1e-6f);
+    if ((threadIdx.x & 15) == 0) scales[(int64_t)m * (K / 128) + k / 128] = s;
+    uint32_t o2[2] = {0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float t = fminf(fmaxf(v[i] / s, qmin), qmax);
+      uint32_t b;
+      if (INT8) b = (uint32_t)(uint8_t)(int8_t)(int)roundf(t);                // libdevice.round: half away from zero
+      else b = (uint32_t)__nv_cvt_float_to_fp8(t, __NV_SATFINITE, __NV_E4M3);
+      o2[i >> 2] |= b << (8 * (i & 3));
+    }
+    *reinterpret_cast<uint2*>(q + (int64_t)m * K + k) = make_uint2(o2[0], o2[1]);
+  }
+}
+
+extern "C" int gl_scale_activations_per_block(const void* x, void* q, float* scales, int32_t M, int32_t K,
+                                              int32_t x_dtype, int32_t q_dtype, void* stream) {
+  if (int rc = check_x("gl_scale_activations_per_block", x, M, K, x_dtype, 128)) return rc;
+  if (!(q_dtype == GL_FP8 || q_dtype == GL_INT8)) GL_FAIL(GL_E_INVALID, "gl_scale_activations_per_block: q_dtype must be FP8 (e4m3) or INT8, got %d", q_dtype);
+  if (M == 0) return GL_OK;
+  if (!q || !scales || ((uintptr_t)q & 7)) GL_FAIL(GL_E_INVALID, "gl_scale_activations_per_block: null or misaligned output");
+  const int64_t units = (int64_t)M * (K / 8);
+  if (q_dtype == GL_INT8) GL_CUDA_CHECK(gl_launch_pdl(per_block_kernel<true>, dim3(grid_units(units)), dim3(256), 0, (cudaStream_t)stream, x, (uint8_t*)q, scales, units, K, x_dtype));
+  else GL_CUDA_CHECK(gl_launch_pdl(per_block_kernel<false>, dim3(grid_units(units)), dim3(256), 0, (cudaStream_t)stream, x, (uint8_t*)q, scales, units, K, x_dtype));
+  return GL_OK;
+}
+
 static int check_layout(const char* fn, int layout, int G) {
   if (layout != 0 && layout != 1) { gl_set_error("%s: scale_layout must be 0 or 1", fn); return GL_E_INVALID; }
   if (layout == 1 && G % 4 != 0) { gl_set_error("%s: scale atoms need K / group_size to be a multiple of 4", fn); return GL_E_INVALID; }

@@ -52,6 +52,14 @@ __global__ void __launch_bounds__(32 * KS) gl_generic_kernel(const GenParams p) 
   if (a.zero_is_scalar && a.zeros) zscalar = gl_load_as_float(a.zeros, 0, a.zeros_dtype);
   const bool x_fp4 = p.is_mx && a.x_dtype == GL_UINT8;   // activations packed e2m1, two per byte
 
+  // channel_scale_mode 5 (128 x 128 block quantisation, gemm_kernels.py:396-450): the sum over each block of 128 k is
+  // multiplied by the activation scale of (row, block) and the weight scale of (block, n / 128) before it is added
+  const bool block_quant = !p.is_mx && a.channel_scale_mode == 5;
+  float bacc[MBG];
+  int biacc[MBG];
+#pragma unroll
+  for (int i = 0; i < MBG; ++i) { bacc[i] = 0.f; biacc[i] = 0; }
+
   const int kwords = a.K / e, per = (kwords + KS - 1) / KS;
   const int kw_begin = min(kwords, (int)threadIdx.y * per), kw_end = valid ? min(kwords, kw_begin + per) : kw_begin;
   for (int kw = kw_begin; kw < kw_end; ++kw) {
@@ -97,7 +105,17 @@ __global__ void __launch_bounds__(32 * KS) gl_generic_kernel(const GenParams p) 
       for (int i = 0; i < MBG; ++i) {
         const int m = m0 + i;
         if (m >= a.M) break;
-        if (p.int_acc) {
+        if (block_quant) {
+          if (p.int_acc) biacc[i] += (int)reinterpret_cast<const int8_t*>(a.x)[(int64_t)m * a.K + k] * bi;
+          else bacc[i] = fmaf(gl_load_as_float(a.x, (int64_t)m * a.K + k, a.x_dtype), b, bacc[i]);
+          if ((k & 127) == 127 || kw == kw_end - 1) {        // end of the block, or of this thread's share of it
+            const int kb = k >> 7;
+            const float sc = reinterpret_cast<const float*>(a.scales_x)[(int64_t)m * (a.K / 128) + kb] *
+                             gl_load_as_float(a.scales, (int64_t)kb * a.s_stride_g + (int64_t)(n >> 7) * a.s_stride_n, a.meta_dtype);
+            acc[i] = fmaf(p.int_acc ? (float)biacc[i] : bacc[i], sc, acc[i]);
+            bacc[i] = 0.f; biacc[i] = 0;
+          }
+        } else if (p.int_acc) {
           iacc[i] += (int)reinterpret_cast<const int8_t*>(a.x)[(int64_t)m * a.K + k] * bi;
         } else {
           float xv;
@@ -135,7 +153,7 @@ __global__ void __launch_bounds__(32 * KS) gl_generic_kernel(const GenParams p) 
   for (int i = 0; i < MBG; ++i) {
     const int m = m0 + i;
     if (m >= a.M) break;
-    float v = p.int_acc ? (float)iacc[i] : acc[i];
+    float v = (p.int_acc && !block_quant) ? (float)iacc[i] : acc[i];
     if (p.is_mx) {
       if (gs == 16 && a.meta_scale) v *= *a.meta_scale;
       if (a.channel_scale_mode == 2) v *= reinterpret_cast<const float*>(a.scales_x)[m];
@@ -159,7 +177,12 @@ int gl_generic_launch(const gl_matmul_args* a, cudaStream_t st) {
   p.gx = a->group_size;
   p.sx_stride = a->K / (a->group_size > 0 ? a->group_size : 1);
   p.int_acc = 0;
-  if (a->channel_scale_mode == 5) GL_FAIL(GL_E_UNSUPPORTED, "gl_matmul: channel_scale_mode 5 (128x128 block quant) is not implemented");
+  if (a->channel_scale_mode == 5) {
+    if (p.is_mx || a->W_nbits != 8 || a->elements_per_sample != 1 || a->W_group_mode != 0)
+      GL_FAIL(GL_E_UNSUPPORTED, "gl_matmul: channel_scale_mode 5 (128x128 block quantisation) takes unpacked 8-bit weights without group modes");
+    if (a->scales == nullptr || a->scales_x == nullptr || a->K % 128 != 0)
+      GL_FAIL(GL_E_INVALID, "gl_matmul: channel_scale_mode 5 needs block scales, per-block activation scales and K %% 128 == 0");
+  }
   if (!p.is_mx && a->input_dtype == GL_INT8 && a->x_dtype == GL_INT8) {
     if (a->W_group_mode == 0 || (a->W_group_mode == 1)) p.int_acc = 1;
   }

@@ -398,7 +398,7 @@ class A8W8_dynamic:
     def from_weights(self, weight, bias=None, scales=None):
         weight, bias = _data(weight), _data(bias)
         if self.block_quant:
-            raise NotImplementedError("128x128 block quantisation (channel_scale_mode 5) is not implemented")
+            return self._from_weights_block_quant(weight, bias=bias, scales=scales)
         w_dtype = self.fp8 if self.fp8 else torch.int8
         input_dtype = TORCH_TO_DTYPE[self.fp8] if self.fp8 else DType.INT8
         in_features, out_features = weight.shape[::-1]
@@ -416,6 +416,42 @@ class A8W8_dynamic:
                               input_dtype=input_dtype, output_dtype=TORCH_TO_DTYPE[dtype], scaled_activations=True)
         layer.pack(W_q, scales, zeros=None, bias=bias)
         layer.W_group_mode, layer.channel_scale_mode = 0, 3   # acc * s_x[m] * s_w[n]
+        return layer
+
+    def _from_weights_block_quant(self, weight, bias=None, scales=None):
+        """128 x 128 block quantisation of the weights with one fp32 scale per block, activations quantised per row and
+        per 128 k in the forward (channel_scale_mode 5; gemlite/helper.py:517-617).  `scales` given: `weight` is already
+        8-bit and `scales` is [ceil(N/128), ceil(K/128)]."""
+        B = 128
+        w_dtype = self.fp8 if self.fp8 else torch.int8
+        input_dtype = TORCH_TO_DTYPE[self.fp8] if self.fp8 else DType.INT8
+        info = torch.finfo(w_dtype) if w_dtype.is_floating_point else torch.iinfo(w_dtype)
+        in_features, out_features = weight.shape[::-1]
+        nb, kb = (out_features + B - 1) // B, (in_features + B - 1) // B
+        if scales is not None:
+            assert weight.dtype == w_dtype, f"Pre-quantized weight must be {w_dtype}, got {weight.dtype}"
+            assert tuple(scales.shape) == (nb, kb), f"Pre-quantized scales must have shape {(nb, kb)}, got {tuple(scales.shape)}"
+            W_q = weight.contiguous().to(device=self.device)
+            scales = scales.to(device=self.device, dtype=torch.float32)
+            dtype = self.dtype if self.dtype is not None else torch.bfloat16
+        else:
+            dtype = weight.dtype if self.dtype is None else self.dtype
+            assert dtype in _FLOAT_DTYPES, "Invalid weight dtype, should be floating point."
+            w = torch.zeros((nb * B, kb * B), dtype=torch.float32, device=self.device)
+            w[:out_features, :in_features] = weight.to(dtype=torch.float32, device=self.device)
+            blocks = w.view(nb, B, kb, B)
+            scales = (blocks.abs().amax(dim=(1, 3)) / info.max).clamp_(min=1e-6)             # [N/B, K/B]
+            W_q = (blocks / scales[:, None, :, None]).clamp_(min=info.min, max=info.max)
+            W_q = W_q.to(w_dtype) if w_dtype.is_floating_point else W_q.round_().to(w_dtype)
+            W_q = W_q.view(nb * B, kb * B)[:out_features, :in_features].contiguous()
+        bias = bias.to(device=self.device, dtype=dtype) if bias is not None else None
+        layer = GemLiteLinear(8, group_size=in_features, in_features=in_features, out_features=out_features,
+                              input_dtype=input_dtype, output_dtype=TORCH_TO_DTYPE[dtype], acc_dtype=DType.FP32, scaled_activations=True)
+        layer.pack(W_q, torch.ones((out_features, 1), dtype=torch.float32, device=self.device), zeros=None, bias=bias)
+        # the block scales replace the placeholder: [K/B, N/B] fp32, block row of k first
+        layer.scales = torch.nn.Parameter(scales.t().contiguous(), requires_grad=False)
+        layer.meta_dtype = DType.FP32
+        layer.W_group_mode, layer.channel_scale_mode = 0, 5
         return layer
 
     def from_linear(self, linear_layer, del_orig=True):

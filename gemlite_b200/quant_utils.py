@@ -228,5 +228,37 @@ def scale_activations_nvfp4(tensor: Tensor, meta_scale=None, scale_layout: int =
     return q, scales, meta_out
 
 
-def scale_activations_per_block(tensor: Tensor, w_dtype: torch.dtype, block_size: int = 128):
-    raise NotImplementedError("128-wide block activation quantisation (channel_scale_mode 5) is not implemented")
+BLOCK_QUANT_SIZE = 128   # gemlite/triton_kernels/config.py
+
+
+def scale_activations_per_block(tensor: Tensor, w_dtype: torch.dtype, block_size: int = BLOCK_QUANT_SIZE) -> Tuple[Tensor, Tensor]:
+    """One scale per row and per 128 consecutive k (the activation side of 128 x 128 block quantisation): returns
+    (q like tensor, scales fp32 [M, K / 128]).  Replaces scale_activations_per_block (gemlite/quant_utils.py:2504-2590)."""
+    if w_dtype not in (torch.float8_e4m3fn, torch.int8):
+        raise NotImplementedError("per-block activation quantisation supports float8_e4m3fn and int8, got %s" % w_dtype)
+    if block_size != BLOCK_QUANT_SIZE:
+        raise NotImplementedError("per-block activation quantisation uses blocks of %d" % BLOCK_QUANT_SIZE)
+    x, shape = _as_2d(tensor)
+    M, K = x.shape
+    assert K % block_size == 0, "K must be divisible by block_size for per-block activation quantization."
+    q = torch.empty((M, K), dtype=w_dtype, device=x.device)
+    scales = torch.empty((M, K // block_size), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().gl_scale_activations_per_block(
+            x.data_ptr(), q.data_ptr(), scales.data_ptr(), M, K, TORCH_TO_DTYPE[x.dtype].value,
+            DType.INT8.value if w_dtype == torch.int8 else DType.FP8.value, _lib.current_stream_ptr(x.device)))
+    return q.view(shape), scales
+
+
+def scale_activations_per_block_torch(tensor: Tensor, w_dtype: torch.dtype, block_size: int = BLOCK_QUANT_SIZE) -> Tuple[Tensor, Tensor]:
+    """The same quantiser in plain torch ops (gemlite/quant_utils.py:2504-2522), the comparison point of the kernel."""
+    lo, hi = get_dtype_range(w_dtype)
+    rows = tensor.to(torch.float32).reshape(-1, tensor.shape[-1])
+    M, K = rows.shape
+    assert K % block_size == 0, "K must be divisible by block_size for per-block activation quantization."
+    t = rows.view(M, K // block_size, block_size)
+    scales = (t.abs().amax(dim=-1) / hi).clamp_(min=1e-6)
+    q = (t / scales.unsqueeze(-1)).clamp_(lo, hi)
+    if not w_dtype.is_floating_point:
+        q = q.round_()
+    return q.to(w_dtype).view(tensor.shape), scales.contiguous()

@@ -212,6 +212,13 @@ GL_API int gl_unpack_over_rows(const void* in, void* out, int64_t rows_packed, i
                         int32_t out_dtype, void* stream);
 
 /* ---- dynamic activation quantisation: gemlite/quant_utils.py --------------------------- */
+/* x [M,K] -> q [M,K] (GL_FP8 e4m3 or GL_INT8) + fp32 scales [M, K/128]: one scale per row and 128 consecutive k,
+ * scale = max(amax / qmax, 1e-6), q = clamp(x / scale) cast (FP8) or rounded half away from zero (INT8); K % 128 == 0.
+ * The activation side of 128 x 128 block quantisation (channel_scale_mode 5).  Replaces
+ * scale_activations_per_block, gemlite/quant_utils.py:2504-2590. */
+GL_API int gl_scale_activations_per_block(const void* x, void* q, float* scales, int32_t M, int32_t K,
+                                          int32_t x_dtype, int32_t q_dtype, void* stream);
+
 /* x [M,K] (x_dtype FP16/BF16/FP32) -> q [M,K] (q_dtype GL_FP8 e4m3 or GL_INT8) + fp32
  * scales [M]; s = max(amax/qmax, 1e-6), q = clamp(x/s) (rounded for int8).
  * Replaces scale_activations_per_token (v3 kernel), gemlite/quant_utils.py:459-539. */

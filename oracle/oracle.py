@@ -216,6 +216,58 @@ def scale_activations_per_token(x, qdtype="fp8"):
     return r.astype(np.int8), s
 
 
+def scale_activations_per_block(x, qdtype="fp8", block=128):
+    """gemlite/quant_utils.py:2504-2522 / 2613-2675: one scale per row and per `block` consecutive k,
+    s = max(amax/qmax, 1e-6); q = clamp(x / s); int8 rounds half away from zero (libdevice.round in the active kernel).
+    x [M, K] fp32 numpy, K % block == 0.  Returns (q bytes / int8 [M, K], s fp32 [M, K/block])."""
+    x = np.asarray(x, dtype=np.float32)
+    M, K = x.shape
+    assert K % block == 0
+    qmax, qmin = (np.float32(448.0), np.float32(-448.0)) if qdtype == "fp8" else (np.float32(127.0), np.float32(-128.0))
+    g = x.reshape(M, K // block, block)
+    s = np.maximum(np.abs(g).max(axis=-1) / qmax, np.float32(1e-6)).astype(np.float32)
+    t = np.clip((g / s[..., None]).astype(np.float32), qmin, qmax).reshape(M, K)
+    if qdtype == "fp8":
+        return e4m3_encode(t), s
+    r = np.where(t >= 0, np.floor(t + np.float32(0.5)), np.ceil(t - np.float32(0.5)))
+    return r.astype(np.int8), s
+
+
+def quantize_block_weights(W, qdtype="fp8", block=128):
+    """gemlite/helper.py:556-575: 128 x 128 blocks of W [N, K] (zero-padded at the edges), one fp32 scale per block,
+    s = max(amax/qmax, 1e-6), q = clamp(W / s) cast (fp8) or rounded half to even (int8, torch.round).
+    Returns (q bytes / int8 [N, K], s fp32 [ceil(N/block), ceil(K/block)])."""
+    W = np.asarray(W, dtype=np.float32)
+    N, K = W.shape
+    nb, kb = -(-N // block), -(-K // block)
+    Wp = np.zeros((nb * block, kb * block), dtype=np.float32)
+    Wp[:N, :K] = W
+    g = Wp.reshape(nb, block, kb, block)
+    qmax, qmin = (np.float32(448.0), np.float32(-448.0)) if qdtype == "fp8" else (np.float32(127.0), np.float32(-128.0))
+    s = np.maximum(np.abs(g).max(axis=(1, 3)) / qmax, np.float32(1e-6)).astype(np.float32)
+    t = np.clip((g / s[:, None, :, None]).astype(np.float32), qmin, qmax).reshape(nb * block, kb * block)[:N, :K]
+    if qdtype == "fp8":
+        return e4m3_encode(t), s
+    return np.rint(t).astype(np.int8), s
+
+
+def matmul_block_quant(xq, sx, wq, sw, qdtype="fp8", block=128, bias=None):
+    """channel_scale_mode 5 (gemlite/triton_kernels/gemm_kernels.py:396-450): for every block kb of `block` k,
+    out[m, n] += (sum_{k in kb} x[m, k] * w[n, k]) * sx[m, kb] * sw[n // block, kb].  float64 accumulation."""
+    X = e4m3_decode(xq).astype(np.float64) if qdtype == "fp8" else np.asarray(xq, dtype=np.float64)
+    W = e4m3_decode(wq).astype(np.float64) if qdtype == "fp8" else np.asarray(wq, dtype=np.float64)
+    M, K = X.shape
+    N = W.shape[0]
+    out = np.zeros((M, N), dtype=np.float64)
+    sw_n = np.repeat(np.asarray(sw, dtype=np.float64), block, axis=0)[:N]           # [N, K/block]
+    for kb in range(K // block):
+        part = X[:, kb * block:(kb + 1) * block] @ W[:, kb * block:(kb + 1) * block].T
+        out += part * np.asarray(sx, dtype=np.float64)[:, kb:kb + 1] * sw_n[:, kb][None, :]
+    if bias is not None:
+        out = out + np.asarray(bias, dtype=np.float64)
+    return out
+
+
 def scale_activations_mxfp4(x):
     """gemlite/quant_utils.py:2005-2105.  Returns (q uint8 [M, K/2], e8m0 bytes [ceil32(M), K/32])."""
     x = np.asarray(x, dtype=np.float32)

@@ -88,3 +88,15 @@ def baseline_inputs(tag, M):
     W = (torch.randn(N, K, generator=g) * 0.02).to(torch.bfloat16)
     gx = torch.Generator().manual_seed(6500 + 10 * idx + M)
     return torch.randn(M, K, generator=gx).to(torch.bfloat16), W
+
+
+# ---- per-block activation quantiser (tests/golden/block_quant_golden.npz) ----
+GOLDEN_BLOCK_QUANT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "block_quant_golden.npz")
+BLOCK_QUANT_CASES = [(7001, 1, 256), (7002, 5, 512), (7003, 33, 1024)]     # (seed, M, K)
+
+
+def block_quant_input(seed, M, K):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(M, K, generator=g) * 1.5
+    x[0, :128] *= 1e-8                      # a block whose scale hits the 1e-6 floor
+    return x.to(torch.bfloat16)
