@@ -281,7 +281,7 @@ def _forward_impl(
     scales_x, meta_scale = None, None
     # block-scaled fp4 layers: the derived copy of the weight scales as 128x4 scale atoms rides on the scales tensor
     w_atoms = None
-    if _KERNEL_OVERRIDE != 1 and channel_scale_mode == 4 and input_dtype in (DType.MXFP4, DType.NVFP4):
+    if _KERNEL_OVERRIDE != 1 and channel_scale_mode == 4 and input_dtype in (DType.MXFP4, DType.NVFP4, DType.MXFP8):
         w_atoms = _scale_atoms_of(scales)
     sx_layout = 0 if w_atoms is None else 1
     if bool(meta_args[0]) and enable_activation_scaling(x.numel() // x.shape[-1]):
@@ -290,7 +290,7 @@ def _forward_impl(
         elif input_dtype in FP8_INT8_DTYPES:
             x, scales_x = scale_activations_per_token(x, w_dtype=DTYPE_TO_TORCH[input_dtype.value])
         elif input_dtype == DType.MXFP8 and channel_scale_mode == 4:
-            x, scales_x = scale_activations_mxfp8(x, w_dtype=torch.float8_e4m3fn)
+            x, scales_x = scale_activations_mxfp8(x, w_dtype=torch.float8_e4m3fn, scale_layout=sx_layout)
         elif input_dtype == DType.MXFP8 and channel_scale_mode == 2:
             x, scales_x = scale_activations_per_token(x, w_dtype=torch.float8_e4m3fn)
         elif input_dtype == DType.MXFP4 and channel_scale_mode == 4:

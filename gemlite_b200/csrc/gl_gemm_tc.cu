@@ -54,6 +54,7 @@ template <> struct KindTraits<KIND_F8F6F4> { static constexpr int ELEMS_PER_ROW 
 template <> struct KindTraits<KIND_I8>     { static constexpr int ELEMS_PER_ROW = 128; static constexpr int SF_ATOMS = 0; };
 template <> struct KindTraits<KIND_MXF4>   { static constexpr int ELEMS_PER_ROW = 256; static constexpr int SF_ATOMS = 2; };
 template <> struct KindTraits<KIND_NVF4>   { static constexpr int ELEMS_PER_ROW = 256; static constexpr int SF_ATOMS = 4; };
+template <> struct KindTraits<KIND_MXF8>   { static constexpr int ELEMS_PER_ROW = 128; static constexpr int SF_ATOMS = 1; };   // 128 e4m3 per row and stage = 4 groups of 32 = one atom
 
 constexpr uint32_t next_pow2_cols(uint32_t c) { return c <= 32 ? 32 : c <= 64 ? 64 : c <= 128 ? 128 : c <= 256 ? 256 : 512; }
 
@@ -232,7 +233,7 @@ __global__ void __launch_bounds__(192, 1) gl_gemm_tc_kernel(const __grid_constan
   // (measured at M = 4096, 16384²: NVFP4, 12 copies per K tile, 0.79 -> 0.75 ms; MXFP4, 6 copies, is better off with a
   // fourth pipeline stage than with the 9 KB of replicated atoms per stage: 0.59 ms against 0.62 ms)
   // MXFP4 copies only the A-side atoms this way: 5 copies per K tile instead of 6 with a fourth stage still fitting.
-  constexpr bool WIDE_A = MX && BN == 256;
+  constexpr bool WIDE_A = MX && BN == 256 && KT::SF_ATOMS >= 2;
   constexpr bool WIDE_B = KIND == KIND_NVF4 && BN == 256;
   constexpr int REP_A = WIDE_A ? 4 : 1, REP_B = WIDE_B ? 4 : 1;
   constexpr int A_BYTES = 128 * 128, B_BYTES = BN * 128;
@@ -394,6 +395,9 @@ __global__ void __launch_bounds__(192, 1) gl_gemm_tc_kernel(const __grid_constan
             } else if constexpr (KIND == KIND_NVF4) {
               mma_ss_block_scaled<KIND>(d_tmem, da + 2 * j, db + 2 * j, p.idesc,
                                         tmem_base + SFA_COL + j * 4, tmem_base + SFB_COL + j * 4 * NBLK, accum);
+            } else if constexpr (KIND == KIND_MXF8) {      // MMA j covers k 32 j .. 32 j + 31: byte j of the atom's scale words
+              mma_ss_block_scaled<KIND>(d_tmem, da + 2 * j, db + 2 * j, p.idesc | ((uint32_t)j << 29) | ((uint32_t)j << 4),
+                                        tmem_base + SFA_COL, tmem_base + SFB_COL, accum);
             } else {
               mma_ss<KIND>(d_tmem, da + 2 * j, db + 2 * j, p.idesc, accum);
             }
@@ -900,7 +904,7 @@ static int launch_a16_kernel(const CUtensorMap& tmA, const CUtensorMap& tmW, con
   return GL_OK;
 }
 
-enum TcPath { TC_NONE = 0, TC_A16WN, TC_FP8, TC_INT8, TC_MXFP4, TC_NVFP4 };
+enum TcPath { TC_NONE = 0, TC_A16WN, TC_FP8, TC_INT8, TC_MXFP4, TC_NVFP4, TC_MXFP8 };
 
 static TcPath classify(const gl_matmul_args* a) {
   if (a->M < 1) return TC_NONE;
@@ -926,6 +930,13 @@ static TcPath classify(const gl_matmul_args* a) {
     if (need_s && ((uintptr_t)a->scales & 15)) return TC_NONE;
     if (need_z && !a->zero_is_scalar && ((uintptr_t)a->zeros & 15)) return TC_NONE;
     return TC_A16WN;
+  }
+  // MXFP8 with block-scaled activations (A8W8_MXFP_dynamic): e4m3 x e4m3, e8m0 scale per 32 on both sides, given as atoms
+  if (a->input_dtype == GL_MXFP8 && a->x_dtype == GL_FP8 && a->w_dtype == GL_FP8 && e == 1 && a->W_nbits == 8 && a->channel_scale_mode == 4 &&
+      a->w_stride_k == 1 && a->w_stride_n == a->K && a->K % 128 == 0 && a->group_size == 32) {
+    if (a->w_scales_atoms == nullptr || a->scales_x == nullptr || a->sx_layout != 1) return TC_NONE;
+    if (((uintptr_t)a->w_scales_atoms & 15) || ((uintptr_t)a->scales_x & 15)) return TC_NONE;
+    return TC_MXFP8;
   }
   // A8W8: e4m3 x e4m3 or int8 x int8, weights [N, K] with K contiguous, optional per-token / per-channel scales
   if (e == 1 && a->W_nbits == 8 && a->W_group_mode == 0 && a->w_stride_k == 1 && a->w_stride_n == a->K && a->K % 16 == 0) {
@@ -1106,6 +1117,27 @@ int gl_gemm_tc_launch(const gl_matmul_args* a, cudaStream_t st) {
     if (int rc = gl_make_tmap_2d(&tmB, a->w, 0, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)a->K, 128, (uint32_t)BN, true)) return rc;
     if (path == TC_FP8) return BN == 256 ? launch_tma_kernel<KIND_F8F6F4, 256, 4>(tmA, tmB, p, st) : launch_tma_kernel<KIND_F8F6F4, 128, 6>(tmA, tmB, p, st);
     return BN == 256 ? launch_tma_kernel<KIND_I8, 256, 4>(tmA, tmB, p, st) : launch_tma_kernel<KIND_I8, 128, 6>(tmA, tmB, p, st);
+  }
+  if (path == TC_MXFP8) {
+    // block-scaled fp8: operands as in the FP8 path (128 bytes = 128 values of K per row and stage), one scale atom per stage
+    p.nkt = a->K / 128;
+    p.sf_kblocks = a->K / 32 / 4;
+    p.meta_scale = nullptr;
+    const int bn8 = swap_bn ? swap_bn : 128;             // (256-column tiles copy scale atoms in pairs: not for one atom per stage)
+    p.idesc = gl_idesc_block_scaled(0, 1, 128, bn8);     // formats: e4m3 x e4m3, e8m0 scales
+    if (swap_bn) {
+      p.M = a->N; p.N = a->M; p.swap = 1;
+      p.sfa = reinterpret_cast<const uint8_t*>(a->w_scales_atoms);
+      p.sfb = reinterpret_cast<const uint8_t*>(a->scales_x);
+      if (int rc = gl_make_tmap_2d(&tmA, a->w, 0, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)a->K, 128, 128, true)) return rc;
+      if (int rc = gl_make_tmap_2d(&tmB, a->x, 0, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->K, 128, (uint32_t)swap_bn, true)) return rc;
+      return swap_bn == 16 ? launch_tma_kernel<KIND_MXF8, 16, 8>(tmA, tmB, p, st) : launch_tma_kernel<KIND_MXF8, 32, 8>(tmA, tmB, p, st);
+    }
+    p.sfa = reinterpret_cast<const uint8_t*>(a->scales_x);
+    p.sfb = reinterpret_cast<const uint8_t*>(a->w_scales_atoms);
+    if (int rc = gl_make_tmap_2d(&tmA, a->x, 0, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->K, 128, 128, true)) return rc;
+    if (int rc = gl_make_tmap_2d(&tmB, a->w, 0, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)a->K, 128, 128, true)) return rc;
+    return launch_tma_kernel<KIND_MXF8, 128, 6>(tmA, tmB, p, st);
   }
   // block-scaled fp4
   const int gs = path == TC_MXFP4 ? 32 : 16;

@@ -163,7 +163,7 @@ __device__ __forceinline__ uint64_t smem_desc_sf2(uint32_t saddr, uint32_t chunk
   return (uint64_t)((saddr >> 4) & 0x3FFFu) | ((uint64_t)((chunk_stride >> 4) & 0x3FFFu) << 16) | (8ull << 32) | (1ull << 46);
 }
 
-enum MmaKind { KIND_F16 = 0, KIND_F8F6F4 = 1, KIND_I8 = 2, KIND_MXF4 = 3, KIND_NVF4 = 4 };
+enum MmaKind { KIND_F16 = 0, KIND_F8F6F4 = 1, KIND_I8 = 2, KIND_MXF4 = 3, KIND_NVF4 = 4, KIND_MXF8 = 5 };
 
 template <int KIND>
 __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
@@ -203,6 +203,10 @@ __device__ __forceinline__ void mma_ss_block_scaled(uint32_t d_tmem, uint64_t ad
   if constexpr (KIND == KIND_MXF4)
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                  "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+                 ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
+  else if constexpr (KIND == KIND_MXF8)      // e4m3 operands, one e8m0 scale per 32 k = per MMA (K = 32)
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
                  ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
   else
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"

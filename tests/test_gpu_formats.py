@@ -136,6 +136,42 @@ def test_weight_only_fp4_decode_kernel(lib, which, dtype):
             assert rel_fro(yn, want) < (0.2 if "W4" in which else 0.06)
 
 
+@pytest.mark.parametrize("M", [1, 3, 16, 33, 100, 300, 1300])       # 1300 rows: 176 tiles, more than one per CTA
+def test_a8w8_mxfp8_block_scaled_tensor_core(lib, M):
+    """MXFP8 activations x MXFP8 weights with block scales on both sides (A8W8_MXFP_dynamic, post_scale=False; the
+    reference's test: tests/test_mxfp.py:73-92) run on the tcgen05 kernel (kind::mxf8f6f4 with e8m0 scale atoms); checked
+    against the oracle fed with the identical quantised operands and against the general kernel."""
+    import ctypes
+    from gemlite_b200 import core, helper, _lib, quant_utils as qu
+    N, K = 2048, 4224                                                           # 33 K tiles of 128, 132 scale groups
+    g = torch.Generator().manual_seed(970 + M)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    lin = torch.nn.Linear(K, N, bias=False, dtype=torch.bfloat16)
+    lin.weight.data = (torch.randn(N, K, generator=g) / 10.0 / (K ** 0.5) * 8).to(torch.bfloat16)
+    W = lin.weight.data.clone()
+    layer = helper.A8W8_MXFP_dynamic(device="cuda:0", dtype=torch.bfloat16, post_scale=False).from_linear(lin.cuda())
+    assert (layer.W_group_mode, layer.channel_scale_mode) == (0, 4)
+    xd = x.cuda()
+    xq, sx = qu.scale_activations_mxfp8(xd, scale_layout=1)
+    out = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    a = core._fill_args(xq.view(M, K), layer.bias, layer.W_q, layer.scales, layer.zeros, sx, None, out, layer.get_meta_args(), -1,
+                        core._scale_atoms_of(layer.scales), 1)
+    assert _lib.lib().gl_matmul_kernel_name(ctypes.byref(a)).decode() == "gl_gemm_tc_kernel"
+    y = layer(xd).float().cpu().numpy()
+    xq_o, sx_o = oracle.scale_activations_mxfp8(x.float().numpy())
+    wq = layer.W_q.t().contiguous().view(torch.uint8).cpu().numpy()
+    sw = layer.scales.contiguous().view(torch.uint8).cpu().numpy()
+    want_q = oracle.matmul_mx(xq_o, sx_o, wq, sw, 32, x_is_fp4=False, w_is_fp4=False)
+    assert rel_fro(y, want_q) < 5e-3, (M, rel_fro(y, want_q))
+    core.set_kernel_override(1)
+    try:
+        yg = layer(xd).float().cpu().numpy()
+    finally:
+        core.set_kernel_override(0)
+    assert rel_fro(y, yg) < 5e-3
+    assert rel_fro(y, (x.double() @ W.double().T).numpy()) < 0.06
+
+
 @pytest.mark.parametrize("fmt", ["mxfp4", "nvfp4"])
 @pytest.mark.parametrize("M", [1, 3, 16, 64, 100])
 def test_a4w4_block_scaled(lib, fmt, M):
