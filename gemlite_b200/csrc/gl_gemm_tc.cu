@@ -851,7 +851,7 @@ template <int KIND, int BN, int STAGES>
 static int launch_tma_kernel(const CUtensorMap& tmA, const CUtensorMap& tmB, const TcParams& p, cudaStream_t st,
                              const CUtensorMap* tmSFA = nullptr, const CUtensorMap* tmSFB = nullptr) {
   using KT = KindTraits<KIND>;
-  constexpr int rep_a = (KT::SF_ATOMS > 0 && BN == 256) ? 4 : 1, rep_b = (KIND == KIND_NVF4 && BN == 256) ? 4 : 1;
+  constexpr int rep_a = (KT::SF_ATOMS >= 2 && BN == 256) ? 4 : 1, rep_b = (KIND == KIND_NVF4 && BN == 256) ? 4 : 1;
   constexpr size_t stage = 128 * 128 + BN * 128 + KT::SF_ATOMS * 512 * (rep_a + rep_b * ((BN + 127) / 128));
   const size_t smem = 1024 + STAGES * stage + (2 * STAGES + 4) * 8 + 32 + 4 * 2 * BN * 4 + 16;
   auto kern = gl_gemm_tc_kernel<KIND, BN, STAGES>;
@@ -1123,7 +1123,7 @@ int gl_gemm_tc_launch(const gl_matmul_args* a, cudaStream_t st) {
     p.nkt = a->K / 128;
     p.sf_kblocks = a->K / 32 / 4;
     p.meta_scale = nullptr;
-    const int bn8 = swap_bn ? swap_bn : 128;             // (256-column tiles copy scale atoms in pairs: not for one atom per stage)
+    const int bn8 = swap_bn ? swap_bn : BN;              // (256-column tiles copy this kind's single atom per operand block one by one)
     p.idesc = gl_idesc_block_scaled(0, 1, 128, bn8);     // formats: e4m3 x e4m3, e8m0 scales
     if (swap_bn) {
       p.M = a->N; p.N = a->M; p.swap = 1;
@@ -1136,8 +1136,8 @@ int gl_gemm_tc_launch(const gl_matmul_args* a, cudaStream_t st) {
     p.sfa = reinterpret_cast<const uint8_t*>(a->scales_x);
     p.sfb = reinterpret_cast<const uint8_t*>(a->w_scales_atoms);
     if (int rc = gl_make_tmap_2d(&tmA, a->x, 0, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->K, 128, 128, true)) return rc;
-    if (int rc = gl_make_tmap_2d(&tmB, a->w, 0, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)a->K, 128, 128, true)) return rc;
-    return launch_tma_kernel<KIND_MXF8, 128, 6>(tmA, tmB, p, st);
+    if (int rc = gl_make_tmap_2d(&tmB, a->w, 0, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)a->K, 128, (uint32_t)BN, true)) return rc;
+    return BN == 256 ? launch_tma_kernel<KIND_MXF8, 256, 4>(tmA, tmB, p, st) : launch_tma_kernel<KIND_MXF8, 128, 6>(tmA, tmB, p, st);
   }
   // block-scaled fp4
   const int gs = path == TC_MXFP4 ? 32 : 16;

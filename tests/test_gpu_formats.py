@@ -136,7 +136,7 @@ def test_weight_only_fp4_decode_kernel(lib, which, dtype):
             assert rel_fro(yn, want) < (0.2 if "W4" in which else 0.06)
 
 
-@pytest.mark.parametrize("M", [1, 3, 16, 33, 100, 300, 1300])       # 1300 rows: 176 tiles, more than one per CTA
+@pytest.mark.parametrize("M", [1, 3, 16, 33, 100, 300, 1300, 3000])   # 1300 rows: 176 tiles of 128 columns, 3000 rows: 192 tiles of 256 columns
 def test_a8w8_mxfp8_block_scaled_tensor_core(lib, M):
     """MXFP8 activations x MXFP8 weights with block scales on both sides (A8W8_MXFP_dynamic, post_scale=False; the
     reference's test: tests/test_mxfp.py:73-92) run on the tcgen05 kernel (kind::mxf8f6f4 with e8m0 scale atoms); checked
