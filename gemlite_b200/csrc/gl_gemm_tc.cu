@@ -46,6 +46,8 @@ struct TcParams {
   const uint8_t* sfa; const uint8_t* sfb; int sf_kblocks;
   // A16Wn
   const void* gscales; const void* gzeros; int group_size; int W_group_mode; int zero_is_scalar;
+  // 128 x 128 block quantisation: fp32 weight scales [K/128][N/128] with these strides (activation scales: scales_x [M][K/128])
+  const float* bq_scales; long long bq_stride_g, bq_stride_n;
 };
 
 template <int KIND> struct KindTraits;
@@ -841,11 +843,132 @@ __global__ void __launch_bounds__((6 + DQW) * 32, DQW == 4 ? 2 : 1) gl_gemm_tc_a
 }
 
 
+// ---- 128 x 128 block quantisation (channel_scale_mode 5): FP8 x FP8 or INT8 x INT8 --------------------------
+// out[m, n] = sum_kb (sum_{k in kb} x[m,k] w[n,k]) * s_x[m, kb] * s_w[kb, n / 128]  (gemm_kernels.py:396-450).  A K tile of
+// 128 bytes is exactly one block, so every K tile's four MMAs start a fresh partial sum in one of two tensor-memory
+// accumulators; the epilogue warps drain it (tcgen05.ld), multiply by the two block scales and add it to the running
+// sums they keep in registers (128 per thread) while the MMAs of the next K tile fill the other accumulator.
+// One 128 x 128 output tile per CTA; both operands by TMA (128-byte swizzle) through a STAGES-deep ring.
+template <bool INT8, int STAGES>
+__global__ void __launch_bounds__(192, 1) gl_gemm_tc_blockq_kernel(const __grid_constant__ CUtensorMap tmA,
+                                                                   const __grid_constant__ CUtensorMap tmB, const TcParams p) {
+  constexpr int A_BYTES = 128 * 128, B_BYTES = 128 * 128, STAGE_BYTES = A_BYTES + B_BYTES, BN = 128;
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;                  // [2] the K tile's partial sum is complete
+  uint64_t* acc_empty = acc_full + 2;                   // [2] ... and has been drained by the four epilogue warps
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  float* sw_s = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(tmem_slot + 1) + 15) & ~(uintptr_t)15);
+  float* b_s = sw_s + BN;
+  __shared__ int s_abort;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (p.M + 127) / 128;
+  const int m0 = (blockIdx.x % tiles_m) * 128, n0 = (blockIdx.x / tiles_m) * BN;
+  stage_epilogue_consts(p, sw_s, b_s, n0, BN);          // bias (no channel scale in this mode: sw_s = 1)
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(acc_full + b, 1); mbar_init(acc_empty + b, kNumEpiWarps); }
+    fence_barrier_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 256);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  gl_launch_dependents();
+  if (warp == 0) {
+    if (lane == 0) {
+      gl_grid_dependency_wait();
+      for (int kt = 0; kt < p.nkt; ++kt) {
+        const int s = kt % STAGES;
+        if (!mbar_wait(empty + s, (uint32_t)(((kt / STAGES) & 1) ^ 1), &s_abort, p.status, 2)) break;
+        unsigned char* st = smem + s * STAGE_BYTES;
+        mbar_expect_tx(full + s, A_BYTES + B_BYTES);
+        tma_load_2d(st, &tmA, full + s, kt * 128, m0);
+        tma_load_2d(st + A_BYTES, &tmB, full + s, kt * 128, n0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int kt = 0; kt < p.nkt && ok; ++kt) {
+        const int s = kt % STAGES, ab = kt & 1;
+        if (!mbar_wait(acc_empty + ab, (uint32_t)(((kt >> 1) & 1) ^ 1), &s_abort, p.status, 6) ||
+            !mbar_wait(full + s, (uint32_t)((kt / STAGES) & 1), &s_abort, p.status, 3)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+        const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sa + A_BYTES);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) mma_ss<INT8 ? KIND_I8 : KIND_F8F6F4>(tmem_base + (uint32_t)(ab * BN), da + 2 * j, db + 2 * j, p.idesc, j > 0 ? 1u : 0u);
+        tc_commit(empty + s);
+        tc_commit(acc_full + ab);
+      }
+    }
+  } else {
+    gl_grid_dependency_wait();
+    const int quad = warp & 3;
+    const int m = m0 + quad * 32 + lane;
+    const int kblocks = p.K / 128;
+    float acc[BN];
+#pragma unroll
+    for (int i = 0; i < BN; ++i) acc[i] = 0.f;
+    bool ok = true;
+    for (int kt = 0; kt < p.nkt && ok; ++kt) {
+      const int ab = kt & 1;
+      // the two block scales of this K tile: requested before the wait
+      const float sx = m < p.M ? p.scales_x[(size_t)m * kblocks + kt] : 0.f;
+      const float sc = sx * p.bq_scales[(long long)kt * p.bq_stride_g + (long long)(n0 >> 7) * p.bq_stride_n];
+      if (!mbar_wait(acc_full + ab, (uint32_t)((kt >> 1) & 1), &s_abort, p.status, 4)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t rr[32];
+        tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ab * BN + c0), rr);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) acc[c0 + i] = fmaf(INT8 ? (float)(int32_t)rr[i] : __uint_as_float(rr[i]), sc, acc[c0 + i]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty + ab);
+    }
+    if (ok && m < p.M) {
+#pragma unroll
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        if (n0 + c0 >= p.N) break;
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = acc[c0 + i];
+        finish_row_chunk(p, m, n0 + c0, v, 1.f, sw_s + c0, b_s + c0);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, 256);
+}
+
 template <typename K>
 static int set_smem(K kern, size_t smem) {
   GL_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   return GL_OK;
 }
+
+template <bool INT8>
+static int launch_blockq_kernel(const CUtensorMap& tmA, const CUtensorMap& tmB, const TcParams& p, cudaStream_t st) {
+  constexpr int STAGES = 6;
+  const size_t smem = 1024 + STAGES * (2 * 128 * 128) + (2 * STAGES + 4) * 8 + 32 + 2 * 128 * 4 + 16;
+  auto kern = gl_gemm_tc_blockq_kernel<INT8, STAGES>;
+  if (int rc = set_smem(kern, smem)) return rc;
+  const int tiles = ((p.M + 127) / 128) * ((p.N + 127) / 128);
+  GL_CUDA_CHECK(gl_launch_pdl(kern, dim3(tiles), dim3(192), smem, st, tmA, tmB, p));
+  return GL_OK;
+}
+
 
 template <int KIND, int BN, int STAGES>
 static int launch_tma_kernel(const CUtensorMap& tmA, const CUtensorMap& tmB, const TcParams& p, cudaStream_t st,
@@ -904,13 +1027,21 @@ static int launch_a16_kernel(const CUtensorMap& tmA, const CUtensorMap& tmW, con
   return GL_OK;
 }
 
-enum TcPath { TC_NONE = 0, TC_A16WN, TC_FP8, TC_INT8, TC_MXFP4, TC_NVFP4, TC_MXFP8 };
+enum TcPath { TC_NONE = 0, TC_A16WN, TC_FP8, TC_INT8, TC_MXFP4, TC_NVFP4, TC_MXFP8, TC_BLOCKQ_FP8, TC_BLOCKQ_INT8 };
 
 static TcPath classify(const gl_matmul_args* a) {
   if (a->M < 1) return TC_NONE;
   if (((uintptr_t)a->x & 15) || ((uintptr_t)a->w & 15) || ((uintptr_t)a->out & 15)) return TC_NONE;
   if (!(a->out_dtype == GL_BF16 || a->out_dtype == GL_FP16 || a->out_dtype == GL_FP32)) return TC_NONE;
-  if (a->channel_scale_mode == 5) return TC_NONE;
+  // 128 x 128 block quantisation: e4m3 x e4m3 or int8 x int8, fp32 block scales on both sides; more than 16 rows (below
+  // that the general kernel's one pass over the weights is shorter than a 128-row tile's pipeline)
+  if (a->channel_scale_mode == 5) {
+    if (a->M <= 16 || a->elements_per_sample != 1 || a->W_nbits != 8 || a->W_group_mode != 0 || a->w_stride_k != 1 || a->w_stride_n != a->K ||
+        a->K % 128 != 0 || a->scales == nullptr || a->scales_x == nullptr || a->meta_dtype != GL_FP32) return TC_NONE;
+    if (a->x_dtype == GL_FP8 && a->w_dtype == GL_FP8 && a->input_dtype == GL_FP8) return TC_BLOCKQ_FP8;
+    if (a->x_dtype == GL_INT8 && a->w_dtype == GL_INT8 && a->input_dtype == GL_INT8) return TC_BLOCKQ_INT8;
+    return TC_NONE;
+  }
   const int e = a->elements_per_sample;
   // A16Wn: fp16 / bf16 activations, 4- or 2-bit codes packed in int32 along K, group-wise meta data
   if ((a->x_dtype == GL_BF16 || a->x_dtype == GL_FP16) && a->input_dtype == a->x_dtype && a->w_dtype == GL_INT32 &&
@@ -1096,6 +1227,16 @@ int gl_gemm_tc_launch(const gl_matmul_args* a, cudaStream_t st) {
     if (a->W_nbits == 2) return GL_A16(__half, 2);
     return GL_A16(__half, 1);
 #undef GL_A16
+  }
+  if (path == TC_BLOCKQ_FP8 || path == TC_BLOCKQ_INT8) {
+    p.nkt = a->K / 128;
+    p.idesc = (path == TC_BLOCKQ_FP8) ? gl_idesc(1, 0, 0, 128, 128) : gl_idesc(2, 1, 1, 128, 128);
+    p.scales_x = reinterpret_cast<const float*>(a->scales_x);
+    p.bq_scales = reinterpret_cast<const float*>(a->scales);
+    p.bq_stride_g = a->s_stride_g; p.bq_stride_n = a->s_stride_n;
+    if (int rc = gl_make_tmap_2d(&tmA, a->x, 0, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->K, 128, 128, true)) return rc;
+    if (int rc = gl_make_tmap_2d(&tmB, a->w, 0, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)a->K, 128, 128, true)) return rc;
+    return path == TC_BLOCKQ_FP8 ? launch_blockq_kernel<false>(tmA, tmB, p, st) : launch_blockq_kernel<true>(tmA, tmB, p, st);
   }
   if (path == TC_FP8 || path == TC_INT8) {
     p.nkt = (a->K + 127) / 128;

@@ -29,6 +29,15 @@ def test_per_block_quantiser_matches_oracle_and_golden(lib):
             assert np.array_equal(st.numpy(), so)
 
 
+def _kernel_name(layer, x, fp8):
+    import ctypes
+    from gemlite_b200 import core, quant_utils as qu, _lib
+    xq, sx = qu.scale_activations_per_block(x, torch.float8_e4m3fn if fp8 else torch.int8)
+    out = torch.empty((x.shape[0], layer.out_features), dtype=x.dtype, device="cuda")
+    a = core._fill_args(xq, layer.bias, layer.W_q, layer.scales, layer.zeros, sx, None, out, layer.get_meta_args(), -1)
+    return _lib.lib().gl_matmul_kernel_name(ctypes.byref(a)).decode()
+
+
 @pytest.mark.parametrize("fp8", [True, False])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_block_quant_layer(lib, fp8, dtype):
@@ -51,9 +60,11 @@ def test_block_quant_layer(lib, fp8, dtype):
         wq = layer.W_q.t().contiguous()
         wq = wq.view(torch.uint8).cpu().numpy() if fp8 else wq.cpu().numpy()
         assert (wq != wq_o).mean() < 5e-3
-        for M in (1, 3, 16, 65, 130):
+        for M in (1, 3, 16, 17, 65, 130, 300):
             x = (torch.randn(M, K, generator=g) / 10.0).to(dtype)
             y = layer(x.cuda()).float().cpu().numpy()
+            # more than 16 rows: the tensor-core kernel (one partial sum per K tile, scaled into register accumulators)
+            assert _kernel_name(layer, x.cuda(), fp8) == ("gl_gemm_tc_kernel" if M > 16 else "gl_generic_kernel")
             xq, sx = oracle.scale_activations_per_block(x.float().numpy(), kind)
             want_q = oracle.matmul_block_quant(xq, sx, wq, layer.scales.t().cpu().numpy(), kind, bias=bias.double().numpy())
             assert rel_fro(y, want_q) < 5e-3, (N, K, M, rel_fro(y, want_q))
