@@ -847,12 +847,16 @@ __global__ void __launch_bounds__((6 + DQW) * 32, DQW == 4 ? 2 : 1) gl_gemm_tc_a
 // out[m, n] = sum_kb (sum_{k in kb} x[m,k] w[n,k]) * s_x[m, kb] * s_w[kb, n / 128]  (gemm_kernels.py:396-450).  A K tile of
 // 128 bytes is exactly one block, so every K tile's four MMAs start a fresh partial sum in one of two tensor-memory
 // accumulators; the epilogue warps drain it (tcgen05.ld), multiply by the two block scales and add it to the running
-// sums they keep in registers (128 per thread) while the MMAs of the next K tile fill the other accumulator.
-// One 128 x 128 output tile per CTA; both operands by TMA (128-byte swizzle) through a STAGES-deep ring.
-template <bool INT8, int STAGES>
-__global__ void __launch_bounds__(192, 1) gl_gemm_tc_blockq_kernel(const __grid_constant__ CUtensorMap tmA,
+// sums they keep in registers while the MMAs of the next K tile fill the other accumulator.  Eight epilogue warps: a
+// warp owns one 32-row quadrant and one half of the columns.
+// One 128 x BN output tile per CTA (BN = 256: two weight blocks side by side, each column half with its own block scale;
+// a K tile then moves 48 KB through shared memory for twice the arithmetic of the 32 KB of BN = 128); both operands by
+// TMA (128-byte swizzle) through a STAGES-deep ring.
+constexpr int kBlockqEpiWarps = 8;
+template <bool INT8, int BN, int STAGES>
+__global__ void __launch_bounds__(64 + 32 * kBlockqEpiWarps, 1) gl_gemm_tc_blockq_kernel(const __grid_constant__ CUtensorMap tmA,
                                                                    const __grid_constant__ CUtensorMap tmB, const TcParams p) {
-  constexpr int A_BYTES = 128 * 128, B_BYTES = 128 * 128, STAGE_BYTES = A_BYTES + B_BYTES, BN = 128;
+  constexpr int A_BYTES = 128 * 128, B_BYTES = BN * 128, STAGE_BYTES = A_BYTES + B_BYTES, HALF = BN / 2;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -870,12 +874,12 @@ __global__ void __launch_bounds__(192, 1) gl_gemm_tc_blockq_kernel(const __grid_
   if (threadIdx.x == 0) {
     s_abort = 0;
     for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(acc_full + b, 1); mbar_init(acc_empty + b, kNumEpiWarps); }
+    for (int b = 0; b < 2; ++b) { mbar_init(acc_full + b, 1); mbar_init(acc_empty + b, kBlockqEpiWarps); }
     fence_barrier_init();
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
   }
-  if (warp == 1) tmem_alloc(tmem_slot, 256);
+  if (warp == 1) tmem_alloc(tmem_slot, 2 * BN);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -898,8 +902,8 @@ __global__ void __launch_bounds__(192, 1) gl_gemm_tc_blockq_kernel(const __grid_
       bool ok = true;
       for (int kt = 0; kt < p.nkt && ok; ++kt) {
         const int s = kt % STAGES, ab = kt & 1;
-        if (!mbar_wait(acc_empty + ab, (uint32_t)(((kt >> 1) & 1) ^ 1), &s_abort, p.status, 6) ||
-            !mbar_wait(full + s, (uint32_t)((kt / STAGES) & 1), &s_abort, p.status, 3)) { ok = false; break; }
+        if (!mbar_wait_spin(acc_empty + ab, (uint32_t)(((kt >> 1) & 1) ^ 1), &s_abort, p.status, 6) ||
+            !mbar_wait_spin(full + s, (uint32_t)((kt / STAGES) & 1), &s_abort, p.status, 3)) { ok = false; break; }
         tc_fence_after();
         const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
         const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sa + A_BYTES);
@@ -911,45 +915,69 @@ __global__ void __launch_bounds__(192, 1) gl_gemm_tc_blockq_kernel(const __grid_
     }
   } else {
     gl_grid_dependency_wait();
-    const int quad = warp & 3;
+    const int quad = warp & 3, cb = ((warp - 2) >> 2) * HALF;   // TMEM lane quadrant and first column of this warp
     const int m = m0 + quad * 32 + lane;
     const int kblocks = p.K / 128;
-    float acc[BN];
+    float acc[HALF];
 #pragma unroll
-    for (int i = 0; i < BN; ++i) acc[i] = 0.f;
+    for (int i = 0; i < HALF; ++i) acc[i] = 0.f;
     bool ok = true;
+    // the two block scales of a K tile are requested one K tile ahead: their latency is off the accumulator hand-over
+    const float* sxp = p.scales_x + (size_t)(m < p.M ? m : 0) * kblocks;
+    const int nblk = min((n0 + cb) >> 7, (p.N - 1) >> 7);           // (a column half past N computes and stores nothing)
+    const float* swp = p.bq_scales + (long long)nblk * p.bq_stride_n;
+    float sx_n = sxp[0], sw_n = swp[0];
     for (int kt = 0; kt < p.nkt && ok; ++kt) {
       const int ab = kt & 1;
-      // the two block scales of this K tile: requested before the wait
-      const float sx = m < p.M ? p.scales_x[(size_t)m * kblocks + kt] : 0.f;
-      const float sc = sx * p.bq_scales[(long long)kt * p.bq_stride_g + (long long)(n0 >> 7) * p.bq_stride_n];
-      if (!mbar_wait(acc_full + ab, (uint32_t)((kt >> 1) & 1), &s_abort, p.status, 4)) { ok = false; break; }
+      const float sc = (m < p.M ? sx_n : 0.f) * sw_n;
+      if (kt + 1 < p.nkt) { sx_n = sxp[kt + 1]; sw_n = swp[(long long)(kt + 1) * p.bq_stride_g]; }
+      if (!mbar_wait_spin(acc_full + ab, (uint32_t)((kt >> 1) & 1), &s_abort, p.status, 4)) { ok = false; break; }
       tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ab * BN + cb);
+      if constexpr (HALF == 64) {                            // both loads in flight, the buffer handed back before the arithmetic
+        uint32_t r0[32], r1[32];
+        tmem_ld_32x32_issue(taddr, r0);
+        tmem_ld_32x32_issue(taddr + 32, r1);
+        tmem_ld_wait();
+        tmem_ld_fence(r0);
+        tmem_ld_fence(r1);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty + ab);
 #pragma unroll
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t rr[32];
-        tmem_ld_32x32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ab * BN + c0), rr);
+        for (int i = 0; i < 32; ++i) {
+          acc[i] = fmaf(INT8 ? (float)(int32_t)r0[i] : __uint_as_float(r0[i]), sc, acc[i]);
+          acc[32 + i] = fmaf(INT8 ? (float)(int32_t)r1[i] : __uint_as_float(r1[i]), sc, acc[32 + i]);
+        }
+      } else {                                               // 128 columns: 32 at a time (registers)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) acc[c0 + i] = fmaf(INT8 ? (float)(int32_t)rr[i] : __uint_as_float(rr[i]), sc, acc[c0 + i]);
+        for (int c0 = 0; c0 < HALF; c0 += 32) {
+          uint32_t rr[32];
+          tmem_ld_32x32(taddr + c0, rr);
+          if (c0 + 32 == HALF) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty + ab);
+          }
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[c0 + i] = fmaf(INT8 ? (float)(int32_t)rr[i] : __uint_as_float(rr[i]), sc, acc[c0 + i]);
+        }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(acc_empty + ab);
     }
     if (ok && m < p.M) {
 #pragma unroll
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        if (n0 + c0 >= p.N) break;
+      for (int c0 = 0; c0 < HALF; c0 += 32) {
+        if (n0 + cb + c0 >= p.N) break;
         float v[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = acc[c0 + i];
-        finish_row_chunk(p, m, n0 + c0, v, 1.f, sw_s + c0, b_s + c0);
+        finish_row_chunk(p, m, n0 + cb + c0, v, 1.f, sw_s + cb + c0, b_s + cb + c0);
       }
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, 256);
+  if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
 }
 
 template <typename K>
@@ -958,14 +986,13 @@ static int set_smem(K kern, size_t smem) {
   return GL_OK;
 }
 
-template <bool INT8>
+template <bool INT8, int BN, int STAGES>
 static int launch_blockq_kernel(const CUtensorMap& tmA, const CUtensorMap& tmB, const TcParams& p, cudaStream_t st) {
-  constexpr int STAGES = 6;
-  const size_t smem = 1024 + STAGES * (2 * 128 * 128) + (2 * STAGES + 4) * 8 + 32 + 2 * 128 * 4 + 16;
-  auto kern = gl_gemm_tc_blockq_kernel<INT8, STAGES>;
+  const size_t smem = 1024 + STAGES * (128 * 128 + BN * 128) + (2 * STAGES + 4) * 8 + 32 + 2 * BN * 4 + 16;
+  auto kern = gl_gemm_tc_blockq_kernel<INT8, BN, STAGES>;
   if (int rc = set_smem(kern, smem)) return rc;
-  const int tiles = ((p.M + 127) / 128) * ((p.N + 127) / 128);
-  GL_CUDA_CHECK(gl_launch_pdl(kern, dim3(tiles), dim3(192), smem, st, tmA, tmB, p));
+  const int tiles = ((p.M + 127) / 128) * ((p.N + BN - 1) / BN);
+  GL_CUDA_CHECK(gl_launch_pdl(kern, dim3(tiles), dim3(64 + 32 * kBlockqEpiWarps), smem, st, tmA, tmB, p));
   return GL_OK;
 }
 
@@ -1230,13 +1257,18 @@ int gl_gemm_tc_launch(const gl_matmul_args* a, cudaStream_t st) {
   }
   if (path == TC_BLOCKQ_FP8 || path == TC_BLOCKQ_INT8) {
     p.nkt = a->K / 128;
-    p.idesc = (path == TC_BLOCKQ_FP8) ? gl_idesc(1, 0, 0, 128, 128) : gl_idesc(2, 1, 1, 128, 128);
+    // 256-column tiles when they still give every SM a tile ("tile_n" in the cache entry overrides)
+    const int bq_req = tc_cfg_int(a, "tile_n", 0);
+    int bq_bn = (a->N >= 256 && (int64_t)((a->M + 127) / 128) * ((a->N + 255) / 256) >= gl_num_sms()) ? 256 : 128;
+    if ((bq_req == 128 || bq_req == 256) && a->N >= bq_req) bq_bn = bq_req;
+    p.idesc = (path == TC_BLOCKQ_FP8) ? gl_idesc(1, 0, 0, 128, bq_bn) : gl_idesc(2, 1, 1, 128, bq_bn);
     p.scales_x = reinterpret_cast<const float*>(a->scales_x);
     p.bq_scales = reinterpret_cast<const float*>(a->scales);
     p.bq_stride_g = a->s_stride_g; p.bq_stride_n = a->s_stride_n;
     if (int rc = gl_make_tmap_2d(&tmA, a->x, 0, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->K, 128, 128, true)) return rc;
-    if (int rc = gl_make_tmap_2d(&tmB, a->w, 0, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)a->K, 128, 128, true)) return rc;
-    return path == TC_BLOCKQ_FP8 ? launch_blockq_kernel<false>(tmA, tmB, p, st) : launch_blockq_kernel<true>(tmA, tmB, p, st);
+    if (int rc = gl_make_tmap_2d(&tmB, a->w, 0, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)a->K, 128, (uint32_t)bq_bn, true)) return rc;
+    if (bq_bn == 256) return path == TC_BLOCKQ_FP8 ? launch_blockq_kernel<false, 256, 4>(tmA, tmB, p, st) : launch_blockq_kernel<true, 256, 4>(tmA, tmB, p, st);
+    return path == TC_BLOCKQ_FP8 ? launch_blockq_kernel<false, 128, 6>(tmA, tmB, p, st) : launch_blockq_kernel<true, 128, 6>(tmA, tmB, p, st);
   }
   if (path == TC_FP8 || path == TC_INT8) {
     p.nkt = (a->K + 127) / 128;

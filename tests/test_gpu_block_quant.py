@@ -75,6 +75,33 @@ def test_block_quant_layer(lib, fp8, dtype):
             assert float(np.abs(y - want).mean()) < (1.5e-2 if fp8 else 5e-3)
 
 
+@pytest.mark.parametrize("fp8", [True, False])
+def test_block_quant_wide_tiles(lib, fp8):
+    """Enough 128 x 256 tiles for every SM (19 x 8): the 256-column form, two weight blocks per tile with a ragged last
+    one (N = 2032), rows ending inside a tile."""
+    from gemlite_b200 import helper, quant_utils as qu
+    N, K, M = 2032, 1024, 2500
+    kind = "fp8" if fp8 else "int8"
+    g = torch.Generator().manual_seed(7400)
+    W = torch.randn(N, K, generator=g) * 0.05
+    W[128:256] *= 30.0                                      # neighbouring weight blocks with very different scales
+    bias = (torch.randn(N, generator=g) * 0.5).to(torch.bfloat16)
+    wq, sw = oracle.quantize_block_weights(W.numpy(), kind)
+    layer = (helper.A8W8_FP8_dynamic if fp8 else helper.A8W8_INT8_dynamic)(device="cuda:0", dtype=torch.bfloat16, block_quant=True).from_weights(
+        torch.from_numpy(wq).view(torch.float8_e4m3fn) if fp8 else torch.from_numpy(wq), scales=torch.from_numpy(sw), bias=bias)
+    x = (torch.randn(M, K, generator=g) / 10.0).to(torch.bfloat16)
+    x[:, 128:256] *= 50.0                                   # ... and activation blocks likewise
+    assert _kernel_name(layer, x.cuda(), fp8) == "gl_gemm_tc_kernel"
+    y = layer(x.cuda()).float().cpu().numpy()
+    xq, sx = qu.scale_activations_per_block(x.cuda(), torch.float8_e4m3fn if fp8 else torch.int8)
+    xq = xq.view(torch.uint8).cpu().numpy() if fp8 else xq.cpu().numpy()
+    want = oracle.matmul_block_quant(xq, sx.cpu().numpy(), wq, sw, kind, bias=bias.double().numpy())
+    assert rel_fro(y, want) < 5e-3, rel_fro(y, want)
+    for rows in (slice(0, 1), slice(M - 1, M), slice(2432, M)):                    # first, last, the ragged last row tile
+        assert rel_fro(y[rows], want[rows]) < 5e-3
+    assert rel_fro(y[:, 1920:], want[:, 1920:]) < 5e-3 and rel_fro(y[:, 128:256], want[:, 128:256]) < 5e-3
+
+
 def test_block_quant_pre_quantised_weights(lib):
     from gemlite_b200 import helper
     N, K = 256, 512
