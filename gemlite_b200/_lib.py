@@ -147,7 +147,13 @@ def require_cuda(t, what):
             "gemlite_b200: %s must be a CUDA tensor; the kernels are CUDA-only and there is no CPU path." % what)
 
 
+_RAW_STREAM = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def current_stream_ptr(device):
+    """cudaStream_t of torch's current stream on `device` (the raw getter skips building a Stream object per call)."""
+    if _RAW_STREAM is not None and device.index is not None:
+        return _RAW_STREAM(device.index)
     return torch.cuda.current_stream(device).cuda_stream
 
 

@@ -158,10 +158,10 @@ def set_kernel_override(value: int):
 
 
 
-def _workspace(device, nbytes):
+def _workspace(device, nbytes, stream_ptr=None):
     if nbytes == 0:
         return None
-    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    key = (device.index, _lib.current_stream_ptr(device) if stream_ptr is None else stream_ptr)
     ws = _WORKSPACES.get(key)
     if ws is None or ws.numel() < nbytes:
         ws = torch.zeros(max(int(nbytes), 8 << 20), dtype=torch.uint8, device=device)
@@ -642,11 +642,18 @@ class GemLiteLinear(torch.nn.Module):
             cache[key] = ent
         a, need = ent[1], ent[2]
         a.x, a.out = x2d.data_ptr(), out.data_ptr()
-        with torch.cuda.device(x.device):
-            ws = _workspace(x.device, need)
+        sp = _lib.current_stream_ptr(x.device)
+        if torch.cuda.current_device() == x.device.index:      # the usual case: no device switch around the launch
+            ws = _workspace(x.device, need, sp)
             if ws is not None:
                 a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
-            status = L.gl_matmul(ctypes.byref(a), _lib.current_stream_ptr(x.device))
+            status = L.gl_matmul(ctypes.byref(a), sp)
+        else:
+            with torch.cuda.device(x.device):
+                ws = _workspace(x.device, need, sp)
+                if ws is not None:
+                    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+                status = L.gl_matmul(ctypes.byref(a), sp)
         if status != 0:
             msg = L.gl_last_error().decode("utf-8", "replace")
             if status == _lib.GL_E_UNSUPPORTED:
