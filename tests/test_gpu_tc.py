@@ -135,6 +135,38 @@ def test_a8w8_tensor_core(lib, fp8, M):
     assert rel_fro(y, want_q) < 5e-3, rel_fro(y, want_q)
 
 
+@pytest.mark.parametrize("kind", ["fp8", "a16w4"])
+def test_banded_tile_order_for_large_activations(lib, kind):
+    """Activations of 64 MB and more switch the tile numbering to bands of 2048 rows (the last band short, the last row
+    tile ragged): every band's rows and the last columns against the product of the identical operands."""
+    from gemlite_b200 import helper, quant_utils as qu
+    g = torch.Generator(device="cuda").manual_seed(97)
+    if kind == "fp8":
+        N, K, M = 520, 8192, 8192 + 2048 + 77              # 81 row tiles: five bands of 16 and one of 1
+        x = torch.randn(M, K, generator=g, device="cuda", dtype=torch.bfloat16)
+        lin = torch.nn.Linear(K, N, bias=False, dtype=torch.bfloat16, device="cuda")
+        lin.weight.data.normal_(0, 0.02, generator=g)
+        layer = helper.A8W8_FP8_dynamic(device="cuda:0", dtype=torch.bfloat16).from_linear(lin)
+        y = layer(x).float()
+        xq, sx = qu.scale_activations_per_token(x, torch.float8_e4m3fn)
+        rows = torch.cat([torch.arange(0, M, 509, device="cuda"), torch.arange(M - 80, M, device="cuda")])
+        want = (xq[rows].float() @ layer.W_q.float()) * sx[rows].view(-1, 1) * layer.scales.float().view(1, -1)
+    else:
+        N, K, M = 1024, 8192, 4096 + 300                    # 256-row tiles (two accumulators): bands of 8, 18 row tiles
+        x0, W_q, s, z, b = make_a16wn(N, K, 4, 128, torch.bfloat16, seed=98, M=1)
+        x = torch.randn(M, K, generator=g, device="cuda", dtype=torch.bfloat16)
+        layer = helper.A16W4_HQQ_INT(device="cuda:0", dtype=torch.bfloat16).from_weights(W_q.cuda(), s.cuda(), z.cuda(), bias=b.cuda())
+        y = layer(x).float()
+        rows = torch.cat([torch.arange(0, M, 211, device="cuda"), torch.arange(M - 80, M, device="cuda")])
+        Wd = ((W_q.double().view(N, -1, 128) - z.view(N, -1).double()[..., None]) * s.view(N, -1).double()[..., None]).view(N, K).float().cuda()
+        want = x[rows].float() @ Wd.T + b.float().cuda()
+    assert _status_word() == 0
+    got = y[rows]
+    assert float((got - want).norm() / want.norm()) < (5e-3 if kind == "fp8" else 1e-2)
+    assert float((got[:, -40:] - want[:, -40:]).norm() / want[:, -40:].norm()) < 1e-2
+    assert float((got[-1] - want[-1]).norm() / want[-1].norm()) < 1e-2
+
+
 @pytest.mark.parametrize("fmt", ["mxfp4", "nvfp4"])
 @pytest.mark.parametrize("M", [1, 16, 100, 300])
 @pytest.mark.parametrize("N,K", [(2048, 4224), (384, 1024)])
