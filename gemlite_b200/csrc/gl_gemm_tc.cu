@@ -49,6 +49,9 @@ struct TcParams {
   // 128 x 128 block quantisation: fp32 weight scales [K/128][N/128] with these strides (activation scales: scales_x [M][K/128])
   const float* bq_scales; long long bq_stride_g, bq_stride_n;
   int band;   // row tiles per band of the tile order (0: one band)
+  // A16Wn, a launch over part of the tiles: grid_tiles CTAs along x (0: all tiles); tail = 1: CTA t is column half t & 1
+  // of the twice as wide tile tile_base + t / 2 (the tiles that a last, partly filled wave would have run)
+  int grid_tiles, tile_base, tail;
 };
 
 template <int KIND> struct KindTraits;
@@ -581,8 +584,14 @@ __global__ void __launch_bounds__((6 + DQW) * 32, DQW == 4 ? 2 : 1) gl_gemm_tc_a
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = SW ? 1 : (p.M + 128 * AM - 1) / (128 * AM);
   int mt, nt;
-  tile_origin(p.band, (int)blockIdx.x, tiles_m, (p.N + BN - 1) / BN, mt, nt);
+  if (p.tail) {
+    tile_origin(p.band, p.tile_base + ((int)blockIdx.x >> 1), tiles_m, (p.N + 2 * BN - 1) / (2 * BN), mt, nt);
+    nt = nt * 2 + ((int)blockIdx.x & 1);
+  } else {
+    tile_origin(p.band, (int)blockIdx.x, tiles_m, (p.N + BN - 1) / BN, mt, nt);
+  }
   const int m0 = mt * (128 * AM), n0 = nt * BN;
+  if (n0 >= p.N) return;                               // (the right half of a ragged last tile: nothing to compute)
   // K tiles of this CTA: blockIdx.y picks one of p.splits equal ranges (the last one may be shorter)
   const int kt_per = (p.nkt + p.splits - 1) / p.splits;
   const int kt0 = blockIdx.y * kt_per;
@@ -1057,7 +1066,7 @@ static int launch_a16_kernel(const CUtensorMap& tmA, const CUtensorMap& tmW, con
   static_assert(smem <= (DQW == 4 ? 113 * 1024 : 232448), "shared memory of the A16Wn kernel");
   auto kern = gl_gemm_tc_a16wn_kernel<XT, NB, BN, STAGES, AM, WS, SW, DQW>;
   if (int rc = set_smem(kern, smem)) return rc;
-  const int tiles = (SW ? 1 : (p.M + 128 * AM - 1) / (128 * AM)) * ((p.N + BN - 1) / BN);
+  const int tiles = p.grid_tiles > 0 ? p.grid_tiles : (SW ? 1 : (p.M + 128 * AM - 1) / (128 * AM)) * ((p.N + BN - 1) / BN);
   // K splits: the CTAs of a tile are one cluster along y and add their partial tiles through distributed shared memory
   if (p.splits > 1 && (p.splits > 8 || (size_t)AM * 128 * (SW ? 64 : BN) * 4 > STAGES * stage + WS * wslot))
     GL_FAIL(GL_E_INVALID, "gl_matmul: %d K splits of a %d x %d tile do not fit the cluster reduction", p.splits, AM * 128, BN);
@@ -1261,6 +1270,38 @@ int gl_gemm_tc_launch(const gl_matmul_args* a, cudaStream_t st) {
 #undef GL_A16_SW
     }
     if (a16.AM == 2) {      // (words of at most 4 bits: three 72 KB stages at BN = 256, four 52 KB stages at BN = 128)
+      // 256 x 256 tiles whose last wave would fill at most half of the SMs: that wave's tiles run as 256 x 128 halves in
+      // a second launch (one wave of about 0.6 of a wide tile's time instead of a whole one; "tail": 0 in the cache
+      // entry turns it off).  8192 x 8192, M = 4096: 512 tiles = 3.46 waves -> 444 tiles + 136 halves.
+      const int sms = gl_num_sms();
+      const int wide_tiles = ((a->M + 255) / 256) * ((a->N + 255) / 256), rem = wide_tiles % sms;
+      if (BN == 256 && p.splits == 1 && wide_tiles > sms && rem > 0 && 2 * rem <= sms && tc_cfg_int(a, "tail", 1) != 0) {
+        TcParams p1 = p, p2 = p;
+        p1.grid_tiles = wide_tiles - rem;
+        p2.grid_tiles = 2 * rem; p2.tile_base = wide_tiles - rem; p2.tail = 1;
+        p2.idesc = gl_idesc(1, a->x_dtype == GL_BF16 ? 1 : 0, a->x_dtype == GL_BF16 ? 1 : 0, 128, 128);
+        CUtensorMap tmB2, tmS2, tmZ2;
+        if (int rc = gl_make_tmap_2d(&tmB2, a->w, 3, (uint64_t)a->N, (uint64_t)(a->K / a->elements_per_sample), (uint64_t)a->N * 4, 128u, (uint32_t)wrows, false)) return rc;
+        tmS2 = tmB2; tmZ2 = tmB2;
+        if (a->W_group_mode >= 2)
+          if (int rc = gl_make_tmap_2d(&tmS2, a->scales, xkind, (uint64_t)a->N, n_groups, (uint64_t)a->N * 2, 128u, 1, false)) return rc;
+        if ((a->W_group_mode == 1 || a->W_group_mode >= 3) && !a->zero_is_scalar)
+          if (int rc = gl_make_tmap_2d(&tmZ2, a->zeros, xkind, (uint64_t)a->N, n_groups, (uint64_t)a->N * 2, 128u, 1, false)) return rc;
+#define GL_A16_TAIL(XT, NB)                                                                          \
+        do {                                                                                        \
+          if (int rc = launch_a16_kernel<XT, NB, 256, 3, 2>(tmA, tmB, tmS, tmZ, p1, st)) return rc;  \
+          return launch_a16_kernel<XT, NB, 128, 4, 2>(tmA, tmB2, tmS2, tmZ2, p2, st);                \
+        } while (0)
+        if (a->x_dtype == GL_BF16) {
+          if (a->W_nbits == 4) GL_A16_TAIL(__nv_bfloat16, 4);
+          if (a->W_nbits == 2) GL_A16_TAIL(__nv_bfloat16, 2);
+          GL_A16_TAIL(__nv_bfloat16, 1);
+        }
+        if (a->W_nbits == 4) GL_A16_TAIL(__half, 4);
+        if (a->W_nbits == 2) GL_A16_TAIL(__half, 2);
+        GL_A16_TAIL(__half, 1);
+#undef GL_A16_TAIL
+      }
 #define GL_A16_2(XT, NB) (BN == 256 ? launch_a16_kernel<XT, NB, 256, 3, 2>(tmA, tmB, tmS, tmZ, p, st) : launch_a16_kernel<XT, NB, 128, 4, 2>(tmA, tmB, tmS, tmZ, p, st))
       if (a->x_dtype == GL_BF16) {
         if (a->W_nbits == 4) return GL_A16_2(__nv_bfloat16, 4);

@@ -135,6 +135,37 @@ def test_a8w8_tensor_core(lib, fp8, M):
     assert rel_fro(y, want_q) < 5e-3, rel_fro(y, want_q)
 
 
+@pytest.mark.parametrize("N", [3976, 3968])
+@pytest.mark.parametrize("nbits,gs", [(4, 128), (2, 64)])
+def test_a16wn_partial_last_wave_runs_as_half_tiles(lib, N, nbits, gs):
+    """11 x 16 = 176 tiles of 256 x 256 on 148 SMs: the 28 tiles of the last wave run as 56 halves of 128 columns in a
+    second launch.  N = 3976: the last tile's right half has 8 columns; N = 3968: it has none.  Same bits as the single
+    launch ("tail": 0 in the cache entry), and both against the dequantised product."""
+    from gemlite_b200 import helper, _lib
+    L = _lib.lib()
+    if torch.cuda.get_device_properties(0).multi_processor_count != 148:
+        pytest.skip("tile counts chosen for 148 SMs")
+    K, M = 2048, 2560 + 37
+    x, W_q, s, z, b = make_a16wn(N, K, nbits, gs, torch.bfloat16, seed=61, M=M)
+    layer = helper.A16Wn_HQQ_INT(device="cuda:0", dtype=torch.bfloat16, W_nbits=nbits).from_weights(W_q.cuda(), s.cuda(), z.cuda(), bias=b.cuda())
+    xd = x.cuda()
+    y = layer(xd)
+    assert _status_word() == 0 and _kernel_name(layer, xd) == "gl_gemm_tc_kernel"
+    sig = "(%d, %d, %d, %d, %d, %d)" % (L.gl_get_closest_m(M), N, K, gs, 32 // nbits, 100 + nbits)
+    try:
+        assert L.gl_cfg_set(b"GEMM", sig.encode(), b'{"tail": 0}') == 0
+        y1 = layer(xd)
+    finally:
+        L.gl_cfg_set(b"GEMM", sig.encode(), b'{"tail": 1}')
+    assert torch.equal(y, y1)
+    Wd = ((W_q.double().view(N, -1, gs) - z.view(N, -1).double()[..., None]) * s.view(N, -1).double()[..., None]).view(N, K)
+    want = (x.double() @ Wd.T + b.double()).numpy()
+    got = y.float().cpu().numpy()
+    assert rel_fro(got, want) < 1e-2
+    assert rel_fro(got[:, 3584:], want[:, 3584:]) < 1e-2 and rel_fro(got[-37:], want[-37:]) < 1e-2      # the half tiles, the ragged rows
+    assert rel_fro(got[:, -8:], want[:, -8:]) < 1e-2
+
+
 @pytest.mark.parametrize("kind", ["fp8", "a16w4"])
 def test_banded_tile_order_for_large_activations(lib, kind):
     """Activations of 64 MB and more switch the tile numbering to bands of 2048 rows (the last band short, the last row
