@@ -71,29 +71,15 @@ __device__ __forceinline__ uint32_t e2m1_code(float v) {
 // the smaller magnitude, and -0.0 gets code 0.  The hardware conversion rounds half to even, so each value is first
 // moved one fp32 ulp towards zero: a tie then lies below the midpoint, and nothing else changes, because a value with at
 // most 11 significant bits is never one fp32 ulp above a midpoint (midpoints have 3 significant bits).  fp32
-// activations do not have that guarantee and keep the threshold form.
+// activations do not have that guarantee and keep the threshold form.  (16384 x 16384 bf16: 0.459 -> 0.281 ms; the seven
+// compares and adds per value had made the kernel issue-bound.  More units per thread and trip, or rows kept in registers
+// by the per-token kernel, were 10-20 % slower: these kernels need their 32 registers per thread, 2048 threads per SM.)
 __device__ __forceinline__ uint32_t e2m1x2_from16(float a, float b) {
   uint32_t ua = __float_as_uint(a), ub = __float_as_uint(b);
   ua = (ua << 1) ? ua - 1u : 0u;
   ub = (ub << 1) ? ub - 1u : 0u;
   return (uint32_t)__nv_cvt_float2_to_fp4x2(make_float2(__uint_as_float(ua), __uint_as_float(ub)), __NV_E2M1, cudaRoundNearest);
 }
-
-// (row, first k) of unit u of 8 consecutive k: 32-bit arithmetic when the unit count allows (a 64-bit division is a
-// subroutine of about a hundred instructions, as much as the rest of a unit's work)
-__device__ __forceinline__ void unit_row_k(int64_t u, int units_per_row, bool small, int& m, int& k) {
-  if (small) {
-    const uint32_t uu = (uint32_t)u, mm = uu / (uint32_t)units_per_row;
-    m = (int)mm;
-    k = (int)(uu - mm * (uint32_t)units_per_row) * 8;
-  } else {
-    m = (int)(u / units_per_row);
-    k = (int)(u - (int64_t)m * units_per_row) * 8;
-  }
-}
-
-constexpr int kRowUnits = 4;     // units of 8 values a thread of the per-token kernel keeps in registers
-constexpr int kUnroll = 4;       // units a thread of the group quantisers loads before it works on the first
 
 // ---------------------------------------------------------------------------------------------
 // per-token: one CTA per row (grid-stride), two passes over the row (second one hits L1/L2)
@@ -105,53 +91,6 @@ __global__ void __launch_bounds__(256) per_token_kernel(const void* __restrict__
   gl_launch_dependents();          // the matmul that follows may set itself up and prefetch weights meanwhile
   gl_grid_dependency_wait();       // x comes from the previous kernel of the stream; q / scales may still be read by it
   const float qmax = INT8 ? 127.f : 448.f, qmin = INT8 ? -128.f : -448.f;
-  auto quantise8 = [&](const float (&v)[8], float s, uint8_t* dst) {
-    uint32_t o[2] = {0u, 0u};
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      float t = fminf(fmaxf(v[i] / s, qmin), qmax);
-      uint32_t b;
-      if (INT8) b = (uint32_t)(uint8_t)(int8_t)(int)roundf(t);
-      else b = (uint32_t)__nv_cvt_float_to_fp8(t, __NV_SATFINITE, __NV_E4M3);
-      o[i >> 2] |= b << (8 * (i & 3));
-    }
-    *reinterpret_cast<uint2*>(dst) = make_uint2(o[0], o[1]);
-  };
-  if (K <= kRowUnits * 8 * 256) {
-    // the row fits the CTA's registers (4 units of 8 values per thread): all loads of a row in flight together, x read once
-    for (int m = blockIdx.x; m < M; m += gridDim.x) {
-      float v[kRowUnits][8];
-      float amax = 0.f;
-#pragma unroll
-      for (int j = 0; j < kRowUnits; ++j) {
-        const int k = (j * 256 + (int)threadIdx.x) * 8;
-        if (k < K) load8(x, (int64_t)m * K + k, x_dtype, v[j]);
-        else {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) v[j][i] = 0.f;
-        }
-      }
-#pragma unroll
-      for (int j = 0; j < kRowUnits; ++j)
-#pragma unroll
-        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[j][i]));
-      amax = warp_max(amax);
-      if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = amax;
-      __syncthreads();
-      float a = 0.f;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) a = fmaxf(a, s_red[i]);
-      const float s = fmaxf(a / qmax, 1e-6f);
-      if (threadIdx.x == 0) scales[m] = s;
-#pragma unroll
-      for (int j = 0; j < kRowUnits; ++j) {
-        const int k = (j * 256 + (int)threadIdx.x) * 8;
-        if (k < K) quantise8(v[j], s, q + (int64_t)m * K + k);
-      }
-      __syncthreads();                                   // s_red is rewritten by the next row
-    }
-    return;
-  }
   for (int m = blockIdx.x; m < M; m += gridDim.x) {
     float amax = 0.f;
     for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
@@ -175,7 +114,16 @@ __global__ void __launch_bounds__(256) per_token_kernel(const void* __restrict__
     for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
       float v[8];
       load8(x, (int64_t)m * K + k, x_dtype, v);
-      quantise8(v, s, q + (int64_t)m * K + k);
+      uint32_t o[2] = {0u, 0u};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float t = fminf(fmaxf(v[i] / s, qmin), qmax);
+        uint32_t b;
+        if (INT8) b = (uint32_t)(uint8_t)(int8_t)(int)roundf(t);
+        else b = (uint32_t)__nv_cvt_float_to_fp8(t, __NV_SATFINITE, __NV_E4M3);
+        o[i >> 2] |= b << (8 * (i & 3));
+      }
+      *reinterpret_cast<uint2*>(q + (int64_t)m * K + k) = make_uint2(o[0], o[1]);
     }
     __syncthreads();
   }
@@ -188,61 +136,49 @@ __global__ void __launch_bounds__(256) mx_quant_kernel(const void* __restrict__ 
                                                        uint8_t* __restrict__ scales, int M, int Mpad, int K, int x_dtype, int layout) {
   gl_launch_dependents();
   gl_grid_dependency_wait();
-  const int units_per_row = K / 8;
+  const int64_t units_per_row = K / 8;
   const int64_t total = (int64_t)Mpad * units_per_row;
-  const bool small = total < (1ll << 31);
-  // A trip handles kUnroll units per thread, one grid stride apart, and issues all their loads before it works on the first
-  // (one 16-byte load per thread and trip left the kernel latency-bound at 2.5-3 TB/s).  Unit counts are multiples of 32
-  // and the bounds are warp-uniform, so every lane takes part in the group shuffles.
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t base = blockIdx.x * (int64_t)blockDim.x + (threadIdx.x & ~31); base < total; base += stride * kUnroll) {
-    float v[kUnroll][8];
-    int ms[kUnroll], ks[kUnroll];
+  // the loop bound is warp-uniform so that every lane takes part in the group shuffles
+  for (int64_t u0 = blockIdx.x * (int64_t)blockDim.x + (threadIdx.x & ~31); u0 < total; u0 += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t u = u0 + (threadIdx.x & 31);
+    const bool valid = u < total;
+    const int m = valid ? (int)(u / units_per_row) : Mpad;
+    const int k = valid ? (int)(u % units_per_row) * 8 : 0;
+    float v[8];
+    const bool real = m < M;
+    if (real) load8(x, (int64_t)m * K + k, x_dtype, v);
+    else {
 #pragma unroll
-    for (int j = 0; j < kUnroll; ++j) {
-      const int64_t u = base + j * stride + (threadIdx.x & 31);
-      ms[j] = Mpad; ks[j] = 0;
-      if (u < total) unit_row_k(u, units_per_row, small, ms[j], ks[j]);
-      if (ms[j] < M) load8(x, (int64_t)ms[j] * K + ks[j], x_dtype, v[j]);
-      else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[j][i] = 0.f;
-      }
+      for (int i = 0; i < 8; ++i) v[i] = 0.f;
     }
+    float amax = 0.f;
 #pragma unroll
-    for (int j = 0; j < kUnroll; ++j) {
-      if (base + j * stride >= total) break;             // warp-uniform
-      const int m = ms[j], k = ks[j];
-      const bool valid = m < Mpad, real = m < M;
-      float amax = 0.f;
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    const uint32_t e = pow2_ceil_exp(amax / (FP4 ? 6.f : 448.f));
+    const float scale = __uint_as_float(e << 23);
+    if (valid && (threadIdx.x & 3) == 0) scales[scale_index(m, k / 32, K / 32, layout)] = real ? (uint8_t)e : (uint8_t)127;
+    if (!real) continue;
+    const float inv = 1.0f / scale;                    // a power of two in [2^-127, 2^30]: multiplying by it is the division, exactly
+    if (FP4) {
+      uint32_t o = 0u;
+      if (x_dtype == GL_FP32) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[j][i]));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-      const uint32_t e = pow2_ceil_exp(amax / (FP4 ? 6.f : 448.f));
-      const float scale = __uint_as_float(e << 23);
-      if (valid && (threadIdx.x & 3) == 0) scales[scale_index(m, k / 32, K / 32, layout)] = real ? (uint8_t)e : (uint8_t)127;
-      if (!real) continue;
-      const float inv = 1.0f / scale;                  // a power of two in [2^-127, 2^30]: multiplying by it is the division, exactly
-      if (FP4) {
-        uint32_t o = 0u;
-        if (x_dtype == GL_FP32) {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) o |= e2m1_code(v[j][i] * inv) << (4 * i);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) o |= e2m1x2_from16(v[j][2 * i] * inv, v[j][2 * i + 1] * inv) << (8 * i);
-        }
-        *reinterpret_cast<uint32_t*>(q + (int64_t)m * (K / 2) + k / 2) = o;
+        for (int i = 0; i < 8; ++i) o |= e2m1_code(v[i] * inv) << (4 * i);
       } else {
-        uint32_t o[2] = {0u, 0u};
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float t = fminf(fmaxf(v[j][i] * inv, -448.f), 448.f);
-          o[i >> 2] |= (uint32_t)__nv_cvt_float_to_fp8(t, __NV_SATFINITE, __NV_E4M3) << (8 * (i & 3));
-        }
-        *reinterpret_cast<uint2*>(q + (int64_t)m * K + k) = make_uint2(o[0], o[1]);
+        for (int i = 0; i < 4; ++i) o |= e2m1x2_from16(v[2 * i] * inv, v[2 * i + 1] * inv) << (8 * i);
       }
+      *reinterpret_cast<uint32_t*>(q + (int64_t)m * (K / 2) + k / 2) = o;
+    } else {
+      uint32_t o[2] = {0u, 0u};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float t = fminf(fmaxf(v[i] * inv, -448.f), 448.f);
+        o[i >> 2] |= (uint32_t)__nv_cvt_float_to_fp8(t, __NV_SATFINITE, __NV_E4M3) << (8 * (i & 3));
+      }
+      *reinterpret_cast<uint2*>(q + (int64_t)m * K + k) = make_uint2(o[0], o[1]);
     }
   }
 }
@@ -254,21 +190,11 @@ __global__ void __launch_bounds__(256) amax_kernel(const void* __restrict__ x, u
   float amax = 0.f;
   gl_launch_dependents();
   gl_grid_dependency_wait();
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t base = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; base < total_units; base += stride * kUnroll) {
-    float v[kUnroll][8];
+  for (int64_t u = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; u < total_units; u += (int64_t)gridDim.x * blockDim.x) {
+    float v[8];
+    load8(x, u * 8, x_dtype, v);
 #pragma unroll
-    for (int j = 0; j < kUnroll; ++j) {
-      if (base + j * stride < total_units) load8(x, (base + j * stride) * 8, x_dtype, v[j]);
-      else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[j][i] = 0.f;
-      }
-    }
-#pragma unroll
-    for (int j = 0; j < kUnroll; ++j)
-#pragma unroll
-      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[j][i]));
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
   }
   amax = warp_max(amax);
   __shared__ float s_red[8];
@@ -293,44 +219,34 @@ __global__ void __launch_bounds__(256) nvfp4_quant_kernel(const void* __restrict
   if (meta_in != nullptr) meta = *meta_in;
   else meta = (448.f * 6.0f) / fmaxf(__uint_as_float(*amax_bits), 1e-6f);
   if (blockIdx.x == 0 && threadIdx.x == 0) *meta_out = meta;
-  const int units_per_row = K / 8;
+  const int64_t units_per_row = K / 8;
   const int64_t total = (int64_t)Mpad * units_per_row;
-  const bool small = total < (1ll << 31);
-  // kUnroll units per thread and trip, loads first (see mx_quant_kernel); bounds are warp-uniform for the group shuffles
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t base = blockIdx.x * (int64_t)blockDim.x + (threadIdx.x & ~31); base < total; base += stride * kUnroll) {
-    float v[kUnroll][8];
-    int ms[kUnroll], ks[kUnroll];
+  // the loop bound is warp-uniform so that every lane takes part in the group shuffles
+  for (int64_t u0 = blockIdx.x * (int64_t)blockDim.x + (threadIdx.x & ~31); u0 < total; u0 += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t u = u0 + (threadIdx.x & 31);
+    const bool valid = u < total;
+    const int m = valid ? (int)(u / units_per_row) : Mpad;
+    const int k = valid ? (int)(u % units_per_row) * 8 : 0;
+    const bool real = m < M;
+    float v[8];
+    if (real) load8(x, (int64_t)m * K + k, x_dtype, v);
+    else {
 #pragma unroll
-    for (int j = 0; j < kUnroll; ++j) {
-      const int64_t u = base + j * stride + (threadIdx.x & 31);
-      ms[j] = Mpad; ks[j] = 0;
-      if (u < total) unit_row_k(u, units_per_row, small, ms[j], ks[j]);
-      if (ms[j] < M) load8(x, (int64_t)ms[j] * K + ks[j], x_dtype, v[j]);
-      else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[j][i] = 0.f;
-      }
+      for (int i = 0; i < 8; ++i) v[i] = 0.f;
     }
+    float amax = 0.f;
 #pragma unroll
-    for (int j = 0; j < kUnroll; ++j) {
-      if (base + j * stride >= total) break;             // warp-uniform
-      const int m = ms[j], k = ks[j];
-      const bool valid = m < Mpad, real = m < M;
-      float amax = 0.f;
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    const float sraw = fminf(amax * meta / 6.f, 448.f);
+    const uint8_t s8 = (uint8_t)__nv_cvt_float_to_fp8(sraw, __NV_SATFINITE, __NV_E4M3);
+    if (valid && (threadIdx.x & 1) == 0) scales[scale_index(m, k / 16, K / 16, layout)] = real ? s8 : (uint8_t)0x38;  // 0x38 = 1.0 e4m3
+    if (!real) continue;
+    const float sfull = fmaxf(gl_e4m3_to_float(s8) / meta, 1e-6f);
+    uint32_t o = 0u;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[j][i]));
-      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-      const float sraw = fminf(amax * meta / 6.f, 448.f);
-      const uint8_t s8 = (uint8_t)__nv_cvt_float_to_fp8(sraw, __NV_SATFINITE, __NV_E4M3);
-      if (valid && (threadIdx.x & 1) == 0) scales[scale_index(m, k / 16, K / 16, layout)] = real ? s8 : (uint8_t)0x38;  // 0x38 = 1.0 e4m3
-      if (!real) continue;
-      const float sfull = fmaxf(gl_e4m3_to_float(s8) / meta, 1e-6f);
-      uint32_t o = 0u;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) o |= e2m1_code(v[j][i] / sfull) << (4 * i);
-      *reinterpret_cast<uint32_t*>(q + (int64_t)m * (K / 2) + k / 2) = o;
-    }
+    for (int i = 0; i < 8; ++i) o |= e2m1_code(v[i] / sfull) << (4 * i);
+    *reinterpret_cast<uint32_t*>(q + (int64_t)m * (K / 2) + k / 2) = o;
   }
 }
 
@@ -377,45 +293,30 @@ __global__ void __launch_bounds__(256) per_block_kernel(const void* __restrict__
   gl_grid_dependency_wait();
   const float qmax = INT8 ? 127.f : 448.f, qmin = INT8 ? -128.f : -448.f;
   const int units_per_row = K / 8;
-  const bool small = total_units < (1ll << 31);
-  // kUnroll units per thread and trip, loads first (see mx_quant_kernel).  The bounds are half-warp-uniform: a block's
-  // sixteen units are either all inside or all outside.
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  const unsigned half_mask = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;       // the other half warp may be past the end
-  for (int64_t base = blockIdx.x * (int64_t)blockDim.x + (threadIdx.x & ~15); base < total_units; base += stride * kUnroll) {
-    float v[kUnroll][8];
-    int ms[kUnroll], ks[kUnroll];
+  // the loop bound is half-warp-uniform: a block's sixteen units are either all inside or all outside
+  for (int64_t u0 = blockIdx.x * (int64_t)blockDim.x + (threadIdx.x & ~15); u0 < total_units; u0 += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t u = u0 + (threadIdx.x & 15);
+    const int m = (int)(u / units_per_row), k = (int)(u % units_per_row) * 8;
+    float v[8];
+    load8(x, (int64_t)m * K + k, x_dtype, v);
+    float amax = 0.f;
 #pragma unroll
-    for (int j = 0; j < kUnroll; ++j) {
-      const int64_t u = base + j * stride + (threadIdx.x & 15);
-      ms[j] = 0; ks[j] = 0;
-      if (u < total_units) {
-        unit_row_k(u, units_per_row, small, ms[j], ks[j]);
-        load8(x, (int64_t)ms[j] * K + ks[j], x_dtype, v[j]);
-      }
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    const unsigned half_mask = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;     // the other half warp may be past the end
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(half_mask, amax, o));
+    const float s = fmaxf(amax / qmax, 1e-6f);
+    if ((threadIdx.x & 15) == 0) scales[(int64_t)m * (K / 128) + k / 128] = s;
+    uint32_t o2[2] = {0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float t = fminf(fmaxf(v[i] / s, qmin), qmax);
+      uint32_t b;
+      if (INT8) b = (uint32_t)(uint8_t)(int8_t)(int)roundf(t);                // libdevice.round: half away from zero
+      else b = (uint32_t)__nv_cvt_float_to_fp8(t, __NV_SATFINITE, __NV_E4M3);
+      o2[i >> 2] |= b << (8 * (i & 3));
     }
-#pragma unroll
-    for (int j = 0; j < kUnroll; ++j) {
-      if (base + j * stride >= total_units) break;       // half-warp-uniform
-      const int m = ms[j], k = ks[j];
-      float amax = 0.f;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[j][i]));
-#pragma unroll
-      for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(half_mask, amax, o));
-      const float s = fmaxf(amax / qmax, 1e-6f);
-      if ((threadIdx.x & 15) == 0) scales[(int64_t)m * (K / 128) + k / 128] = s;
-      uint32_t o2[2] = {0u, 0u};
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float t = fminf(fmaxf(v[j][i] / s, qmin), qmax);
-        uint32_t b;
-        if (INT8) b = (uint32_t)(uint8_t)(int8_t)(int)roundf(t);              // libdevice.round: half away from zero
-        else b = (uint32_t)__nv_cvt_float_to_fp8(t, __NV_SATFINITE, __NV_E4M3);
-        o2[i >> 2] |= b << (8 * (i & 3));
-      }
-      *reinterpret_cast<uint2*>(q + (int64_t)m * K + k) = make_uint2(o2[0], o2[1]);
-    }
+    *reinterpret_cast<uint2*>(q + (int64_t)m * K + k) = make_uint2(o2[0], o2[1]);
   }
 }
 
