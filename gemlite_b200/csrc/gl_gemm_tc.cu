@@ -365,7 +365,7 @@ __global__ void __launch_bounds__(192, 1) gl_gemm_tc_kernel(const __grid_constan
         for (int kt = 0; kt < p.nkt; ++kt, ++it) {
           const int s = it % STAGES;
           if ((int)it < pre) { load_b(kt, s, n0, valid_nb); continue; }      // the other half of a stage opened above
-          if (!mbar_wait(empty + s, ((it / STAGES) & 1u) ^ 1u, &s_abort, p.status, 2)) { ok = false; break; }
+          if (!mbar_wait_spin(empty + s, ((it / STAGES) & 1u) ^ 1u, &s_abort, p.status, 2)) { ok = false; break; }
           mbar_expect_tx(full + s, stage_bytes(kt, valid_nb));
           load_a(kt, s, m0);
           load_b(kt, s, n0, valid_nb);
@@ -384,7 +384,7 @@ __global__ void __launch_bounds__(192, 1) gl_gemm_tc_kernel(const __grid_constan
         const uint32_t d_tmem = tmem_base + ab * ACC_STRIDE;
         for (int kt = 0; kt < p.nkt; ++kt, ++it) {
           const int s = it % STAGES;
-          if (!mbar_wait(full + s, (it / STAGES) & 1u, &s_abort, p.status, 3)) { ok = false; break; }
+          if (!mbar_wait_spin(full + s, (it / STAGES) & 1u, &s_abort, p.status, 3)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + s * STAGE_BYTES), sb = sa + A_BYTES;
           if (MX) {
@@ -878,8 +878,8 @@ __global__ void __launch_bounds__((6 + DQW) * 32, DQW == 4 ? 2 : 1) gl_gemm_tc_a
 
 // ---- 128 x 128 block quantisation (channel_scale_mode 5): FP8 x FP8 or INT8 x INT8 --------------------------
 // out[m, n] = sum_kb (sum_{k in kb} x[m,k] w[n,k]) * s_x[m, kb] * s_w[kb, n / 128]  (gemm_kernels.py:396-450).  A K tile of
-// 128 bytes is exactly one block, so every K tile's four MMAs start a fresh partial sum in one of two tensor-memory
-// accumulators; the epilogue warps drain it (tcgen05.ld), multiply by the two block scales and add it to the running
+// 128 bytes is exactly one block, so every K tile's four MMAs start a fresh partial sum in one of the tensor-memory
+// accumulators (512 / BN of them, used in turn); the epilogue warps drain it (tcgen05.ld), multiply by the two block scales and add it to the running
 // sums they keep in registers while the MMAs of the next K tile fill the other accumulator.  Eight epilogue warps: a
 // warp owns one 32-row quadrant and one half of the columns.
 // One 128 x BN output tile per CTA (BN = 256: two weight blocks side by side, each column half with its own block scale;
@@ -890,13 +890,14 @@ template <bool INT8, int BN, int STAGES>
 __global__ void __launch_bounds__(64 + 32 * kBlockqEpiWarps, 1) gl_gemm_tc_blockq_kernel(const __grid_constant__ CUtensorMap tmA,
                                                                    const __grid_constant__ CUtensorMap tmB, const TcParams p) {
   constexpr int A_BYTES = 128 * 128, B_BYTES = BN * 128, STAGE_BYTES = A_BYTES + B_BYTES, HALF = BN / 2;
+  constexpr int NBUF = 512 / BN;                        // accumulators: all of tensor memory, so that the MMAs run ahead of the drain
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = smem_dyn + ((1024u - (smem_u32(smem_dyn) & 1023u)) & 1023u);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
   uint64_t* empty = full + STAGES;
-  uint64_t* acc_full = empty + STAGES;                  // [2] the K tile's partial sum is complete
-  uint64_t* acc_empty = acc_full + 2;                   // [2] ... and has been drained by the four epilogue warps
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* acc_full = empty + STAGES;                  // [NBUF] the K tile's partial sum is complete
+  uint64_t* acc_empty = acc_full + 8;                   // [NBUF] ... and has been drained by the eight epilogue warps
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 8);
   float* sw_s = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(tmem_slot + 1) + 15) & ~(uintptr_t)15);
   float* b_s = sw_s + BN;
   __shared__ int s_abort;
@@ -909,12 +910,12 @@ __global__ void __launch_bounds__(64 + 32 * kBlockqEpiWarps, 1) gl_gemm_tc_block
   if (threadIdx.x == 0) {
     s_abort = 0;
     for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(acc_full + b, 1); mbar_init(acc_empty + b, kBlockqEpiWarps); }
+    for (int b = 0; b < NBUF; ++b) { mbar_init(acc_full + b, 1); mbar_init(acc_empty + b, kBlockqEpiWarps); }
     fence_barrier_init();
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
   }
-  if (warp == 1) tmem_alloc(tmem_slot, 2 * BN);
+  if (warp == 1) tmem_alloc(tmem_slot, NBUF * BN);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -925,7 +926,7 @@ __global__ void __launch_bounds__(64 + 32 * kBlockqEpiWarps, 1) gl_gemm_tc_block
       gl_grid_dependency_wait();
       for (int kt = 0; kt < p.nkt; ++kt) {
         const int s = kt % STAGES;
-        if (!mbar_wait(empty + s, (uint32_t)(((kt / STAGES) & 1) ^ 1), &s_abort, p.status, 2)) break;
+        if (!mbar_wait_spin(empty + s, (uint32_t)(((kt / STAGES) & 1) ^ 1), &s_abort, p.status, 2)) break;
         unsigned char* st = smem + s * STAGE_BYTES;
         mbar_expect_tx(full + s, A_BYTES + B_BYTES);
         tma_load_2d(st, &tmA, full + s, kt * 128, m0);
@@ -936,8 +937,8 @@ __global__ void __launch_bounds__(64 + 32 * kBlockqEpiWarps, 1) gl_gemm_tc_block
     if (lane == 0) {
       bool ok = true;
       for (int kt = 0; kt < p.nkt && ok; ++kt) {
-        const int s = kt % STAGES, ab = kt & 1;
-        if (!mbar_wait_spin(acc_empty + ab, (uint32_t)(((kt >> 1) & 1) ^ 1), &s_abort, p.status, 6) ||
+        const int s = kt % STAGES, ab = kt % NBUF;
+        if (!mbar_wait_spin(acc_empty + ab, (uint32_t)(((kt / NBUF) & 1) ^ 1), &s_abort, p.status, 6) ||
             !mbar_wait_spin(full + s, (uint32_t)((kt / STAGES) & 1), &s_abort, p.status, 3)) { ok = false; break; }
         tc_fence_after();
         const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
@@ -963,10 +964,10 @@ __global__ void __launch_bounds__(64 + 32 * kBlockqEpiWarps, 1) gl_gemm_tc_block
     const float* swp = p.bq_scales + (long long)nblk * p.bq_stride_n;
     float sx_n = sxp[0], sw_n = swp[0];
     for (int kt = 0; kt < p.nkt && ok; ++kt) {
-      const int ab = kt & 1;
+      const int ab = kt % NBUF;
       const float sc = (m < p.M ? sx_n : 0.f) * sw_n;
       if (kt + 1 < p.nkt) { sx_n = sxp[kt + 1]; sw_n = swp[(long long)(kt + 1) * p.bq_stride_g]; }
-      if (!mbar_wait_spin(acc_full + ab, (uint32_t)((kt >> 1) & 1), &s_abort, p.status, 4)) { ok = false; break; }
+      if (!mbar_wait_spin(acc_full + ab, (uint32_t)((kt / NBUF) & 1), &s_abort, p.status, 4)) { ok = false; break; }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(ab * BN + cb);
       if constexpr (HALF == 64) {                            // both loads in flight, the buffer handed back before the arithmetic
@@ -1012,7 +1013,7 @@ __global__ void __launch_bounds__(64 + 32 * kBlockqEpiWarps, 1) gl_gemm_tc_block
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
+  if (warp == 1) tmem_dealloc(tmem_base, NBUF * BN);
 }
 
 template <typename K>
@@ -1023,7 +1024,7 @@ static int set_smem(K kern, size_t smem) {
 
 template <bool INT8, int BN, int STAGES>
 static int launch_blockq_kernel(const CUtensorMap& tmA, const CUtensorMap& tmB, const TcParams& p, cudaStream_t st) {
-  const size_t smem = 1024 + STAGES * (128 * 128 + BN * 128) + (2 * STAGES + 4) * 8 + 32 + 2 * BN * 4 + 16;
+  const size_t smem = 1024 + STAGES * (128 * 128 + BN * 128) + (2 * STAGES + 16) * 8 + 32 + 2 * BN * 4 + 16;
   auto kern = gl_gemm_tc_blockq_kernel<INT8, BN, STAGES>;
   if (int rc = set_smem(kern, smem)) return rc;
   const int tiles = ((p.M + 127) / 128) * ((p.N + BN - 1) / BN);
@@ -1095,10 +1096,9 @@ static TcPath classify(const gl_matmul_args* a) {
   if (a->M < 1) return TC_NONE;
   if (((uintptr_t)a->x & 15) || ((uintptr_t)a->w & 15) || ((uintptr_t)a->out & 15)) return TC_NONE;
   if (!(a->out_dtype == GL_BF16 || a->out_dtype == GL_FP16 || a->out_dtype == GL_FP32)) return TC_NONE;
-  // 128 x 128 block quantisation: e4m3 x e4m3 or int8 x int8, fp32 block scales on both sides; more than 16 rows (below
-  // that the general kernel's one pass over the weights is shorter than a 128-row tile's pipeline)
+  // 128 x 128 block quantisation: e4m3 x e4m3 or int8 x int8, fp32 block scales on both sides
   if (a->channel_scale_mode == 5) {
-    if (a->M <= 16 || a->elements_per_sample != 1 || a->W_nbits != 8 || a->W_group_mode != 0 || a->w_stride_k != 1 || a->w_stride_n != a->K ||
+    if (a->elements_per_sample != 1 || a->W_nbits != 8 || a->W_group_mode != 0 || a->w_stride_k != 1 || a->w_stride_n != a->K ||
         a->K % 128 != 0 || a->scales == nullptr || a->scales_x == nullptr || a->meta_dtype != GL_FP32) return TC_NONE;
     if (a->x_dtype == GL_FP8 && a->w_dtype == GL_FP8 && a->input_dtype == GL_FP8) return TC_BLOCKQ_FP8;
     if (a->x_dtype == GL_INT8 && a->w_dtype == GL_INT8 && a->input_dtype == GL_INT8) return TC_BLOCKQ_INT8;
@@ -1327,9 +1327,13 @@ int gl_gemm_tc_launch(const gl_matmul_args* a, cudaStream_t st) {
   }
   if (path == TC_BLOCKQ_FP8 || path == TC_BLOCKQ_INT8) {
     p.nkt = a->K / 128;
-    // 256-column tiles when they still give every SM a tile ("tile_n" in the cache entry overrides)
+    // 256-column tiles when they still give every SM a tile ("tile_n" in the cache entry overrides).  Decode sizes: an MMA
+    // reads its 128-row operand (here the mostly empty x tile) at 32 B/clk, 128 cycles per 32 bytes of K whatever the
+    // number of weight columns, so a CTA streams 128-column weight tiles at 32 B/clk at best; 64-column tiles on twice
+    // as many SMs measured the same total (8192 x 8192, M = 1: 37 against 32 us) and are not built.
     const int bq_req = tc_cfg_int(a, "tile_n", 0);
-    int bq_bn = (a->N >= 256 && (int64_t)((a->M + 127) / 128) * ((a->N + 255) / 256) >= gl_num_sms()) ? 256 : 128;
+    const int64_t bq_tm = (a->M + 127) / 128;
+    int bq_bn = (a->N >= 256 && bq_tm * ((a->N + 255) / 256) >= gl_num_sms()) ? 256 : 128;
     if ((bq_req == 128 || bq_req == 256) && a->N >= bq_req) bq_bn = bq_req;
     p.idesc = (path == TC_BLOCKQ_FP8) ? gl_idesc(1, 0, 0, 128, bq_bn) : gl_idesc(2, 1, 1, 128, bq_bn);
     p.scales_x = reinterpret_cast<const float*>(a->scales_x);

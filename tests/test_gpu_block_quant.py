@@ -60,11 +60,18 @@ def test_block_quant_layer(lib, fp8, dtype):
         wq = layer.W_q.t().contiguous()
         wq = wq.view(torch.uint8).cpu().numpy() if fp8 else wq.cpu().numpy()
         assert (wq != wq_o).mean() < 5e-3
-        for M in (1, 3, 16, 17, 65, 130, 300):
+        for M in (1, 3, 16, 17, 65, 130, 300, 700):
             x = (torch.randn(M, K, generator=g) / 10.0).to(dtype)
             y = layer(x.cuda()).float().cpu().numpy()
-            # more than 16 rows: the tensor-core kernel (one partial sum per K tile, scaled into register accumulators)
-            assert _kernel_name(layer, x.cuda(), fp8) == ("gl_gemm_tc_kernel" if M > 16 else "gl_generic_kernel")
+            # the tensor-core kernel (one partial sum per K tile, scaled into register accumulators) at every batch size
+            assert _kernel_name(layer, x.cuda(), fp8) == "gl_gemm_tc_kernel"
+            from gemlite_b200 import core
+            core.set_kernel_override(1)                                            # ... and the general kernel agrees with it
+            try:
+                y_gen = layer(x.cuda()).float().cpu().numpy()
+            finally:
+                core.set_kernel_override(0)
+            assert rel_fro(y, y_gen) < 5e-3
             xq, sx = oracle.scale_activations_per_block(x.float().numpy(), kind)
             want_q = oracle.matmul_block_quant(xq, sx, wq, layer.scales.t().cpu().numpy(), kind, bias=bias.double().numpy())
             assert rel_fro(y, want_q) < 5e-3, (N, K, M, rel_fro(y, want_q))
