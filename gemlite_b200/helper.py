@@ -534,6 +534,93 @@ class A8W4_MXFP_dynamic(A8Wn_MXFP_dynamic):
 
 # ---------------------------------------------------------------------------------------------
 # the M buckets of get_closest_m, largest first
+class A8Wn_HQQ_INT_dynamic(A16Wn):
+    """FP8 activations quantised per token in the forward x packed 8/4/2-bit codes with group-wise scales and zeros
+    (gemlite/helper.py:712-830): `pack(..., fma_mode=False)`, so grouped layers run mode 3 `(q - z) * s` with the
+    activation scale on the finished sums (channel mode 2); one group per row folds the weight scale into the epilogue
+    when `post_scale` is set (modes 1 / 3)."""
+
+    def __init__(self, device="cuda:0", packing_bitwidth=None, dtype=None, post_scale=default_post_scale, fp8=default_fp8,
+                 fp32_scale=False, W_nbits=None):
+        assert W_nbits is not None, "W_nbits argument should be either 8, 4 or 2, not None."
+        super().__init__(device=device, dtype=dtype, packing_bitwidth=packing_bitwidth, post_scale=post_scale)
+        self.fp8, self.fp32_scale, self.W_nbits = fp8, fp32_scale, W_nbits
+
+    def from_packed_weights(self, W_q_packed, scales, zeros, bias=None):
+        group_size = W_q_packed.numel() * (self.W_nbits // 4) // scales.numel()
+        return self.from_weights_(W_q_packed, scales, zeros, self.W_nbits, group_size, bias=bias, packed=True)
+
+    def from_weights(self, W_q, scales, zeros, bias=None):
+        return self.from_weights_(W_q, scales, zeros, self.W_nbits, W_q.numel() // scales.numel(), bias=bias)
+
+    def from_weights_(self, W_q, scales, zeros, W_nbits, group_size, bias=None, quant_type="INT", packed=False):
+        assert quant_type == "INT", "dynamic FP8 activations take integer codes"
+        W_q, bias = _data(W_q), _data(bias)
+        dtype = self.dtype if self.dtype is not None else (scales.dtype if scales.dtype in (torch.float16, torch.bfloat16) else torch.float16)
+        assert dtype in _FLOAT_DTYPES, "Invalid scales.dtype, should be floating point."
+        in_features, out_features = W_q.shape[::-1]
+        if packed:
+            in_features = scales.numel() * group_size // out_features
+        layer = GemLiteLinear(W_nbits, group_size=group_size, in_features=in_features, out_features=out_features,
+                              input_dtype=TORCH_TO_DTYPE[self.fp8], output_dtype=TORCH_TO_DTYPE[dtype], scaled_activations=True)
+        layer.pack(W_q.to(self.device),
+                   scales.to(device=self.device, dtype=torch.float32 if self.fp32_scale else dtype) if scales is not None else None,
+                   zeros.to(device=self.device, dtype=dtype) if zeros is not None else None,
+                   bias=bias.to(device=self.device, dtype=dtype) if bias is not None else None,
+                   packing_bitwidth=self.packing_bitwidth, fma_mode=False, packed=packed)
+        if group_size == in_features:
+            layer.W_group_mode, layer.channel_scale_mode = (1, 3) if self.post_scale else (3, 2)
+        return layer
+
+
+class A8W4_HQQ_INT_dynamic(A8Wn_HQQ_INT_dynamic):
+    def __init__(self, device="cuda:0", packing_bitwidth=None, dtype=None, post_scale=default_post_scale, fp8=default_fp8, fp32_scale=False):
+        super().__init__(device, packing_bitwidth, dtype, post_scale, fp8, fp32_scale, W_nbits=4)
+
+
+class A8W2_HQQ_INT_dynamic(A8Wn_HQQ_INT_dynamic):
+    def __init__(self, device="cuda:0", packing_bitwidth=None, dtype=None, post_scale=default_post_scale, fp8=default_fp8, fp32_scale=False):
+        super().__init__(device, packing_bitwidth, dtype, post_scale, fp8, fp32_scale, W_nbits=2)
+
+
+class _Ternary:
+    """BitNet layers (gemlite/helper.py:1208-1320): weights in {-1, 0, 1} stored as 2-bit codes w + 1 with the scalar
+    zero 1 (mode 1, shift only) and one tensor-wide weight scale applied to the finished sums."""
+    input_int8 = False
+
+    def __init__(self, device="cuda:0", dtype=None, fp32_scale=True):
+        self.device, self.dtype, self.fp32_scale = device, dtype, fp32_scale
+
+    def from_weights(self, weight, weight_scale, bias=None):
+        weight, bias = _data(weight), _data(bias)
+        dtype = weight.dtype if self.dtype is None else self.dtype
+        assert dtype in _FLOAT_DTYPES, "Invalid weight.dtype, should be floating point."
+        codes = (weight.to(device=self.device, dtype=dtype) + 1).to(torch.uint8)
+        out_features, in_features = codes.shape
+        scales = torch.full((out_features, 1), float(weight_scale.item() if hasattr(weight_scale, "item") else weight_scale),
+                            dtype=torch.float32 if self.fp32_scale else dtype, device=self.device)
+        layer = GemLiteLinear(2, group_size=in_features, in_features=in_features, out_features=out_features,
+                              input_dtype=DType.INT8 if self.input_int8 else TORCH_TO_DTYPE[dtype],
+                              output_dtype=TORCH_TO_DTYPE[dtype], scaled_activations=self.input_int8)
+        layer.pack(codes, scales=scales, zeros=1, bias=bias.to(device=self.device, dtype=dtype) if bias is not None else None)
+        layer.W_group_mode = 1                                   # shift only
+        layer.channel_scale_mode = 3 if self.input_int8 else 1   # activation and weight scales / weight scale, after the sum
+        return layer
+
+    def from_bitlinear(self, linear_layer, del_orig=True):
+        out = self.from_weights(linear_layer.weight, linear_layer.weight_scale, bias=linear_layer.bias)
+        cleanup_linear(linear_layer, del_orig)
+        return out
+
+
+class A16W158_INT(_Ternary):
+    input_int8 = False
+
+
+class A8W158_INT_dynamic(_Ternary):
+    input_int8 = True
+
+
 default_batch_sizes = [4096, 3072, 2048, 1536, 1024, 768, 512, 384, 256, 192, 128, 96, 64, 48, 32, 24, 16, 8, 4, 2, 1]
 
 

@@ -187,3 +187,49 @@ def test_fp8_times_packed_unscaled(lib, data):                  # tests/test_int
         return (torch.randn((M, K), generator=gx, dtype=CD, device=DEV) / 10.0).to(FP8)
 
     _check(layer, lambda x: x.to(CD) @ W.T, 5e-3, inputs)
+
+
+def test_processor_fp8_activations_packed_codes(lib, data):     # helper.py:712-870 (A8W4_HQQ_INT_dynamic)
+    from gemlite_b200 import helper
+    from gemlite_b200.quant_utils import scale_activations_per_token_torch
+    W, W_q, scales, zeros, xs = data
+    layer = helper.A8W4_HQQ_INT_dynamic(device=DEV, dtype=CD).from_weights(W_q, scales, zeros)
+    assert (layer.W_group_mode, layer.channel_scale_mode, layer.scaled_activations) == (3, 2, True)
+
+    def ref(x):
+        xq, sx = scale_activations_per_token_torch(x, w_dtype=FP8)
+        return (xq.to(CD) @ W.T) * sx
+
+    _check(layer, ref, 5e-3, lambda M: xs[M])
+    # one group per row with the weight scale folded into the epilogue
+    g = torch.Generator(device=DEV).manual_seed(21)
+    s_row = (torch.rand((N, 1), generator=g, device=DEV) * 1e-3 + 5e-4).to(CD)
+    z_row = torch.full((N, 1), 7.0, device=DEV, dtype=CD)
+    Wr = (W_q.to(torch.float32) - 7.0) * s_row.float()
+    for post_scale, modes in ((True, (1, 3)), (False, (3, 2))):
+        lyr = helper.A8W4_HQQ_INT_dynamic(device=DEV, dtype=CD, post_scale=post_scale).from_weights(W_q, s_row, z_row)
+        assert (lyr.W_group_mode, lyr.channel_scale_mode) == modes
+        _check(lyr, lambda x: ((scale_activations_per_token_torch(x, w_dtype=FP8)[0].float() @ Wr.T)
+                               * scale_activations_per_token_torch(x, w_dtype=FP8)[1]), 5e-3, lambda M: xs[M])
+
+
+@pytest.mark.parametrize("dynamic", [False, True])
+def test_processor_ternary_weights(lib, data, dynamic):         # helper.py:1208-1320 (A16W158_INT, A8W158_INT_dynamic)
+    from gemlite_b200 import helper
+    from gemlite_b200.quant_utils import scale_activations_per_token_torch
+    _, _, _, _, xs = data
+    g = torch.Generator(device=DEV).manual_seed(22)
+    w = (torch.randint(0, 3, (N, K), generator=g, device=DEV) - 1).to(CD)
+    bias = (torch.randn(N, generator=g, device=DEV) * 0.1).to(CD)
+    w_scale = torch.tensor(0.0123, device=DEV)
+    proc = (helper.A8W158_INT_dynamic if dynamic else helper.A16W158_INT)(device=DEV, dtype=CD)
+    layer = proc.from_weights(w, w_scale, bias=bias)
+    assert layer.W_nbits == 2 and layer.W_group_mode == 1 and layer.channel_scale_mode == (3 if dynamic else 1)
+
+    def ref(x):
+        if dynamic:
+            xq, sx = scale_activations_per_token_torch(x, w_dtype=torch.int8)
+            return (xq.float() @ w.float().T) * sx * 0.0123 + bias.float()
+        return (x.float() @ w.float().T) * 0.0123 + bias.float()
+
+    _check(layer, ref, 5e-3, lambda M: xs[M])
