@@ -233,3 +233,37 @@ def test_processor_ternary_weights(lib, data, dynamic):         # helper.py:1208
         return (x.float() @ w.float().T) * 0.0123 + bias.float()
 
     _check(layer, ref, 5e-3, lambda M: xs[M])
+
+
+# ---- the block-scaled processors on the reference's MX test (tests/test_mxfp.py:30-103): Linear(4224 -> 2048) with its
+# weights divided by 10, bf16, against the unquantised layer; tolerances as written there per processor
+MX_CASES = [  # (processor, keyword arguments, packed bytes per weight, tolerance)
+    ("A8W8_MXFP_dynamic", {"post_scale": True}, 1.0, 2e-4),
+    ("A8W8_MXFP_dynamic", {"post_scale": False}, 1.0, 2e-4),
+    ("A8W4_MXFP_dynamic", {}, 0.5, 7e-4),
+    ("A4W4_MXFP_dynamic", {}, 0.5, 1e-3),
+    ("A4W4_NVFP_dynamic", {}, 0.5, 2e-3),
+    ("A16W8_MXFP", {}, 1.0, 2e-4),          # (commented out there, same criterion)
+    ("A16W4_MXFP", {}, 0.5, 7e-4),
+]
+
+
+@pytest.mark.parametrize("name,kw,bytes_per_weight,tol", MX_CASES)
+def test_block_scaled_processors_on_the_reference_mx_case(lib, name, kw, bytes_per_weight, tol):
+    from gemlite_b200 import helper
+    Kmx, Nmx = 4224, 2048
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(Kmx, Nmx, device=DEV, dtype=CD, bias=False)
+    lin.weight.data /= 10.0
+    lin.weight.requires_grad = False
+    layer = getattr(helper, name)(device=DEV, dtype=CD, **kw).from_linear(lin, del_orig=False)
+    assert layer.W_q.numel() * layer.W_q.itemsize == int(Kmx * Nmx * bytes_per_weight)
+    assert layer.scaled_activations == (not name.startswith("A16"))
+    for M in [1, 3, 16, 30, 32, 60, 100, 128]:
+        g = torch.Generator(device=DEV).manual_seed(M)
+        x = torch.randn((M, Kmx), generator=g, dtype=CD, device=DEV) / 10.0
+        want = lin(x).float()
+        for fam in ("GEMM", "GEMM_SPLITK"):
+            got = layer.forward_manual(x, matmul_type=fam).float()
+            err = (want - got).abs().mean().item()
+            assert err < tol, (name, kw, fam, M, err, tol)
