@@ -770,13 +770,10 @@ __global__ void __launch_bounds__((6 + DQW) * 32, DQW == 4 ? 2 : 1) gl_gemm_tc_a
       if (need_s) { const XT sv = reinterpret_cast<const XT*>(wring + ws * WSLOT_BYTES + W_BYTES)[nl]; s2 = h2(sv, sv); }
       if (need_z) { const XT zv = reinterpret_cast<const XT*>(wring + ws * WSLOT_BYTES + W_BYTES + META_BYTES)[nl]; z2 = h2(zv, zv); }
       unsigned char* brow = st + A_BYTES + nl * 128;
-      // all packed words into registers first: the ring slot goes back to its producer at once, and the stores below may
-      // alias the words for the compiler
+      // all packed words into registers first (the stores below may alias the words for the compiler)
       uint32_t wv[RPW];
 #pragma unroll
       for (int cc = 0; cc < RPW; ++cc) wv[cc] = wst[(c_begin + cc) * BN + nl];
-      __syncwarp();
-      if (lane == 0) mbar_arrive(wempty + ws);
       TC_CK(c2);
       // the dequantised tile of K tile i - STAGES must have been consumed before its slot is overwritten (swapped: the
       // tile is built in registers first and the wait comes before the store to tensor memory)
@@ -842,6 +839,14 @@ __global__ void __launch_bounds__((6 + DQW) * 32, DQW == 4 ? 2 : 1) gl_gemm_tc_a
         }
       };
       if (p.W_group_mode == 4) unpack_tile(std::true_type{}); else unpack_tile(std::false_type{});
+      // The ring slot goes back to its producer only now, after the tile has been unpacked.  Handing it back right after
+      // the loads above (words, scale and zero already in registers) gave wrong values in 16-byte granules of a tile's
+      // scale row (8 columns, all rows of the tile) in a few calls out of a hundred whenever the MMAs, not the dequant
+      // warps, set the pace (two accumulators per CTA); neither volatile loads, nor an instruction consuming the words
+      // before the arrive, nor expect_tx ordered before the scale / zero copies changed that, so the cause is not known.
+      // Released here the same calls were bit-identical 540 times out of 540, at the same speed.
+      __syncwarp();
+      if (lane == 0) mbar_arrive(wempty + ws);
       TC_CK(c4); TC_ACC(acc2, c3, c4);
       if constexpr (SW > 0) {
         if (first_of_stage) {

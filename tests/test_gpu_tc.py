@@ -166,6 +166,37 @@ def test_a16wn_partial_last_wave_runs_as_half_tiles(lib, N, nbits, gs):
     assert rel_fro(got[:, -8:], want[:, -8:]) < 1e-2
 
 
+@pytest.mark.parametrize("M,cfg", [(2597, b'{}'), (2048, b'{"tail": 0}'), (2597, b'{"tail": 0, "tile_n": 128}')])
+def test_a16wn_back_to_back_calls_are_bit_identical(lib, M, cfg):
+    """Two accumulators per CTA make the MMAs, not the dequant warps, set the pace: the regime in which a packed-word
+    slot handed back to its producer before the tile was unpacked gave wrong scale granules in 10-25 % of the calls.
+    48 calls in a row (each overlapping the previous one's tail) must agree bit for bit, and with the dequantised product."""
+    from gemlite_b200 import helper, _lib
+    L = _lib.lib()
+    N, K = 3976, 2048
+    x, W_q, s, z, b = make_a16wn(N, K, 4, 128, torch.bfloat16, seed=62, M=M)
+    layer = helper.A16W4_HQQ_INT(device="cuda:0", dtype=torch.bfloat16).from_weights(W_q.cuda(), s.cuda(), z.cuda(), bias=b.cuda())
+    xd = x.cuda()
+    sig = "(%d, %d, %d, 128, 8, 104)" % (L.gl_get_closest_m(M), N, K)
+    try:
+        assert L.gl_cfg_set(b"GEMM", sig.encode(), cfg) == 0
+        outs = [layer(xd).clone() for _ in range(48)]
+        torch.cuda.synchronize()
+    finally:
+        L.gl_cfg_set(b"GEMM", sig.encode(), b'{}')
+    assert _status_word() == 0
+    differing = [i for i, o in enumerate(outs) if not torch.equal(o, outs[0])]
+    assert differing == [], differing
+    Wd = ((W_q.double().view(N, -1, 128) - z.view(N, -1).double()[..., None]) * s.view(N, -1).double()[..., None]).view(N, K)
+    want = (x.double() @ Wd.T + b.double()).numpy()
+    got = outs[-1].float().cpu().numpy()
+    assert rel_fro(got, want) < 1e-2
+    # no 32-column block of any 256-row tile may stand out either (a wrong scale granule is invisible in the whole-matrix norm)
+    err = np.abs(got - want)
+    blk = err[: (M // 256) * 256, : (N // 32) * 32].reshape(M // 256, 256, N // 32, 32).mean(axis=(1, 3))
+    assert blk.max() < 4 * np.median(blk) + 1e-3, (float(blk.max()), float(np.median(blk)))
+
+
 @pytest.mark.parametrize("kind", ["fp8", "a16w4"])
 def test_banded_tile_order_for_large_activations(lib, kind):
     """Activations of 64 MB and more switch the tile numbering to bands of 2048 rows (the last band short, the last row
