@@ -842,9 +842,10 @@ __global__ void __launch_bounds__((6 + DQW) * 32, DQW == 4 ? 2 : 1) gl_gemm_tc_a
       // The ring slot goes back to its producer only now, after the tile has been unpacked.  Handing it back right after
       // the loads above (words, scale and zero already in registers) gave wrong values in 16-byte granules of a tile's
       // scale row (8 columns, all rows of the tile) in a few calls out of a hundred whenever the MMAs, not the dequant
-      // warps, set the pace (two accumulators per CTA); neither volatile loads, nor an instruction consuming the words
-      // before the arrive, nor expect_tx ordered before the scale / zero copies changed that, so the cause is not known.
-      // Released here the same calls were bit-identical 540 times out of 540, at the same speed.
+      // warps, set the pace (two accumulators per CTA); neither volatile loads, nor an instruction consuming words, scale
+      // and zero before the arrive, nor a warp barrier before the proxy fence, nor expect_tx ordered before the scale /
+      // zero copies changed that, so the cause is not known.  Released here the same calls were bit-identical in some
+      // 3000 calls out of 3000, at the same speed.
       __syncwarp();
       if (lane == 0) mbar_arrive(wempty + ws);
       TC_CK(c4); TC_ACC(acc2, c3, c4);
