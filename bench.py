@@ -475,8 +475,8 @@ def check_output(layer, fmt, x, y, W_ref=None):
     if fmt.startswith("A16"):
         W = W_ref if W_ref is not None else _dequant_packed_int(layer)
         ref = x[idx].float() @ W + (layer.bias.float() if layer.bias is not None else 0.0)
-    elif fmt == "FP8":
-        xq, sx = qu.scale_activations_per_token(x, torch.float8_e4m3fn)
+    elif fmt in ("FP8", "INT8"):
+        xq, sx = qu.scale_activations_per_token(x, torch.float8_e4m3fn if fmt == "FP8" else torch.int8)
         ref = (xq[idx].float() @ layer.W_q.float()) * sx[idx].view(-1, 1) * layer.scales.float().view(1, -1)
     elif fmt == "FP8blk":          # 128 x 128 block scales: per-block partial products scaled by s_x[m, kb] * s_w[kb, nb]
         xq, sx = qu.scale_activations_per_block(x, torch.float8_e4m3fn)
@@ -584,7 +584,7 @@ def sweep_gemm(device, only=None, mma_peaks=None):
     ref_graph = bench_reference().get("reference_triton_timings_graph", {}).get("timings", {})
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.int8, device=device)
     dense_peak = {"A16W4": 2250.0, "A16W2": 2250.0, "A16W8": 2250.0, "FP8": 4500.0, "MXFP4": 9000.0, "NVFP4": 9000.0,
-                  "A16W8c": 2250.0, "A16W4MX": 2250.0, "MXFP8": 4500.0, "FP8blk": 4500.0}     # nominal dense TFLOP/s
+                  "A16W8c": 2250.0, "A16W4MX": 2250.0, "MXFP8": 4500.0, "FP8blk": 4500.0, "INT8": 4500.0}     # nominal dense TFLOP/s
 
     def timed(fn, reps=10):
         for _ in range(3):
@@ -609,12 +609,12 @@ def sweep_gemm(device, only=None, mma_peaks=None):
             z = (torch.rand(N * K // gs, 1, generator=g, device=device) * (2 ** nbits - 1)).to(torch.bfloat16)
             b = (torch.randn(N, generator=g, device=device) * 0.01).to(torch.bfloat16)
             return helper.A16Wn_HQQ_INT(device=str(device), dtype=torch.bfloat16, W_nbits=nbits).from_weights(W_q, sc, z, bias=b), K, N
-        K, N = (4096, 14336) if fmt == "FP8" else ((8192, 8192) if fmt in ("A16W8c", "A16W4MX", "MXFP8", "FP8blk") else (16384, 16384))
+        K, N = (4096, 14336) if fmt in ("FP8", "INT8") else ((8192, 8192) if fmt in ("A16W8c", "A16W4MX", "MXFP8", "FP8blk") else (16384, 16384))
         lin = torch.nn.Linear(K, N, bias=False, dtype=torch.bfloat16, device=device)
         lin.weight.data.normal_(0, 0.02, generator=g)
         # A16W8c: weight-only INT8 with one scale per channel; A16W4MX: weight-only MXFP4 (16-bit activations)
         P = {"FP8": helper.A8W8_FP8_dynamic, "MXFP4": helper.A4W4_MXFP_dynamic, "NVFP4": helper.A4W4_NVFP_dynamic,
-             "A16W8c": helper.A16W8_INT8, "A16W4MX": helper.A16W4_MXFP, "MXFP8": helper.A8W8_MXFP_dynamic, "FP8blk": helper.A8W8_FP8_dynamic}[fmt]
+             "A16W8c": helper.A16W8_INT8, "A16W4MX": helper.A16W4_MXFP, "MXFP8": helper.A8W8_MXFP_dynamic, "FP8blk": helper.A8W8_FP8_dynamic, "INT8": helper.A8W8_INT8_dynamic}[fmt]
         if fmt == "FP8blk":      # one fp32 scale per 128 x 128 weight block, activations per row and 128 k
             return P(device=str(device), dtype=torch.bfloat16, block_quant=True).from_linear(lin), K, N
         if fmt == "MXFP8":       # block scales on both operands
@@ -624,17 +624,17 @@ def sweep_gemm(device, only=None, mma_peaks=None):
     res = []
     stream = torch.cuda.Stream(device)
     cases = (("A16W4", (32, 64, 256, 1024, 4096, 8192)), ("A16W2", (1, 16, 64, 256, 1024, 4096, 8192)), ("A16W8", (1, 16, 1024)), ("FP8", (1, 16, 128, 1024, 4096)),
-             ("MXFP4", (1, 64, 512, 4096, 16384)), ("NVFP4", (1, 64, 512, 4096, 16384)), ("A16W8c", (1, 4)), ("A16W4MX", (1, 4)), ("MXFP8", (1, 4096)), ("FP8blk", (1024, 4096)))
+             ("MXFP4", (1, 64, 512, 4096, 16384)), ("NVFP4", (1, 64, 512, 4096, 16384)), ("A16W8c", (1, 4)), ("A16W4MX", (1, 4)), ("MXFP8", (1, 4096)), ("FP8blk", (1024, 4096)), ("INT8", (1, 4096)))
     if only is not None:
         cases = ((only[0], (only[1],)),)
     for fmt, Ms in cases:
         try:
             layer, K, N = make(fmt)
-            wbytes = N * K // {"FP8": 1, "A16W8": 1, "A16W8c": 1, "MXFP8": 1, "FP8blk": 1, "A16W2": 4}.get(fmt, 2)
+            wbytes = N * K // {"FP8": 1, "INT8": 1, "A16W8": 1, "A16W8c": 1, "MXFP8": 1, "FP8blk": 1, "A16W2": 4}.get(fmt, 2)
             W_ref = (layer.W_q.float() * layer.scales.float().view(1, -1)) if fmt == "A16W8c" else (
                 _decode_fp4(layer.W_q.t().contiguous(), layer.scales.contiguous().view(torch.uint8), 32, True).t().contiguous()) if fmt == "A16W4MX" else (
                 _dequant_packed_int(layer)) if fmt.startswith("A16") else (
-                None if fmt in ("FP8", "MXFP8", "FP8blk") else _decode_fp4(layer.W_q.t().contiguous(), layer.scales.contiguous().view(torch.uint8),
+                None if fmt in ("FP8", "INT8", "MXFP8", "FP8blk") else _decode_fp4(layer.W_q.t().contiguous(), layer.scales.contiguous().view(torch.uint8),
                                                       32 if fmt == "MXFP4" else 16, fmt == "MXFP4"))
             for M in Ms:
                 x = torch.randn(M, K, dtype=torch.bfloat16, device=device)
@@ -664,10 +664,10 @@ def sweep_gemm(device, only=None, mma_peaks=None):
                     row["ms"] = ms
                 tf = 2.0 * M * N * K / ms / 1e9
                 row.update({"TFLOPs": tf, "frac_dense_nominal": tf / dense_peak[fmt]})
-                pk = (mma_peaks or {}).get({"FP8": "fp8", "MXFP8": "fp8", "FP8blk": "fp8", "MXFP4": "mxfp4", "NVFP4": "nvfp4"}.get(fmt, "bf16"))
+                pk = (mma_peaks or {}).get({"FP8": "fp8", "INT8": "int8", "MXFP8": "fp8", "FP8blk": "fp8", "MXFP4": "mxfp4", "NVFP4": "nvfp4"}.get(fmt, "bf16"))
                 if pk:
                     row["frac_measured_mma_peak"] = tf / pk
-                key = "%s_%dx%d_M%d" % (fmt, K if fmt == "FP8" else N, N if fmt == "FP8" else K, M)
+                key = "%s_%dx%d_M%d" % (fmt, K if fmt in ("FP8", "INT8") else N, N if fmt in ("FP8", "INT8") else K, M)
                 r, rg = ref.get(key), ref_graph.get(key)
                 if rg and M <= 512:          # same protocol as this row: graph replay over distinct layers
                     row["ref_triton_ms"] = rg["ms_per_layer"]
