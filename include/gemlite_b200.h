@@ -85,7 +85,10 @@ enum {
  *            (s_stride_n, s_stride_g) given the same way (s_stride_g = distance between
  *            groups of one output column).
  *   zeros    same layout as scales, dtype zeros_dtype; or one scalar when zero_is_scalar.
- *   scales_x activation scales: [M] fp32 (modes 2/3), [Mpad, K/gx] bytes (mode 4).
+ *            128x128 block quantisation (mode 5): fp32, logical [K/128, N/128] (both rounded up) with
+ *            strides (s_stride_g, s_stride_n); unpacked 8-bit weights (gemlite/helper.py:517-617).
+ *   scales_x activation scales: [M] fp32 (modes 2/3), [Mpad, K/gx] bytes (mode 4),
+ *            [M, K/128] fp32 (mode 5, from gl_scale_activations_per_block).
  *   bias     [N] in out_dtype or NULL.  Fused into the kernel epilogue (the reference adds
  *            it with a separate torch op, gemlite/core.py:271-272).
  *   out      [M,N] row-major, out_dtype (FP16/BF16/FP32).
