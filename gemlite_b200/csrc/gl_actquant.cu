@@ -81,6 +81,19 @@ __device__ __forceinline__ uint32_t e2m1x2_from16(float a, float b) {
   return (uint32_t)__nv_cvt_float2_to_fp4x2(make_float2(__uint_as_float(ua), __uint_as_float(ub)), __NV_E2M1, cudaRoundNearest);
 }
 
+// (row, first k) of unit u, units of 8 consecutive k: a shift and a mask when a row holds a power of two of them (`shift`
+// >= 0; every benchmark shape), else the 64-bit division (a subroutine of about a hundred instructions)
+__device__ __forceinline__ void unit_row_k(int64_t u, int64_t units_per_row, int shift, int& m, int& k) {
+  if (shift >= 0) {
+    m = (int)(u >> shift);
+    k = (int)(u & (units_per_row - 1)) * 8;
+  } else {
+    m = (int)(u / units_per_row);
+    k = (int)(u % units_per_row) * 8;
+  }
+}
+__device__ __forceinline__ int pow2_shift(int64_t v) { return (v & (v - 1)) == 0 ? 63 - __clzll(v) : -1; }
+
 // ---------------------------------------------------------------------------------------------
 // per-token: one CTA per row (grid-stride), two passes over the row (second one hits L1/L2)
 template <bool INT8>
@@ -138,12 +151,13 @@ __global__ void __launch_bounds__(256) mx_quant_kernel(const void* __restrict__ 
   gl_grid_dependency_wait();
   const int64_t units_per_row = K / 8;
   const int64_t total = (int64_t)Mpad * units_per_row;
+  const int shift = pow2_shift(units_per_row);
   // the loop bound is warp-uniform so that every lane takes part in the group shuffles
   for (int64_t u0 = blockIdx.x * (int64_t)blockDim.x + (threadIdx.x & ~31); u0 < total; u0 += (int64_t)gridDim.x * blockDim.x) {
     const int64_t u = u0 + (threadIdx.x & 31);
     const bool valid = u < total;
-    const int m = valid ? (int)(u / units_per_row) : Mpad;
-    const int k = valid ? (int)(u % units_per_row) * 8 : 0;
+    int m = Mpad, k = 0;
+    if (valid) unit_row_k(u, units_per_row, shift, m, k);
     float v[8];
     const bool real = m < M;
     if (real) load8(x, (int64_t)m * K + k, x_dtype, v);
@@ -221,12 +235,13 @@ __global__ void __launch_bounds__(256) nvfp4_quant_kernel(const void* __restrict
   if (blockIdx.x == 0 && threadIdx.x == 0) *meta_out = meta;
   const int64_t units_per_row = K / 8;
   const int64_t total = (int64_t)Mpad * units_per_row;
+  const int shift = pow2_shift(units_per_row);
   // the loop bound is warp-uniform so that every lane takes part in the group shuffles
   for (int64_t u0 = blockIdx.x * (int64_t)blockDim.x + (threadIdx.x & ~31); u0 < total; u0 += (int64_t)gridDim.x * blockDim.x) {
     const int64_t u = u0 + (threadIdx.x & 31);
     const bool valid = u < total;
-    const int m = valid ? (int)(u / units_per_row) : Mpad;
-    const int k = valid ? (int)(u % units_per_row) * 8 : 0;
+    int m = Mpad, k = 0;
+    if (valid) unit_row_k(u, units_per_row, shift, m, k);
     const bool real = m < M;
     float v[8];
     if (real) load8(x, (int64_t)m * K + k, x_dtype, v);
@@ -293,10 +308,12 @@ __global__ void __launch_bounds__(256) per_block_kernel(const void* __restrict__
   gl_grid_dependency_wait();
   const float qmax = INT8 ? 127.f : 448.f, qmin = INT8 ? -128.f : -448.f;
   const int units_per_row = K / 8;
+  const int shift = pow2_shift(units_per_row);
   // the loop bound is half-warp-uniform: a block's sixteen units are either all inside or all outside
   for (int64_t u0 = blockIdx.x * (int64_t)blockDim.x + (threadIdx.x & ~15); u0 < total_units; u0 += (int64_t)gridDim.x * blockDim.x) {
     const int64_t u = u0 + (threadIdx.x & 15);
-    const int m = (int)(u / units_per_row), k = (int)(u % units_per_row) * 8;
+    int m, k;
+    unit_row_k(u, units_per_row, shift, m, k);
     float v[8];
     load8(x, (int64_t)m * K + k, x_dtype, v);
     float amax = 0.f;
