@@ -59,13 +59,6 @@ __device__ __forceinline__ int64_t scale_index(int m, int kg, int G, int layout)
   return ((int64_t)(m >> 7) * (G >> 2) + (kg >> 2)) * 512 + (m & 31) * 16 + ((m & 127) >> 5) * 4 + (kg & 3);
 }
 
-// e2m1 code of a scaled value: number of magnitude thresholds exceeded, sign in bit 3
-__device__ __forceinline__ uint32_t e2m1_code(float v) {
-  const float a = fabsf(v);
-  uint32_t idx = (a > 0.25f) + (a > 0.75f) + (a > 1.25f) + (a > 1.75f) + (a > 2.5f) + (a > 3.5f) + (a > 5.0f);
-  return (v >= 0.f) ? idx : (idx + 8u);
-}
-
 // Two e2m1 codes (low nibble = a, high nibble = b) of values that came from 16-bit activations times a power of two.
 // The reference's thresholds are strict (> 0.25, > 0.75, ...): a value exactly half way between two e2m1 numbers goes to
 // the smaller magnitude, and -0.0 gets code 0.  The hardware conversion rounds half to even, so each value is first
@@ -79,6 +72,20 @@ __device__ __forceinline__ uint32_t e2m1x2_from16(float a, float b) {
   ua = (ua << 1) ? ua - 1u : 0u;
   ub = (ub << 1) ? ub - 1u : 0u;
   return (uint32_t)__nv_cvt_float2_to_fp4x2(make_float2(__uint_as_float(ua), __uint_as_float(ub)), __NV_E2M1, cudaRoundNearest);
+}
+
+// Two e2m1 codes of arbitrary fp32 values (NVFP4, fp32 activations): the hardware conversion (round half to even) agrees
+// with the reference's strict thresholds except on the three midpoints it rounds up, 0.75 / 1.75 / 3.5, where the code
+// is one too high, and on -0.0, which the reference codes as +0 (`v >= 0`); both are put right here.  Seven compares
+// and adds per value become three compares.
+__device__ __forceinline__ uint32_t e2m1x2_exact(float a, float b) {
+  a = __fadd_rn(a, 0.0f);                                  // -0.0 -> +0.0, everything else unchanged
+  b = __fadd_rn(b, 0.0f);
+  const uint32_t c = (uint32_t)__nv_cvt_float2_to_fp4x2(make_float2(a, b), __NV_E2M1, cudaRoundNearest);
+  const uint32_t ma = __float_as_uint(a) & 0x7fffffffu, mb = __float_as_uint(b) & 0x7fffffffu;
+  const uint32_t ta = (ma == 0x3f400000u) | (ma == 0x3fe00000u) | (ma == 0x40600000u);
+  const uint32_t tb = (mb == 0x3f400000u) | (mb == 0x3fe00000u) | (mb == 0x40600000u);
+  return c - ta - (tb << 4);
 }
 
 // (row, first k) of unit u, units of 8 consecutive k: a shift and a mask when a row holds a power of two of them (`shift`
@@ -179,7 +186,7 @@ __global__ void __launch_bounds__(256) mx_quant_kernel(const void* __restrict__ 
       uint32_t o = 0u;
       if (x_dtype == GL_FP32) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) o |= e2m1_code(v[i] * inv) << (4 * i);
+        for (int i = 0; i < 4; ++i) o |= e2m1x2_exact(v[2 * i] * inv, v[2 * i + 1] * inv) << (8 * i);
       } else {
 #pragma unroll
         for (int i = 0; i < 4; ++i) o |= e2m1x2_from16(v[2 * i] * inv, v[2 * i + 1] * inv) << (8 * i);
@@ -260,7 +267,7 @@ __global__ void __launch_bounds__(256) nvfp4_quant_kernel(const void* __restrict
     const float sfull = fmaxf(gl_e4m3_to_float(s8) / meta, 1e-6f);
     uint32_t o = 0u;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) o |= e2m1_code(v[i] / sfull) << (4 * i);
+    for (int i = 0; i < 4; ++i) o |= e2m1x2_exact(v[2 * i] / sfull, v[2 * i + 1] / sfull) << (8 * i);
     *reinterpret_cast<uint32_t*>(q + (int64_t)m * (K / 2) + k / 2) = o;
   }
 }

@@ -67,6 +67,48 @@ def test_nvfp4_dynamic_and_static(lib, M, K):
     assert np.array_equal(s.view(torch.uint8).cpu().numpy(), os_) and np.array_equal(q.cpu().numpy(), oq)
 
 
+def _midpoint_groups(scale, group):
+    """Rows of groups whose scaled values sit on and next to every e2m1 midpoint, both signs, with signed zeros: the
+    group's largest magnitude is 6 * scale, so the group scale is exactly `scale` (a power of two)."""
+    mids = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], dtype=np.float32)
+    vals = []
+    for m in mids:
+        for d in (0, 1, -1):                                  # the midpoint, one fp32 ulp above it, one below
+            f = np.nextafter(m, np.float32(np.inf if d > 0 else -np.inf)) if d else m
+            vals += [f, -f]
+    vals += [0.0, -0.0, 1e-30, -1e-30, 0.1, -0.1, 6.0, -6.0, 7.5, 5.5, -5.5, 0.5, 1.0, -3.0]
+    vals = np.array(vals, dtype=np.float32)
+    n_groups = -(-len(vals) // (group - 1))
+    out = np.zeros((n_groups, group), dtype=np.float32)
+    for g in range(n_groups):
+        chunk = vals[g * (group - 1):(g + 1) * (group - 1)]
+        out[g, :len(chunk)] = chunk
+        out[g, group - 1] = 6.0                               # pins the group's amax (7.5 is clipped below)
+    out = np.clip(out, -6.0, 6.0)
+    return (out * np.float32(scale)).astype(np.float32)
+
+
+def test_fp4_codes_on_and_around_the_midpoints(lib):
+    """The codes come from the hardware conversion plus corrections (ties go to the smaller magnitude, -0.0 is +0): values
+    exactly on a midpoint, one ulp either side, signed zeros and saturation, against the oracle's thresholds."""
+    from gemlite_b200 import quant_utils as qu
+    # NVFP4 with a given tensor scale of 1: group scale = e4m3(amax / 6) = 0.5, so x / 0.5 is exact
+    g16 = _midpoint_groups(0.5, 16)
+    x = torch.from_numpy(g16.reshape(1, -1).copy())
+    x = torch.cat([x, torch.zeros(1, (-x.shape[1]) % 64)], dim=1) if x.shape[1] % 64 else x
+    q, s, meta = qu.scale_activations_nvfp4(x.cuda(), meta_scale=torch.tensor([1.0], device="cuda"))
+    oq, os_, _ = oracle.scale_activations_nvfp4(x.numpy(), meta_scale=1.0)
+    assert np.array_equal(s.view(torch.uint8).cpu().numpy(), os_) and np.array_equal(q.cpu().numpy(), oq)
+    # MXFP4: fp32 activations (exact form) and bf16 activations (nudged form; the ulp neighbours round to the midpoints in bf16)
+    g32 = _midpoint_groups(0.25, 32)
+    x32 = torch.from_numpy(g32.reshape(1, -1).copy())
+    x32 = torch.cat([x32, torch.zeros(1, (-x32.shape[1]) % 128)], dim=1) if x32.shape[1] % 128 else x32
+    for xin in (x32, x32.to(torch.bfloat16), x32.to(torch.float16)):
+        q, s = qu.scale_activations_mxfp4(xin.cuda())
+        oq, os_ = oracle.scale_activations_mxfp4(xin.float().numpy())
+        assert np.array_equal(s.cpu().numpy(), os_) and np.array_equal(q.cpu().numpy(), oq), xin.dtype
+
+
 def test_full_size_properties(lib):
     # 4096 x 16384 bf16 (the largest benchmark activation that the oracle would take minutes on):
     # decoded values never exceed the group amax by more than the format allows, scales are powers of two
