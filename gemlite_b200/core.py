@@ -284,6 +284,8 @@ def _forward_impl(
     if _KERNEL_OVERRIDE != 1 and channel_scale_mode == 4 and input_dtype in (DType.MXFP4, DType.NVFP4, DType.MXFP8):
         w_atoms = _scale_atoms_of(scales)
     sx_layout = 0 if w_atoms is None else 1
+    if _KERNEL_OVERRIDE != 1 and channel_scale_mode == 2 and input_dtype == DType.MXFP8 and meta_args[1] == 8:
+        w_atoms = _scale_atoms_of(scales)      # MXFP8 weights, activations scaled per token: weight atoms only
     if bool(meta_args[0]) and enable_activation_scaling(x.numel() // x.shape[-1]):
         if input_dtype in FP8_INT8_DTYPES and channel_scale_mode == 5:
             x, scales_x = scale_activations_per_block(x, w_dtype=DTYPE_TO_TORCH[input_dtype.value])

@@ -294,6 +294,17 @@ __global__ void __launch_bounds__(192, 1) gl_gemm_tc_kernel(const __grid_constan
         reinterpret_cast<uint32_t*>(smem + s * STAGE_BYTES + A_BYTES + B_BYTES)[i] = 0u;
     fence_proxy_async_smem();
   }
+  if (MX && (p.sfa == nullptr || p.sfb == nullptr)) {
+    // an operand without block scales (activations quantised per token, their scale applied by the epilogue): its atoms
+    // are never loaded and hold e8m0 1.0 in every stage
+    __syncthreads();                                     // (after the zero fill above, which other threads did)
+    for (int s = 0; s < STAGES; ++s) {
+      uint32_t* sf = reinterpret_cast<uint32_t*>(smem + s * STAGE_BYTES + A_BYTES + B_BYTES);
+      if (p.sfa == nullptr) for (int i = threadIdx.x; i < SFA_BYTES / 4; i += blockDim.x) sf[i] = 0x7f7f7f7fu;
+      if (p.sfb == nullptr) for (int i = threadIdx.x; i < SFB_BYTES / 4; i += blockDim.x) sf[SFA_BYTES / 4 + i] = 0x7f7f7f7fu;
+    }
+    fence_proxy_async_smem();
+  }
   if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
   tc_fence_before();
   __syncthreads();
@@ -310,15 +321,15 @@ __global__ void __launch_bounds__(192, 1) gl_gemm_tc_kernel(const __grid_constan
         uint32_t bytes = A_BYTES + B_BYTES;
         if (MX) {
           const int atoms = min(KT::SF_ATOMS, p.sf_kblocks - kt * KT::SF_ATOMS);
-          bytes += WIDE_A ? (uint32_t)SFA_BYTES : (uint32_t)atoms * 512u;            // wide boxes are always whole
-          bytes += WIDE_B ? (uint32_t)SFB_BYTES : (uint32_t)atoms * 512u * valid_nb;
+          if (p.sfa != nullptr) bytes += WIDE_A ? (uint32_t)SFA_BYTES : (uint32_t)atoms * 512u;            // wide boxes are always whole
+          if (p.sfb != nullptr) bytes += WIDE_B ? (uint32_t)SFB_BYTES : (uint32_t)atoms * 512u * valid_nb;
         }
         return bytes;
       };
       auto load_a = [&](int kt, int s, int m0) {           // operand A of the kernel and its scale atoms
         unsigned char* st = smem + s * STAGE_BYTES;
         tma_load_2d(st, &tmA, full + s, kt * 128, m0);
-        if (MX) {
+        if (MX && p.sfa != nullptr) {
           const int atoms = min(KT::SF_ATOMS, p.sf_kblocks - kt * KT::SF_ATOMS);
           const size_t koff = (size_t)kt * KT::SF_ATOMS;
           if (WIDE_A) tma_load_4d(st + A_BYTES + B_BYTES, &tmSFA, full + s, 0, 0, kt * KT::SF_ATOMS, m0 / 128);
@@ -328,7 +339,7 @@ __global__ void __launch_bounds__(192, 1) gl_gemm_tc_kernel(const __grid_constan
       auto load_b = [&](int kt, int s, int n0, int valid_nb) {
         unsigned char* st = smem + s * STAGE_BYTES;
         tma_load_2d(st + A_BYTES, &tmB, full + s, kt * 128, n0);
-        if (MX) {
+        if (MX && p.sfb != nullptr) {
           const int atoms = min(KT::SF_ATOMS, p.sf_kblocks - kt * KT::SF_ATOMS);
           const size_t koff = (size_t)kt * KT::SF_ATOMS;
           if (WIDE_B) {
@@ -1131,9 +1142,12 @@ static TcPath classify(const gl_matmul_args* a) {
     return TC_A16WN;
   }
   // MXFP8 with block-scaled activations (A8W8_MXFP_dynamic): e4m3 x e4m3, e8m0 scale per 32 on both sides, given as atoms
-  if (a->input_dtype == GL_MXFP8 && a->x_dtype == GL_FP8 && a->w_dtype == GL_FP8 && e == 1 && a->W_nbits == 8 && a->channel_scale_mode == 4 &&
+  // ... or with activations quantised per token (A8W8_MXFP_dynamic(post_scale=True), channel_scale_mode 2): the same MMA kind
+  // with unit activation scale atoms, the token's fp32 scale applied by the epilogue
+  if (a->input_dtype == GL_MXFP8 && a->x_dtype == GL_FP8 && a->w_dtype == GL_FP8 && e == 1 && a->W_nbits == 8 &&
+      (a->channel_scale_mode == 4 || a->channel_scale_mode == 2) &&
       a->w_stride_k == 1 && a->w_stride_n == a->K && a->K % 128 == 0 && a->group_size == 32) {
-    if (a->w_scales_atoms == nullptr || a->scales_x == nullptr || a->sx_layout != 1) return TC_NONE;
+    if (a->w_scales_atoms == nullptr || a->scales_x == nullptr || (a->channel_scale_mode == 4 && a->sx_layout != 1)) return TC_NONE;
     if (((uintptr_t)a->w_scales_atoms & 15) || ((uintptr_t)a->scales_x & 15)) return TC_NONE;
     return TC_MXFP8;
   }
@@ -1378,15 +1392,17 @@ int gl_gemm_tc_launch(const gl_matmul_args* a, cudaStream_t st) {
     p.meta_scale = nullptr;
     const int bn8 = swap_bn ? swap_bn : BN;              // (256-column tiles copy this kind's single atom per operand block one by one)
     p.idesc = gl_idesc_block_scaled(0, 1, 128, bn8);     // formats: e4m3 x e4m3, e8m0 scales
+    const bool per_token = a->channel_scale_mode == 2;  // no activation atoms: fp32 scale per token in the epilogue
+    if (per_token) p.scales_x = reinterpret_cast<const float*>(a->scales_x);
     if (swap_bn) {
       p.M = a->N; p.N = a->M; p.swap = 1;
       p.sfa = reinterpret_cast<const uint8_t*>(a->w_scales_atoms);
-      p.sfb = reinterpret_cast<const uint8_t*>(a->scales_x);
+      p.sfb = per_token ? nullptr : reinterpret_cast<const uint8_t*>(a->scales_x);
       if (int rc = gl_make_tmap_2d(&tmA, a->w, 0, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)a->K, 128, 128, true)) return rc;
       if (int rc = gl_make_tmap_2d(&tmB, a->x, 0, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->K, 128, (uint32_t)swap_bn, true)) return rc;
       return swap_bn == 16 ? launch_tma_kernel<KIND_MXF8, 16, 8>(tmA, tmB, p, st) : launch_tma_kernel<KIND_MXF8, 32, 8>(tmA, tmB, p, st);
     }
-    p.sfa = reinterpret_cast<const uint8_t*>(a->scales_x);
+    p.sfa = per_token ? nullptr : reinterpret_cast<const uint8_t*>(a->scales_x);
     p.sfb = reinterpret_cast<const uint8_t*>(a->w_scales_atoms);
     if (int rc = gl_make_tmap_2d(&tmA, a->x, 0, (uint64_t)a->K, (uint64_t)a->M, (uint64_t)a->K, 128, 128, true)) return rc;
     if (int rc = gl_make_tmap_2d(&tmB, a->w, 0, (uint64_t)a->K, (uint64_t)a->N, (uint64_t)a->K, 128, (uint32_t)BN, true)) return rc;

@@ -172,6 +172,47 @@ def test_a8w8_mxfp8_block_scaled_tensor_core(lib, M):
     assert rel_fro(y, (x.double() @ W.double().T).numpy()) < 0.06
 
 
+@pytest.mark.parametrize("M", [1, 3, 16, 33, 100, 300, 1300, 3000])
+def test_a8w8_mxfp8_weights_per_token_activations_tensor_core(lib, M):
+    """A8W8_MXFP_dynamic(post_scale=True) (tests/test_mxfp.py:73-79): FP8 activations with one fp32 scale per token,
+    MXFP8 weights.  The block-scaled MMA runs with unit activation scale atoms and the epilogue applies the token scale;
+    checked against the product of the identical quantised operands and against the general kernel."""
+    import ctypes
+    from gemlite_b200 import core, helper, _lib, quant_utils as qu
+    N, K = 2048, 4224
+    g = torch.Generator().manual_seed(990 + M)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    x[M // 2] *= 37.0                                                            # token scales that differ a lot
+    lin = torch.nn.Linear(K, N, bias=True, dtype=torch.bfloat16)
+    lin.weight.data = (torch.randn(N, K, generator=g) / 10.0 / (K ** 0.5) * 8).to(torch.bfloat16)
+    lin.bias.data = (torch.randn(N, generator=g) * 0.5).to(torch.bfloat16)
+    W, bias = lin.weight.data.clone(), lin.bias.data.clone()
+    layer = helper.A8W8_MXFP_dynamic(device="cuda:0", dtype=torch.bfloat16, post_scale=True).from_linear(lin.cuda())
+    assert (layer.W_group_mode, layer.channel_scale_mode) == (0, 2)
+    xd = x.cuda()
+    xq, sx = qu.scale_activations_per_token(xd, torch.float8_e4m3fn)
+    out = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    a = core._fill_args(xq.view(M, K), layer.bias, layer.W_q, layer.scales, layer.zeros, sx, None, out, layer.get_meta_args(), -1,
+                        core._scale_atoms_of(layer.scales), 0)
+    assert _lib.lib().gl_matmul_kernel_name(ctypes.byref(a)).decode() == "gl_gemm_tc_kernel"
+    y = layer(xd).float().cpu().numpy()
+    assert core.matmul_status("cuda:0", clear=False) == 0
+    wq = layer.W_q.t().contiguous().view(torch.uint8).cpu().numpy()
+    sw = layer.scales.contiguous().view(torch.uint8).cpu().numpy()
+    Wd = (oracle.e4m3_decode(wq).astype(np.float64).reshape(N, K // 32, 32) * np.exp2(sw[:N].astype(np.float64) - 127.0)[..., None]).reshape(N, K)
+    xq_o, sx_o = oracle.scale_activations_per_token(x.float().numpy(), "fp8")
+    want_q = (oracle.e4m3_decode(xq_o).astype(np.float64) @ Wd.T) * sx_o.astype(np.float64).reshape(-1, 1) + bias.double().numpy()
+    assert rel_fro(y, want_q) < 5e-3, (M, rel_fro(y, want_q))
+    assert rel_fro(y[M // 2], want_q[M // 2]) < 5e-3 and rel_fro(y[-1], want_q[-1]) < 5e-3
+    core.set_kernel_override(1)
+    try:
+        yg = layer(xd).float().cpu().numpy()
+    finally:
+        core.set_kernel_override(0)
+    assert rel_fro(y, yg) < 5e-3
+    assert rel_fro(y, (x.double() @ W.double().T + bias.double()).numpy()) < 0.06
+
+
 @pytest.mark.parametrize("fmt", ["mxfp4", "nvfp4"])
 @pytest.mark.parametrize("M", [1, 3, 16, 64, 100])
 def test_a4w4_block_scaled(lib, fmt, M):
