@@ -34,6 +34,7 @@ def _check(tag, layer, K, rnd):
 def test_packed_layers(lib, seed):
     from gemlite_b200 import helper
     rnd = random.Random(seed)
+    torch.manual_seed(seed)
     for it in range(8):
         nbits, gs = rnd.choice([4, 4, 2, 8, 1]), rnd.choice([64, 128, 256])
         N, K = rnd.choice([8, 16, 32]) * rnd.randint(4, 180), gs * rnd.randint(2, 40)
@@ -50,6 +51,7 @@ def test_packed_layers(lib, seed):
 def test_quantised_activation_layers(lib, kind):
     from gemlite_b200 import helper
     rnd = random.Random(len(kind) * 7 + ord(kind[0]))
+    torch.manual_seed(len(kind))
     kw = dict(device=DEV, dtype=torch.bfloat16)
     make = {"fp8": lambda: helper.A8W8_FP8_dynamic(**kw), "int8": lambda: helper.A8W8_INT8_dynamic(**kw),
             "fp8_block": lambda: helper.A8W8_FP8_dynamic(block_quant=True, **kw),
