@@ -194,6 +194,74 @@ def scale_activations_mxfp4(tensor: Tensor, scale_layout: int = 0) -> Tuple[Tens
     return q, scales
 
 
+# ---- the block-scaled quantisers in plain torch ops (any device): the comparison points the reference keeps beside its
+# kernels (gemlite/quant_utils.py:712-747, 1131-1175, 1177-1224), here with the arithmetic of the active kernels so that
+# codes and scale bytes agree bit for bit with `scale_activations_mx*` / `_nvfp4` above (row layout of the scales).
+_E2M1_MIDPOINTS = (0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0)
+
+
+def _pow2_ceil_exponent(v: Tensor) -> Tensor:
+    """Biased exponent of 2^ceil(log2 v), clamped to [2^-30, 2^127], from the fp32 bit pattern (quant_utils.py:697-705)."""
+    bits = v.to(torch.float32).contiguous().view(torch.int32)
+    e = ((bits >> 23) & 0xFF) + ((bits & 0x7FFFFF) != 0).to(torch.int32)
+    return e.clamp(127 - 30, 254)
+
+
+def _e2m1_codes(v: Tensor) -> Tensor:
+    """e2m1 code of every value: the number of midpoints it exceeds, sign in bit 3 (quant_utils.py:66-73, 2081-2090)."""
+    a = v.abs()
+    idx = torch.zeros_like(v, dtype=torch.int32)
+    for t in _E2M1_MIDPOINTS:
+        idx += (a > t).to(torch.int32)
+    return torch.where(v >= 0, idx, idx + 8).to(torch.uint8)
+
+
+def _pad_rows(rows: int, pad: int) -> int:
+    return (rows + pad - 1) // pad * pad
+
+
+def scale_activations_mxfp8_torch(tensor: Tensor, w_dtype: torch.dtype = torch.float8_e4m3fn) -> Tuple[Tensor, Tensor]:
+    x = tensor.reshape(-1, tensor.shape[-1]).to(torch.float32)
+    M, K = x.shape
+    g = x.view(M, K // 32, 32)
+    e = _pow2_ceil_exponent(g.abs().amax(-1) / 448.0)
+    scale = (e << 23).view(torch.float32)
+    q = (g / scale.unsqueeze(-1)).clamp(-448.0, 448.0).to(w_dtype).view(tensor.shape)
+    scales = torch.full((_pad_rows(M, 32), K // 32), 127, dtype=torch.uint8, device=x.device)
+    scales[:M] = e.to(torch.uint8)
+    return q, scales
+
+
+def scale_activations_mxfp4_torch(tensor: Tensor) -> Tuple[Tensor, Tensor]:
+    x = tensor.reshape(-1, tensor.shape[-1]).to(torch.float32)
+    M, K = x.shape
+    g = x.view(M, K // 32, 32)
+    e = _pow2_ceil_exponent(g.abs().amax(-1) / 6.0)
+    scale = (e << 23).view(torch.float32)
+    codes = _e2m1_codes(g / scale.unsqueeze(-1)).view(M, K)
+    q = codes[:, 0::2] | (codes[:, 1::2] << 4)
+    scales = torch.full((_pad_rows(M, 32), K // 32), 127, dtype=torch.uint8, device=x.device)
+    scales[:M] = e.to(torch.uint8)
+    return q, scales
+
+
+def scale_activations_nvfp4_torch(tensor: Tensor, meta_scale=None) -> Tuple[Tensor, Tensor, Tensor]:
+    x = tensor.reshape(-1, tensor.shape[-1]).to(torch.float32)
+    M, K = x.shape
+    if meta_scale is None:
+        meta = torch.tensor(448.0 * 6.0, dtype=torch.float32, device=x.device) / x.abs().amax().clamp(min=1e-6)
+    else:
+        meta = torch.as_tensor(meta_scale, dtype=torch.float32, device=x.device).reshape(())
+    g = x.view(M, K // 16, 16)
+    s8 = ((g.abs().amax(-1) * meta) / 6.0).clamp(max=448.0).to(torch.float8_e4m3fn)
+    full = (s8.to(torch.float32) / meta).clamp(min=1e-6)
+    codes = _e2m1_codes(g / full.unsqueeze(-1)).view(M, K)
+    q = codes[:, 0::2] | (codes[:, 1::2] << 4)
+    scales = torch.full((_pad_rows(M, 16), K // 16), 1.0, dtype=torch.float32, device=x.device).to(torch.float8_e4m3fn)
+    scales[:M] = s8
+    return q, scales, meta.reshape(1)
+
+
 _NVFP4_SCRATCH = {}
 
 

@@ -109,6 +109,24 @@ def test_fp4_codes_on_and_around_the_midpoints(lib):
         assert np.array_equal(s.cpu().numpy(), os_) and np.array_equal(q.cpu().numpy(), oq), xin.dtype
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_kernels_match_the_torch_restatements_on_the_device(lib, dtype):
+    """The block-scaled `scale_activations_*_torch` run on the GPU as plain torch ops: same codes and scale bytes as the
+    kernels.  (The per-token one is not compared here: torch divides by a scalar on the GPU by multiplying with its
+    reciprocal, one ulp off the kernel's IEEE division; kernel and restatement each match the oracle on their own.)"""
+    from gemlite_b200 import quant_utils as qu
+    x = _x(77, 37, 4224, dtype, 2.0).cuda()
+    q, s = qu.scale_activations_mxfp8(x)
+    qt, st = qu.scale_activations_mxfp8_torch(x)
+    assert torch.equal(q.view(torch.uint8), qt.view(torch.uint8)) and torch.equal(s, st)
+    q, s = qu.scale_activations_mxfp4(x)
+    qt, st = qu.scale_activations_mxfp4_torch(x)
+    assert torch.equal(q, qt) and torch.equal(s, st)
+    q, s, m = qu.scale_activations_nvfp4(x)
+    qt, st, mt = qu.scale_activations_nvfp4_torch(x)
+    assert torch.equal(m.reshape(-1), mt.reshape(-1)) and torch.equal(q, qt) and torch.equal(s.view(torch.uint8), st.view(torch.uint8))
+
+
 def test_full_size_properties(lib):
     # 4096 x 16384 bf16 (the largest benchmark activation that the oracle would take minutes on):
     # decoded values never exceed the group amax by more than the format allows, scales are powers of two
