@@ -86,3 +86,34 @@ def test_weight_only_decode_kernels_are_selected():
     # grouped zeros or a K that is not a multiple of 16 bytes are not what these kernels take
     assert name(1, 8192, 8192, DType.INT8, 8, 1, 128, DType.BF16, 4, 0, 8192) == "gl_generic_kernel"
     assert name(1, 512, 1000, DType.INT8, 8, 1, 1000, DType.BF16, 2, 0, 1000) == "gl_generic_kernel"
+
+
+def test_quantised_activation_paths_are_selected():
+    """FP8 / INT8 with channel scales or 128 x 128 block scales, and MXFP8 weights with block-scaled or per-token
+    activations, go to the tensor-core kernels at every batch size; what they cannot take stays on the general kernel."""
+    L = _lib.lib()
+
+    def name(M, N, K, dt, csm, input_dtype=None, group=None, atoms=True, sx_layout=0, meta=DType.FP32):
+        a = _args(M, N, K, 8, K if group is None else group)
+        a.elements_per_sample = 1
+        a.w_dtype = a.x_dtype = dt.value
+        a.input_dtype = (dt if input_dtype is None else input_dtype).value
+        a.W_group_mode, a.channel_scale_mode = 0, csm
+        a.w_stride_k, a.w_stride_n = 1, K
+        a.meta_dtype = meta.value
+        a.scales_x = FAKE
+        a.sx_layout = sx_layout
+        a.w_scales_atoms = FAKE if atoms else None
+        a.s_stride_g, a.s_stride_n = (N + 127) // 128, 1
+        return L.gl_matmul_kernel_name(ctypes.byref(a)).decode()
+
+    for M in (1, 16, 17, 64, 300, 4096):
+        for dt in (DType.FP8, DType.INT8):
+            assert name(M, 14336, 4096, dt, 3) == "gl_gemm_tc_kernel"                    # per-token x per-channel scales
+            assert name(M, 8192, 8192, dt, 5) == "gl_gemm_tc_kernel"                     # 128 x 128 block scales
+        assert name(M, 8192, 8192, DType.FP8, 4, DType.MXFP8, 32, sx_layout=1) == "gl_gemm_tc_kernel"   # MXFP8 x MXFP8
+        assert name(M, 8192, 8192, DType.FP8, 2, DType.MXFP8, 32) == "gl_gemm_tc_kernel"                # MXFP8 weights, per-token x
+    # block scales that are not fp32, a K that is not a multiple of 128, MXFP8 without the scale atoms
+    assert name(64, 8192, 8192, DType.FP8, 5, meta=DType.BF16) == "gl_generic_kernel"
+    assert name(64, 8192, 4160, DType.FP8, 5) == "gl_generic_kernel"
+    assert name(64, 8192, 8192, DType.FP8, 2, DType.MXFP8, 32, atoms=False) == "gl_generic_kernel"
